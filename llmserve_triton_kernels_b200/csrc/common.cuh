@@ -1,0 +1,61 @@
+// Shared device helpers for the sm_100a kernels of this engine.
+//
+// Every exported launcher is `extern "C"`, takes raw device pointers, plain integers and the
+// stream it must launch on, and returns a cudaError_t as int (0 = success).  Element types are
+// passed as a code: 0 = float32, 1 = bfloat16.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LLM_F32 0
+#define LLM_BF16 1
+
+#define LLM_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Error codes above the CUDA range, for argument checks done in the launchers.
+#define LLM_ERR_BAD_ARGUMENT 10001
+#define LLM_ERR_UNSUPPORTED 10002
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads, same value returned to every thread.  `scratch` holds
+// 33 floats of shared memory.  The order of additions is fixed by the thread layout alone.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        const int nwarps = (blockDim.x + 31) >> 5;
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+static inline int launch_status() { return (int)cudaGetLastError(); }

@@ -1,0 +1,198 @@
+// Row-wise kernels: token embedding, RMS norm fused with the residual sum, rotary encoding fused
+// with the write of keys and values into their pages, and the gated activation.
+//
+// All of them are bound by memory traffic; each row is read once and written once.  Statistics,
+// angles and the residual sum are 32-bit whatever the element type.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// embedding: out[t, :] = float(table[ids[t], :])
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                             int hidden, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;  // launch-side checks reject such ids; never read out of range
+    const T* src = table + (size_t)id * hidden;
+    float* dst = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+LLM_EXPORT int llm_embed(const int* ids, const void* table, int table_dtype, float* out, int n, int hidden,
+                         int vocab, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == LLM_F32)
+        embed_kernel<float><<<n, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
+    else if (table_dtype == LLM_BF16)
+        embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+    else
+        return LLM_ERR_BAD_ARGUMENT;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMS norm with the residual sum: v = resid[row] (+ delta[row]); resid[row] = v (when all rows are
+// produced); out[i] = v * rsqrt(mean(v^2) + eps) * weight.  `rows` selects input rows (then the
+// residual is left untouched).
+// ---------------------------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ weight,
+                               float eps, const int* __restrict__ rows, TO* __restrict__ out, int hidden) {
+    extern __shared__ float row[];  // hidden floats, then 33 for the reduction
+    float* scratch = row + hidden;
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    float* x = resid + (size_t)r * hidden;
+    const TD* d = delta ? delta + (size_t)r * hidden : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[i];
+        if (d) v += to_float(d[i]);
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = rsqrtf(ss / (float)hidden + eps);
+    TO* y = out + (size_t)o * hidden;
+    const bool write_back = d && !rows;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = row[i];
+        if (write_back) x[i] = v;
+        y[i] = from_float<TO>(v * scale * weight[i]);
+    }
+}
+
+template <typename TD, typename TO>
+static int rmsnorm_launch(float* resid, const void* delta, const float* weight, float eps, const int* rows, void* out,
+                          int n_out, int hidden, cudaStream_t stream) {
+    const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+    if (smem > 200 * 1024) return LLM_ERR_UNSUPPORTED;
+    auto kernel = rmsnorm_kernel<TD, TO>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    kernel<<<n_out, threads, smem, stream>>>(resid, (const TD*)delta, weight, eps, rows, (TO*)out, hidden);
+    return launch_status();
+}
+
+LLM_EXPORT int llm_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* weight, float eps,
+                           const int* rows, void* out, int out_dtype, int n_out, int hidden, cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    if (out_dtype == LLM_F32 && (delta == nullptr || delta_dtype == LLM_F32))
+        return rmsnorm_launch<float, float>(resid, delta, weight, eps, rows, out, n_out, hidden, stream);
+    if (out_dtype == LLM_BF16 && (delta == nullptr || delta_dtype == LLM_BF16))
+        return rmsnorm_launch<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, eps, rows, out, n_out, hidden, stream);
+    if (out_dtype == LLM_BF16 && delta_dtype == LLM_F32)
+        return rmsnorm_launch<float, __nv_bfloat16>(resid, delta, weight, eps, rows, out, n_out, hidden, stream);
+    if (out_dtype == LLM_F32 && delta_dtype == LLM_BF16)
+        return rmsnorm_launch<__nv_bfloat16, float>(resid, delta, weight, eps, rows, out, n_out, hidden, stream);
+    return LLM_ERR_BAD_ARGUMENT;
+}
+
+// ---------------------------------------------------------------------------------------------
+// rotary encoding of q (in place) and k, and the write of k and v into their pages.
+//
+// qkv row: [H query heads | KV key heads | KV value heads] x D (the last two only when write_kv).
+// table row p: [cos(p * f_0..f_{D/2-1}) | sin(...)], 32-bit; null: no rotation.
+// pool plane: [pages, 2, KV, page_size, D]; slot = page * page_size + offset.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                     const float* __restrict__ table, int table_rows, const int* __restrict__ slot_map,
+                                     T* __restrict__ pool, int H, int KV, int D, int page_size, int write_kv) {
+    const int t = blockIdx.x;
+    T* row = qkv + (size_t)t * row_stride;
+    const int half = D >> 1;
+    int pos = positions[t];
+    if (pos < 0) pos = 0;
+    if (pos >= table_rows) pos = table_rows - 1;  // guarded on the host; never read out of range
+    const float* cs = table ? table + (size_t)pos * D : nullptr;
+
+    size_t k_base = 0, v_base = 0;
+    if (write_kv) {
+        const int slot = slot_map[t];
+        const int page = slot / page_size, off = slot - page * page_size;
+        k_base = ((size_t)(page * 2 + 0) * KV) * page_size * D + (size_t)off * D;
+        v_base = ((size_t)(page * 2 + 1) * KV) * page_size * D + (size_t)off * D;
+    }
+    const size_t head_stride = (size_t)page_size * D;
+
+    // query heads, rotated in place
+    for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        T* x = row + h * D;
+        const float a = to_float(x[j]), b = to_float(x[j + half]);
+        const float c = cs ? cs[j] : 1.f, s = cs ? cs[half + j] : 0.f;
+        x[j] = from_float<T>(a * c - b * s);
+        x[j + half] = from_float<T>(b * c + a * s);
+    }
+    if (!write_kv) return;
+    // key heads, rotated into their page
+    for (int i = threadIdx.x; i < KV * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        const T* x = row + (H + h) * D;
+        const float a = to_float(x[j]), b = to_float(x[j + half]);
+        const float c = cs ? cs[j] : 1.f, s = cs ? cs[half + j] : 0.f;
+        T* dst = pool + k_base + h * head_stride;
+        dst[j] = from_float<T>(a * c - b * s);
+        dst[j + half] = from_float<T>(b * c + a * s);
+    }
+    // value heads, copied
+    for (int i = threadIdx.x; i < KV * D; i += blockDim.x) {
+        const int h = i / D, j = i - h * D;
+        pool[v_base + h * head_stride + j] = row[(H + KV + h) * D + j];
+    }
+}
+
+LLM_EXPORT int llm_rope_kv_write(void* qkv, int dtype, int row_stride, const int* positions, const float* table,
+                                 int table_rows, const int* slot_map, void* pool, int n, int H, int KV, int D,
+                                 int page_size, int write_kv, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if ((D & 1) || D <= 0 || H <= 0 || KV < 0 || page_size <= 0) return LLM_ERR_BAD_ARGUMENT;
+    const int work = H * (D / 2);
+    const int threads = work >= 512 ? 256 : 128;
+    if (dtype == LLM_F32)
+        rope_kv_write_kernel<float><<<n, threads, 0, stream>>>((float*)qkv, row_stride, positions, table, table_rows,
+                                                               slot_map, (float*)pool, H, KV, D, page_size, write_kv);
+    else if (dtype == LLM_BF16)
+        rope_kv_write_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((__nv_bfloat16*)qkv, row_stride, positions, table,
+                                                                       table_rows, slot_map, (__nv_bfloat16*)pool, H, KV,
+                                                                       D, page_size, write_kv);
+    else
+        return LLM_ERR_BAD_ARGUMENT;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// gated activation: out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j], in 32-bit
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t t = i / inter;
+        const int j = (int)(i - t * inter);
+        const float g = to_float(gate_up[t * 2 * inter + j]);
+        const float u = to_float(gate_up[t * 2 * inter + inter + j]);
+        out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int inter, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const size_t total = (size_t)n * inter;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == LLM_F32)
+        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    else if (dtype == LLM_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+                                                                     inter, total);
+    else
+        return LLM_ERR_BAD_ARGUMENT;
+    return launch_status();
+}

@@ -1,0 +1,112 @@
+"""A runnable model built from a :class:`ModelPlan`: the same class for every architecture.
+
+It owns the token table, the layers (blocks of parts), the final norm and the output matrix,
+declares every tensor it expects by checkpoint name, and runs one step over a flat batch of
+tokens.  Parity for the order of operations: src/llmserve/model/llama.py:155-185 (embedding,
+the layers in order, gather of the wanted rows *before* the final norm, output matrix).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..parts.base import Block, PagedKVSpec, StateSpec, TensorSpec, build_part
+from .plan import ModelPlan
+
+
+class Model:
+    def __init__(self, plan: ModelPlan, dtype: torch.dtype, device: torch.device | str):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"compute dtype must be bfloat16 or float32, got {dtype}")
+        self.plan = plan
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.blocks: list[Block] = []
+        self._named_parts: list[tuple[str, object]] = []  # (prefix, part) of every tensor-owning part
+        for spec in plan.layers:
+            parts = {}
+            for role, category in (
+                ("mixer_norm", "norm"),
+                ("mixer", "mixer"),
+                ("ff_norm", "norm"),
+                ("feed_forward", "feed_forward"),
+            ):
+                part_spec = getattr(spec, role)
+                parts[role] = build_part(category, part_spec)
+                self._named_parts.append((part_spec.prefix, parts[role]))
+            block = build_part("block", type(spec.block)(spec.block.kind, {**spec.block.params, **parts}, spec.block.prefix))
+            self._named_parts.append((spec.block.prefix, block))
+            self.blocks.append(block)
+        self.final_norm = build_part("norm", plan.final_norm)
+        self._named_parts.append((plan.final_norm.prefix, self.final_norm))
+        self.embedding: torch.Tensor | None = None
+        self.head: torch.Tensor | None = None
+
+    # ------------------------------------------------------------------ tensors
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        """Every tensor of the checkpoint by its full name."""
+        plan = self.plan
+        specs = {plan.embedding: TensorSpec((plan.vocab_size, plan.hidden_size))}
+        for prefix, part in self._named_parts:
+            for local, spec in part.tensors().items():
+                name = prefix + local
+                if name in specs:
+                    raise ValueError(f"two parts claim the tensor {name!r}")
+                specs[name] = spec
+        if plan.head is not None:
+            specs[plan.head] = TensorSpec((plan.vocab_size, plan.hidden_size))
+        return specs
+
+    def ignored_tensor_names(self) -> set[str]:
+        """Names a checkpoint may carry that the model does not read (a copy of a tied output matrix)."""
+        return {"lm_head.weight"} if self.plan.head is None else set()
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        plan = self.plan
+        self.embedding = tensors[plan.embedding].to(device=self.device, dtype=self.dtype).contiguous()
+        if plan.head is None:
+            self.head = self.embedding
+        else:
+            self.head = tensors[plan.head].to(device=self.device, dtype=self.dtype).contiguous()
+        for prefix, part in self._named_parts:
+            local = {name: tensors[prefix + name] for name in part.tensors()}
+            part.bind(local, self.dtype, self.device)
+
+    def weight_bytes(self) -> int:
+        """Bytes of every distinct weight tensor a step reads (the token table only if it is also the head)."""
+        seen: dict[int, int] = {}
+
+        def visit(obj):
+            for value in vars(obj).values():
+                if isinstance(value, torch.Tensor):
+                    seen[value.data_ptr()] = value.numel() * value.element_size()
+                elif hasattr(value, "bind") and hasattr(value, "tensors"):
+                    visit(value)
+
+        for _, part in self._named_parts:
+            visit(part)
+        seen[self.head.data_ptr()] = self.head.numel() * self.head.element_size()
+        return sum(seen.values())
+
+    # ------------------------------------------------------------------ caches
+    def cache_specs(self) -> list[PagedKVSpec | StateSpec | None]:
+        """For each entry of the order: what its mixer keeps, or None if it keeps nothing of its
+        own (no cache, or it reads an earlier entry's)."""
+        out = []
+        for run in self.plan.schedule:
+            out.append(None if run.cache_of is not None else self.blocks[run.layer].mixer.cache_spec())
+        return out
+
+    # ------------------------------------------------------------------ step
+    def forward(self, ctx, caches) -> torch.Tensor:
+        """Run the tokens of ``ctx`` through every entry of the order; ``caches[i]`` is the view
+        of entry i's cache.  Returns 32-bit logits ``[len(ctx.logit_rows), vocab]``."""
+        resid = ops.embed(ctx.token_ids, self.embedding)
+        pending = None
+        for i, run in enumerate(self.plan.schedule):
+            pending = self.blocks[run.layer].forward(resid, pending, ctx, caches[i])
+        if ctx.num_logits == 0:
+            return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+        x = self.final_norm.add_forward(resid, pending, rows=ctx.logit_rows)
+        return ops.linear(x, self.head, out_dtype=torch.float32)

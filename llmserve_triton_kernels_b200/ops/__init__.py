@@ -1,0 +1,276 @@
+"""The engine's device operations: thin, checked wrappers over the CUDA library.
+
+Every function here launches hand-written sm_100a kernels from ``csrc/`` on the current CUDA
+stream (the bfloat16 matrix products may go to the vendor's library, as the reference's do:
+src/llmserve/model/llama.py:80-88, 120, 185 call ``F.linear``).  There is no CPU path: without
+a CUDA device, or if the library cannot be built and loaded, the first call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from . import build as _build
+
+_F32, _BF16 = 0, 1
+_lib = None
+_lock = threading.Lock()
+
+_vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_SIGNATURES = {
+    "llm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
+    "llm_rmsnorm": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
+    "llm_rope_kv_write": [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_attention_generic": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "llm_argmax": [_vp, _i, _i, _vp, _vp],
+    "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library():
+    """The loaded CUDA library; built first if it is missing or out of date."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not torch.cuda.is_available():
+                raise KernelError(
+                    "no CUDA device is visible: this engine has no CPU path (its kernels are sm_100a CUDA)"
+                )
+            path = _build.build()
+            lib = ctypes.CDLL(str(path))
+            for name, args in _SIGNATURES.items():
+                fn = getattr(lib, name)
+                fn.argtypes = args
+                fn.restype = ctypes.c_int
+            lib.llm_error_string.argtypes = [ctypes.c_int]
+            lib.llm_error_string.restype = ctypes.c_char_p
+            _lib = lib
+    return _lib
+
+
+def loaded_library_path() -> str | None:
+    return None if _lib is None else _lib._name
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        text = _lib.llm_error_string(code).decode() if _lib is not None else ""
+        raise KernelError(f"{what}: error {code} ({text})")
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"element type {dtype} is not supported (float32 or bfloat16)")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    _need(t.dtype == torch.int32 and t.is_contiguous() and t.is_cuda, f"{name} must be a contiguous int32 CUDA tensor")
+
+
+# ------------------------------------------------------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """``float32(table[ids])``: ids ``[N]`` int32, table ``[vocab, hidden]`` -> ``[N, hidden]`` float32."""
+    _i32(ids, "ids")
+    _need(table.dim() == 2 and table.is_contiguous(), "the token table must be a contiguous matrix")
+    n, (vocab, hidden) = ids.numel(), table.shape
+    out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _check(library().llm_embed(_ptr(ids), _ptr(table), _code(table.dtype), _ptr(out), n, hidden, vocab, _stream()), "embed")
+    return out
+
+
+def rmsnorm(
+    resid: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float,
+    delta: torch.Tensor | None = None,
+    rows: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.float32,
+) -> torch.Tensor:
+    """``v = resid (+ delta)``; returns ``v * rsqrt(mean(v^2) + eps) * weight`` in ``out_dtype``.
+    Without ``rows`` the sum is written back to ``resid`` (float32, in place); with ``rows``
+    (int32) only those rows are produced and ``resid`` is not changed."""
+    _need(resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous(), "the residual must be a contiguous float32 matrix")
+    _need(weight.dtype == torch.float32 and weight.numel() == resid.shape[1], "the norm weight must be float32 of the row size")
+    if delta is not None:
+        _need(delta.shape == resid.shape and delta.is_contiguous(), "delta must have the residual's shape")
+    if rows is not None:
+        _i32(rows, "rows")
+    n_out = resid.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n_out, resid.shape[1]), dtype=out_dtype, device=resid.device)
+    code = library().llm_rmsnorm(
+        _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else -1, _ptr(weight), float(eps),
+        _ptr(rows), _ptr(out), _code(out_dtype), n_out, resid.shape[1], _stream(),
+    )
+    _check(code, "rmsnorm")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x [M, K] @ w [N, K]^T -> [M, N]``.  float32 operands run on the CUDA cores in true 32-bit
+    (fixed summation order); bfloat16 operands accumulate in 32-bit on the tensor cores."""
+    _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not match")
+    _need(x.dtype == w.dtype, f"linear: operand types differ ({x.dtype}, {w.dtype})")
+    _need(x.stride(1) == 1 and w.is_contiguous(), "linear: operands must have unit inner stride")
+    out_dtype = out_dtype or x.dtype
+    m, k = x.shape
+    n = w.shape[0]
+    if x.dtype == torch.float32:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        code = library().llm_gemm_simt(
+            _ptr(x), _F32, _ptr(w), _F32, _ptr(out), _code(out_dtype), m, n, k, x.stride(0), k, n, _stream()
+        )
+        _check(code, "linear (float32)")
+        return out
+    _need(x.dtype == torch.bfloat16, f"linear: element type {x.dtype} is not supported")
+    library()  # the engine never runs without its kernels, even where a matrix product is the vendor's
+    if out_dtype == torch.bfloat16:
+        return torch.matmul(x, w.t())
+    return torch.matmul(x, w.t()).to(out_dtype)
+
+
+def rope_kv_write(
+    qkv: torch.Tensor,
+    positions: torch.Tensor,
+    table: torch.Tensor | None,
+    slot_map: torch.Tensor | None,
+    pool: torch.Tensor | None,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    write_kv: bool = True,
+) -> None:
+    """Rotate the query heads of each ``qkv`` row in place by its position's table row, and (with
+    ``write_kv``) store the rotated key heads and the value heads at the row's slot of ``pool``
+    ``[pages, 2, kv_heads, page_size, head_dim]``.  ``table`` None: no rotation."""
+    n = qkv.shape[0]
+    width = (num_heads + (2 * num_kv_heads if write_kv else 0)) * head_dim
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= width, f"qkv rows must hold {width} elements")
+    _i32(positions, "positions")
+    table_rows = 0
+    if table is not None:
+        _need(table.dtype == torch.float32 and table.is_contiguous() and table.shape[1] == head_dim, "the rotary table must be float32 [positions, head_dim]")
+        table_rows = table.shape[0]
+    page_size = 1
+    if write_kv:
+        _i32(slot_map, "slot_map")
+        _need(pool.dtype == qkv.dtype and pool.is_contiguous() and pool.dim() == 5, "the pool plane must be contiguous [pages, 2, kv_heads, page_size, head_dim] of the qkv type")
+        _need(pool.shape[1] == 2 and pool.shape[2] == num_kv_heads and pool.shape[4] == head_dim, "the pool plane does not match the heads")
+        page_size = pool.shape[3]
+    code = library().llm_rope_kv_write(
+        _ptr(qkv), _code(qkv.dtype), qkv.stride(0), _ptr(positions), _ptr(table), table_rows, _ptr(slot_map),
+        _ptr(pool), n, num_heads, num_kv_heads if write_kv else 0, head_dim, page_size, int(write_kv), _stream(),
+    )
+    _check(code, "rope_kv_write")
+
+
+def rope_inplace(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor) -> None:
+    """Rotate ``x [N, heads, head_dim]`` (a view with unit inner strides per head) in place."""
+    if x.shape[1] == 0 or x.shape[0] == 0:
+        return
+    _need(x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == x.shape[2], "rope_inplace: x must be [N, heads, head_dim] with packed heads")
+    flat = x.as_strided((x.shape[0], x.shape[1] * x.shape[2]), (x.stride(0), 1), x.storage_offset())
+    rope_kv_write(flat, positions, table, None, None, x.shape[1], 0, x.shape[2], write_kv=False)
+
+
+def paged_attention(
+    qkv: torch.Tensor,
+    pool: torch.Tensor,
+    page_table: torch.Tensor,
+    ctx,
+    *,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    scale: float,
+    window: int | None = None,
+) -> torch.Tensor:
+    """Attention of every new token over its request's cached keys and values.
+
+    ``qkv`` rows start with the (already rotated) query heads; the new tokens' keys and values are
+    already in ``pool``.  ``ctx`` gives ``token_request``, ``cu_tokens`` and ``context_lens``:
+    the token at flat row t of request r stands at position
+    ``context_lens[r] - (cu_tokens[r+1] - cu_tokens[r]) + (t - cu_tokens[r])`` and sees the keys
+    at positions ``max(0, p - window + 1) .. p``.  Returns ``[N, num_heads * head_dim]``."""
+    n = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] >= num_heads * head_dim, "qkv rows must start with the query heads")
+    _need(pool.dtype == qkv.dtype and pool.is_contiguous() and pool.dim() == 5, "the pool plane must be contiguous and of the query type")
+    _need(tuple(pool.shape[1:3]) == (2, num_kv_heads) and pool.shape[4] == head_dim, "the pool plane does not match the heads")
+    _need(head_dim % 16 == 0 and head_dim <= 256, f"head_dim {head_dim} is not supported (multiples of 16 up to 256)")
+    _i32(page_table, "page_table")
+    out = torch.empty((n, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    code = library().llm_attention_generic(
+        _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _code(qkv.dtype), _ptr(page_table),
+        page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), n, num_heads,
+        num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), _stream(),
+    )
+    _check(code, "paged_attention")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate_up[:, :I]) * gate_up[:, I:]`` computed in 32-bit -> ``[N, I]``."""
+    _need(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0, "gate_up must be a contiguous [N, 2 I] matrix")
+    n, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _check(library().llm_swiglu(_ptr(gate_up), _ptr(out), _code(gate_up.dtype), n, inter, _stream()), "swiglu")
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Index of the largest logit of each row (the lowest index among equals) -> int32 ``[rows]``."""
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous float32 matrix")
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    _check(library().llm_argmax(_ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(
+    logits: torch.Tensor,
+    temperature: torch.Tensor,
+    top_k: torch.Tensor,
+    top_p: torch.Tensor,
+    seeds: torch.Tensor,
+    counters: torch.Tensor,
+) -> torch.Tensor:
+    """One token per row: argmax where ``temperature <= 0``, else a draw from
+    ``softmax(logits / temperature)`` cut by ``top_k`` (0: off) and ``top_p`` (1: off) at the
+    uniform number that ``(seed, counter)`` gives.  All parameter tensors are ``[rows]`` on the
+    device: float32, int32, float32, int64, int64."""
+    _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous float32 matrix")
+    rows = logits.shape[0]
+    for t, dt, name in ((temperature, torch.float32, "temperature"), (top_k, torch.int32, "top_k"), (top_p, torch.float32, "top_p"), (seeds, torch.int64, "seeds"), (counters, torch.int64, "counters")):
+        _need(t.dtype == dt and t.numel() == rows and t.is_contiguous() and t.is_cuda, f"{name} must be {dt} [rows] on the device")
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    code = library().llm_sample(
+        _ptr(logits), rows, logits.shape[1], _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seeds), _ptr(counters),
+        _ptr(out), _stream(),
+    )
+    _check(code, "sample")
+    return out

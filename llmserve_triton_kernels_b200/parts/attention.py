@@ -1,0 +1,95 @@
+"""Grouped-query attention over a paged cache of keys and values.
+
+Parity: src/llmserve/model/llama.py:57-88 (projections without bias, rotary encoding of q and k
+before the cache write, head-major concatenation into the output projection) and
+src/llmserve/kvcache/paged.py:81-110 (key j is visible to the query at position p iff j <= p;
+consecutive query heads share a key/value head; softmax scale 1/sqrt(head_dim), which arrives
+here as the parameter ``scale``).  ``window`` (None in Llama) limits a query to the last
+``window`` keys, itself included.  With ``own_kv=False`` the layer has no key and value
+projections and reads the cache that an earlier layer of the order wrote.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Mixer, PagedKVSpec, PartSpec, TensorSpec, build_part, register_part
+
+
+class PagedAttention(Mixer):
+    def __init__(
+        self,
+        hidden_size: int,
+        num_heads: int,
+        num_kv_heads: int,
+        head_dim: int,
+        scale: float,
+        window: int | None = None,
+        position: PartSpec | None = None,
+        own_kv: bool = True,
+    ):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads {num_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if window is not None and window < 1:
+            raise ValueError(f"window must be positive or None, got {window}")
+        self.hidden_size = int(hidden_size)
+        self.num_heads = int(num_heads)
+        self.num_kv_heads = int(num_kv_heads)
+        self.head_dim = int(head_dim)
+        self.scale = float(scale)
+        self.window = None if window is None else int(window)
+        self.own_kv = bool(own_kv)
+        self.position = build_part("position", position) if position is not None else None
+        self.w_in: torch.Tensor | None = None  # [(H + 2 KV) D, hidden], or [H D, hidden] without own_kv
+        self.w_out: torch.Tensor | None = None  # [hidden, H D]
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        q = self.num_heads * self.head_dim
+        kv = self.num_kv_heads * self.head_dim
+        specs = {"q_proj.weight": TensorSpec((q, self.hidden_size))}
+        if self.own_kv:
+            specs["k_proj.weight"] = TensorSpec((kv, self.hidden_size))
+            specs["v_proj.weight"] = TensorSpec((kv, self.hidden_size))
+        specs["o_proj.weight"] = TensorSpec((self.hidden_size, q))
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        names = ["q_proj.weight"] + (["k_proj.weight", "v_proj.weight"] if self.own_kv else [])
+        fused = torch.cat([tensors[n].to(dtype) for n in names], dim=0)
+        self.w_in = fused.to(device).contiguous()
+        self.w_out = tensors["o_proj.weight"].to(device=device, dtype=dtype).contiguous()
+        if self.position is not None:
+            self.position.bind({}, dtype, device)
+
+    def cache_spec(self) -> PagedKVSpec:
+        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, x, ctx, cache):
+        H, KV, D = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = ops.linear(x, self.w_in)
+        table = getattr(self.position, "rotary_table", None)
+        if self.position is not None and table is None:
+            # a position encoding without a table: let it rewrite q and k, then store unrotated
+            n = qkv.shape[0]
+            q = qkv[:, : H * D].unflatten(1, (H, D))
+            k = qkv[:, H * D : (H + KV) * D].unflatten(1, (KV, D)) if self.own_kv else qkv.new_empty((n, 0, D))
+            self.position.apply(q, k, ctx.positions)
+        ops.rope_kv_write(
+            qkv, ctx.positions, table, cache.slot_map, cache.pool, H, KV, D, write_kv=self.own_kv
+        )
+        out = ops.paged_attention(
+            qkv,
+            cache.pool,
+            cache.page_table,
+            ctx,
+            num_heads=H,
+            num_kv_heads=KV,
+            head_dim=D,
+            scale=self.scale,
+            window=self.window,
+        )
+        return ops.linear(out, self.w_out)
+
+
+register_part("mixer", "attention", PagedAttention)

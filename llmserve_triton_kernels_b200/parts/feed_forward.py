@@ -1,0 +1,46 @@
+"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))`` without biases.
+
+Parity: src/llmserve/model/llama.py:112-120, where the activation is SiLU
+(``z * sigmoid(z)``); the gate and up matrices are stacked at load so that one matrix product
+feeds the activation kernel.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import FeedForward, TensorSpec, register_part
+
+_ACTIVATIONS = ("silu",)
+
+
+class GatedMLP(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+        if activation not in _ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not built; known: {_ACTIVATIONS}")
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.activation = activation
+        self.w_gate_up: torch.Tensor | None = None  # [2 I, hidden]: gate rows, then up rows
+        self.w_down: torch.Tensor | None = None  # [hidden, I]
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        i, h = self.intermediate_size, self.hidden_size
+        return {
+            "gate_proj.weight": TensorSpec((i, h)),
+            "up_proj.weight": TensorSpec((i, h)),
+            "down_proj.weight": TensorSpec((h, i)),
+        }
+
+    def bind(self, tensors, dtype, device) -> None:
+        fused = torch.cat([tensors["gate_proj.weight"].to(dtype), tensors["up_proj.weight"].to(dtype)], dim=0)
+        self.w_gate_up = fused.to(device).contiguous()
+        self.w_down = tensors["down_proj.weight"].to(device=device, dtype=dtype).contiguous()
+
+    def forward(self, x, ctx):
+        gate_up = ops.linear(x, self.w_gate_up)
+        return ops.linear(ops.swiglu(gate_up), self.w_down)
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)
