@@ -45,3 +45,15 @@ def model_folder(tmp_path_factory):
         return made[key]
 
     return make
+
+
+@pytest.fixture
+def plain_ops_engine(monkeypatch):
+    """Replaces every device operation by its plain torch statement, so that the engine's host
+    logic runs on the CPU.  The engine itself has no CPU path; this is a test device only."""
+    import plain_ops
+    from llmserve_triton_kernels_b200 import ops
+
+    for name in plain_ops.ALL:
+        monkeypatch.setattr(ops, name, getattr(plain_ops, name))
+    return ops

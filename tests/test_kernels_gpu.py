@@ -1,0 +1,259 @@
+"""Each CUDA kernel alone against its plain torch statement, at sizes the tiny models do not
+have: head sizes in steps of 16, group sizes that are no power of two, widths and vocabularies
+that are no power of two, page sizes 4 to 64, windows, and inputs made so that one far key or
+one page's edge decides the result."""
+
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_llama
+import plain_ops
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from llmserve_triton_kernels_b200 import ops as o
+
+    return o
+
+
+def tol(dtype, scale=1.0):
+    return dict(atol=(2e-6 if dtype == torch.float32 else 1.6e-2) * scale, rtol=(1e-5 if dtype == torch.float32 else 1.6e-2))
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,hidden,n", [(300, 72, 5), (1000, 2048, 33), (17, 16, 1)])
+def test_embed(dtype, vocab, hidden, n):
+    table = rnd(vocab, hidden, dtype=dtype)
+    ids = torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(1)).to(torch.int32).to(DEV)
+    got = ops().embed(ids, table)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got, plain_ops.embed(ids, table), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,n", [(72, 7), (2048, 19), (5000, 3), (16, 1)])
+@pytest.mark.parametrize("eps", [1e-5, 1e-2])
+def test_rmsnorm_with_residual_sum(dtype, hidden, n, eps):
+    resid = rnd(n, hidden, seed=2)
+    delta = rnd(n, hidden, dtype=dtype, seed=3)
+    weight = 1 + rnd(hidden, seed=4, std=0.1)
+    want_resid = resid.clone()
+    want = plain_ops.rmsnorm(want_resid, weight, eps, delta=delta, out_dtype=dtype)
+    got = ops().rmsnorm(resid, weight, eps, delta=delta, out_dtype=dtype)
+    torch.testing.assert_close(resid, want_resid, atol=1e-6, rtol=1e-6)  # the sum was written back
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+    # chosen rows only: nothing is written back
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32, device=DEV)
+    before = resid.clone()
+    got_rows = ops().rmsnorm(resid, weight, eps, delta=delta, rows=rows, out_dtype=dtype)
+    torch.testing.assert_close(resid, before, atol=0, rtol=0)
+    want_rows = plain_ops.rmsnorm(before.clone(), weight, eps, delta=delta, rows=rows, out_dtype=dtype)
+    torch.testing.assert_close(got_rows.float(), want_rows.float(), **tol(dtype))
+    # without a delta
+    torch.testing.assert_close(
+        ops().rmsnorm(resid, weight, eps, out_dtype=dtype).float(),
+        plain_ops.rmsnorm(resid.clone(), weight, eps, out_dtype=dtype).float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 40, 24), (7, 172, 64), (65, 129, 173), (130, 64, 2048), (3, 1000, 5)])
+def test_linear_float32_is_true_32_bit_and_row_independent(m, n, k):
+    x, w = rnd(m, k, seed=5), rnd(n, k, seed=6)
+    got = ops().linear(x, w)
+    want = (x.double() @ w.double().t()).float()
+    torch.testing.assert_close(got, want, atol=2e-6 * k**0.5, rtol=1e-5)
+    # a row's result is bit-identical whatever else is in the batch
+    alone = ops().linear(x[m - 1 : m].contiguous(), w)
+    assert torch.equal(alone[0], got[m - 1])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 48, 64), (9, 344, 96), (130, 2560, 2048), (64, 100, 172)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_bfloat16(m, n, k, out_dtype):
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=7), rnd(n, k, dtype=torch.bfloat16, seed=8, std=0.05)
+    got = ops().linear(x, w, out_dtype=out_dtype)
+    assert got.dtype == out_dtype
+    want = x.double() @ w.double().t()
+    torch.testing.assert_close(got.double(), want, atol=2e-2 * 0.05 * k**0.5, rtol=1e-2)
+
+
+def make_cache(requests, KV, D, page_size, dtype, seed=0, shuffle=True):
+    """A pool with the keys and values of ``requests`` (list of context lengths) on shuffled pages."""
+    pages_of = [-(-n // page_size) for n in requests]
+    total = sum(pages_of) + 3
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(seed)) if shuffle else torch.arange(total)
+    pool = torch.zeros(total, 2, KV, page_size, D, dtype=dtype, device=DEV)
+    width = max(pages_of)
+    table = torch.zeros(len(requests), width, dtype=torch.int32)
+    keys, values, at = [], [], 0
+    for r, n in enumerate(requests):
+        k, v = rnd(n, KV, D, seed=seed + 10 + r), rnd(n, KV, D, seed=seed + 50 + r)
+        keys.append(k)
+        values.append(v)
+        table[r, : pages_of[r]] = perm[at : at + pages_of[r]].to(torch.int32)
+        at += pages_of[r]
+    return pool, table.to(DEV), keys, values
+
+
+def fill_pool(pool, table, keys, values, page_size):
+    for r, (k, v) in enumerate(zip(keys, values)):
+        for j in range(k.shape[0]):
+            page, off = int(table[r, j // page_size]), j % page_size
+            pool[page, 0, :, off] = k[j].to(pool.dtype)
+            pool[page, 1, :, off] = v[j].to(pool.dtype)
+
+
+def step_ctx(ctx_lens, q_lens):
+    cu = [0]
+    for q in q_lens:
+        cu.append(cu[-1] + q)
+    token_request = [r for r, q in enumerate(q_lens) for _ in range(q)]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    return SimpleNamespace(cu_tokens=i32(cu), context_lens=i32(ctx_lens), token_request=i32(token_request))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize(
+    "H,KV,D,page_size,window",
+    [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 2, 48, 4, None), (8, 8, 64, 16, 9), (5, 5, 80, 32, None),
+     (12, 4, 128, 64, 33), (2, 1, 256, 16, None), (7, 7, 112, 16, 1)],
+)
+def test_paged_attention_mixed_batch(dtype, H, KV, D, page_size, window):
+    ctx_lens, q_lens = [70, 1, 33, 129, 17], [5, 1, 33, 1, 2]  # a portion, a first token, a whole prompt, decodes
+    pool, table, keys, values = make_cache(ctx_lens, KV, D, page_size, dtype)
+    fill_pool(pool, table, keys, values, page_size)
+    ctx = step_ctx(ctx_lens, q_lens)
+    n = sum(q_lens)
+    q = rnd(n, H * D + 24, dtype=dtype, seed=99)  # rows are wider than the query heads, as in a fused projection
+    kw = dict(num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5, window=window)
+    got = ops().paged_attention(q, pool, table, ctx, **kw)
+    want = plain_ops.paged_attention(q, pool, table, ctx, **kw)
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far_key", [0, 15, 16, 511, 512, 700])
+def test_paged_attention_finds_one_far_key(dtype, far_key):
+    """One key among 701 is made to match the query: the output must be that key's value.  A
+    kernel that loses a key at a page's edge or at a chunk's edge would return an average."""
+    H, KV, D, page_size, n = 4, 2, 64, 16, 701
+    pool, table, keys, values = make_cache([n], KV, D, page_size, dtype, seed=3)
+    q = rnd(1, H * D, dtype=dtype, seed=5, std=0.1)
+    direction = torch.nn.functional.normalize(rnd(D, seed=6), dim=0)
+    q.view(H, D)[:] = (direction * 24).to(dtype)
+    keys[0][:] = keys[0] * 0.05
+    keys[0][far_key] = direction * 24
+    fill_pool(pool, table, keys, values, page_size)
+    ctx = step_ctx([n], [1])
+    got = ops().paged_attention(q, pool, table, ctx, num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5)
+    want = values[0][far_key].to(dtype).float().repeat_interleave(H // KV, dim=0).reshape(1, H * D)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 16, 17, 40])
+def test_paged_attention_window_edge(dtype, window):
+    """The key just outside the window shouts; the key just inside whispers.  The result must
+    not contain the value of the key outside."""
+    H, KV, D, page_size, n = 2, 1, 32, 8, 100
+    pool, table, keys, values = make_cache([n], KV, D, page_size, dtype, seed=4)
+    direction = torch.nn.functional.normalize(rnd(D, seed=6), dim=0)
+    q = (direction * 20).repeat(H).reshape(1, H * D).to(dtype)
+    keys[0][:] = keys[0] * 0.01
+    keys[0][n - 1 - window] = direction * 20  # outside: position p - window
+    values[0][n - 1 - window] = 1000.0
+    fill_pool(pool, table, keys, values, page_size)
+    ctx = step_ctx([n], [1])
+    kw = dict(num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5, window=window)
+    got = ops().paged_attention(q, pool, table, ctx, **kw)
+    want = plain_ops.paged_attention(q, pool, table, ctx, **kw)
+    assert got.float().abs().max() < 100
+    torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,KV,D,page_size", [(4, 2, 16, 16), (3, 1, 32, 8), (5, 5, 80, 4), (32, 4, 64, 16)])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_rope_kv_write(dtype, H, KV, D, page_size, rotate):
+    n, theta, max_pos = 11, 500000.0, 300
+    positions = torch.tensor([0, 1, 2, 7, 8, 9, 255, 299, 31, 32, 33], dtype=torch.int32, device=DEV)
+    cos, sin = plain_llama.rope_cos_sin(torch.arange(max_pos), D, theta)
+    table = torch.cat((cos[:, : D // 2], sin[:, : D // 2]), dim=-1).contiguous().to(DEV) if rotate else None
+    qkv = rnd(n, (H + 2 * KV) * D, dtype=dtype, seed=11)
+    pages = 8
+    slot_map = torch.randperm(pages * page_size, generator=torch.Generator().manual_seed(2))[:n].to(torch.int32).to(DEV)
+    pool_a = torch.zeros(pages, 2, KV, page_size, D, dtype=dtype, device=DEV)
+    pool_b = pool_a.clone()
+    qkv_a, qkv_b = qkv.clone(), qkv.clone()
+    ops().rope_kv_write(qkv_a, positions, table, slot_map, pool_a, H, KV, D)
+    plain_ops.rope_kv_write(qkv_b, positions, table, slot_map, pool_b, H, KV, D)
+    torch.testing.assert_close(qkv_a.float(), qkv_b.float(), **tol(dtype))
+    torch.testing.assert_close(pool_a.float(), pool_b.float(), **tol(dtype))
+    if rotate:  # and against the reference's own formulation with concatenated halves
+        q = qkv[:, : H * D].float().view(n, H, D).transpose(0, 1).cpu()
+        c, s = cos[positions.cpu().long()], sin[positions.cpu().long()]
+        want = plain_llama.apply_rope(q, c, s).transpose(0, 1).reshape(n, H * D)
+        torch.testing.assert_close(qkv_a[:, : H * D].float().cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,inter", [(3, 172), (17, 5632), (1, 16)])
+def test_swiglu(dtype, n, inter):
+    gate_up = rnd(n, 2 * inter, dtype=dtype, seed=12, std=3.0)
+    torch.testing.assert_close(ops().swiglu(gate_up).float(), plain_ops.swiglu(gate_up).float(), **tol(dtype, 3.0))
+
+
+@pytest.mark.parametrize("rows,vocab", [(1, 256), (5, 32000), (3, 50257), (2, 7)])
+def test_argmax_lowest_index_among_equals(rows, vocab):
+    logits = rnd(rows, vocab, seed=13)
+    logits[0, vocab // 2] = 50.0
+    logits[0, vocab - 1] = 50.0
+    got = ops().argmax(logits)
+    assert got.tolist() == torch.argmax(logits.cpu(), dim=-1).tolist()
+    assert got[0].item() == vocab // 2
+
+
+@pytest.mark.parametrize("vocab", [384, 32000, 50257])
+def test_sample_matches_plain_sampler(vocab):
+    rows = 12
+    logits = rnd(rows, vocab, seed=14, std=2.0)
+    temperature = torch.tensor([0.0, 0.8, 0.8, 1.0, 1.5, 0.3, 0.8, 0.8, 1.0, 1.0, 0.7, 2.0], device=DEV)
+    top_k = torch.tensor([0, 0, 50, 1, 0, 0, 5, 0, 200, 0, 40, 0], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.9, 1.0, 1.0, 0.5, 0.95, 1e-6, 0.8, 1.0], device=DEV)
+    seeds = torch.arange(100, 100 + rows, dtype=torch.int64, device=DEV)
+    for counter in (0, 1, 17):
+        counters = torch.full((rows,), counter, dtype=torch.int64, device=DEV)
+        got = ops().sample(logits, temperature, top_k, top_p, seeds, counters).tolist()
+        want = plain_ops.sample(logits, temperature, top_k, top_p, seeds, counters).tolist()
+        assert got == want
+    assert got[0] == int(torch.argmax(logits[0]).item())  # temperature 0
+    assert got[3] == int(torch.argmax(logits[3]).item())  # top_k = 1
+    assert got[9] == int(torch.argmax(logits[9]).item())  # a tiny top_p keeps the top token only
+
+
+def test_sample_follows_the_distribution():
+    vocab, draws = 50, 4000
+    logits = rnd(1, vocab, seed=15).repeat(draws, 1).contiguous()
+    t = torch.full((draws,), 0.9, device=DEV)
+    k = torch.full((draws,), 10, dtype=torch.int32, device=DEV)
+    p = torch.full((draws,), 1.0, device=DEV)
+    seeds = torch.full((draws,), 77, dtype=torch.int64, device=DEV)
+    counters = torch.arange(draws, dtype=torch.int64, device=DEV)
+    got = ops().sample(logits, t, k, p, seeds, counters).cpu().long()
+    probs = plain_llama.filtered_probs(logits[0].cpu(), 0.9, top_k=10)
+    freq = torch.bincount(got, minlength=vocab).double() / draws
+    assert freq[probs == 0].sum() == 0  # nothing outside the top 10
+    assert (freq - probs.double()).abs().max() < 0.03

@@ -1,0 +1,88 @@
+"""Trace replay in every way of cutting the work, against the plain implementation.
+
+The same requests are replayed whole, with the last 32 tokens decoded one by one, in portions
+of changing size, and mixed with other requests over a pool so small that pages are used
+again.  On the GPU ``bin/trace_run`` runs as a user would start it, in 32-bit and in bfloat16;
+without a GPU the same traces go through the replay program in-process with the plain
+operations patched in, which checks the host side (cache, batches, step function).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+import tiny_configs
+import trace_tools
+
+F32_RTOL = 2e-5  # of the largest |logit| of the row's reference; the arithmetic is all 32-bit
+BF16_RTOL = 2e-2  # bfloat16 keeps 8 bits: ~20 roundings of ~2^-9 between the tokens and the logits
+
+
+def tolerance(dtype: str):
+    r = F32_RTOL if dtype == "float32" else BF16_RTOL
+    return lambda ref: r * max(float(np.abs(ref).max()), 1e-3)
+
+
+def requests_for(name: str) -> dict[str, list[int]]:
+    """The configuration's prompts, each followed by 34 given tokens, and one long request."""
+    cfg, _, prompt_seed, lens = tiny_configs.TINY[name]
+    vocab, limit = cfg["vocab_size"], cfg["max_position_embeddings"]
+    seqs = tiny_configs.seeded_tokens(vocab, [n + 34 for n in lens] + [limit - 3], prompt_seed + 100)
+    return {f"r{i}": s for i, s in enumerate(seqs)}
+
+
+def all_modes(name: str) -> tuple[trace_tools.Trace, dict[str, list[int]]]:
+    """One trace holding the four ways, request names tagged by way."""
+    reqs = requests_for(name)
+    trace = trace_tools.Trace()
+    flat: dict[str, list[int]] = {}
+    for req, tokens in reqs.items():
+        for tag, make in (("w", trace_tools.whole), ("d", trace_tools.decode_tail), ("p", trace_tools.portions)):
+            trace.extend(make(f"{tag}.{req}", tokens))
+            flat[f"{tag}.{req}"] = tokens
+    short = {f"m.{r}": t for r, t in list(reqs.items())[:-1]}
+    # twice through, so that the second round runs on pages that the first one gave back
+    both = {**short, **{k + "'": v for k, v in short.items()}}
+    prefill = {k: len(v) - 34 for k, v in both.items()}
+    trace.extend(trace_tools.mixed(both, prefill, chunk=16, live=4))
+    flat.update(both)
+    return trace, flat
+
+
+def expected_logits(model_dir, flat):
+    cfg, w = plain_llama.read_model(model_dir)
+    cache: dict[tuple, torch.Tensor] = {}
+    out = {}
+    for req, tokens in flat.items():
+        key = tuple(tokens)
+        if key not in cache:
+            cache[key] = plain_llama.forward(cfg, w, tokens)
+        out[req] = cache[key]
+    return out
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_replay_host_logic_with_plain_operations(name, model_folder, tmp_path, plain_ops_engine):
+    cfg, seed, _, _ = tiny_configs.TINY[name]
+    folder = model_folder(cfg, seed, torch.float32)
+    trace, flat = all_modes(name)
+    got = trace_tools.run_trace_inprocess(folder, "float32", trace, tmp_path, page_size=8 if name == "b" else 16)
+    assert len(got) == sum(len(v) for v in trace.rows.values())
+    trace_tools.compare(got, expected_logits(folder, flat), tolerance("float32"))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_replay_on_gpu(name, dtype, model_folder, tmp_path):
+    cfg, seed, _, _ = tiny_configs.TINY[name]
+    storage = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = model_folder(cfg, seed, storage)
+    trace, flat = all_modes(name)
+    got = trace_tools.run_trace(folder, dtype, trace, tmp_path, page_size=8 if name == "b" else None)
+    assert len(got) == sum(len(v) for v in trace.rows.values())
+    worst = trace_tools.compare(got, expected_logits(folder, flat), tolerance(dtype))
+    print(f"worst row (fraction of tolerance, (request, position, diff)): {worst}")
