@@ -1,8 +1,8 @@
 // y[M, N] = x[M, K] * w[N, K]^T on the CUDA cores with 32-bit fused multiply-adds.
 //
 // This is the matrix product of the true 32-bit path (no tensor cores, no reduced-precision
-// mode), and it takes every size.  Each output element is accumulated over k = 0..K-1 in that
-// order by one thread, so a row's result does not depend on how many other rows are in the
+// mode), and it takes every size.  Each output element is accumulated by one thread, k-tile
+// by k-tile in ascending k, so a row's result does not depend on how many other rows are in the
 // batch or where the row lies in it.
 #include "common.cuh"
 
@@ -36,6 +36,13 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restr
             ws[lk + e][lrow] = (n < N && k < K) ? to_float(w[(size_t)n * ldw + k]) : 0.f;
         }
         __syncthreads();
+        // a partial sum per k-tile, then one addition into the total: the rounding error grows with
+        // sqrt(K / BK) instead of sqrt(K), and the order is still fixed
+        float part[TM][TN];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j) part[i][j] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             float a[TM], b[TN];
@@ -46,8 +53,12 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restr
 #pragma unroll
             for (int i = 0; i < TM; ++i)
 #pragma unroll
-                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < TN; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j) acc[i][j] += part[i][j];
         __syncthreads();
     }
 #pragma unroll

@@ -59,6 +59,26 @@ def library():
     return _lib
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of the library have been launched by this process (a CUDA graph's replay
+    counts the launches it captured)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _launch(name: str, *args) -> int:
+    global _launches
+    _launches += 1
+    return getattr(library(), name)(*args)
+
+
 def loaded_library_path() -> str | None:
     return None if _lib is None else _lib._name
 
@@ -101,7 +121,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     _need(table.dim() == 2 and table.is_contiguous(), "the token table must be a contiguous matrix")
     n, (vocab, hidden) = ids.numel(), table.shape
     out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
-    _check(library().llm_embed(_ptr(ids), _ptr(table), _code(table.dtype), _ptr(out), n, hidden, vocab, _stream()), "embed")
+    _check(_launch("llm_embed", _ptr(ids), _ptr(table), _code(table.dtype), _ptr(out), n, hidden, vocab, _stream()), "embed")
     return out
 
 
@@ -124,7 +144,7 @@ def rmsnorm(
         _i32(rows, "rows")
     n_out = resid.shape[0] if rows is None else rows.numel()
     out = torch.empty((n_out, resid.shape[1]), dtype=out_dtype, device=resid.device)
-    code = library().llm_rmsnorm(
+    code = _launch("llm_rmsnorm", 
         _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else -1, _ptr(weight), float(eps),
         _ptr(rows), _ptr(out), _code(out_dtype), n_out, resid.shape[1], _stream(),
     )
@@ -143,7 +163,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     n = w.shape[0]
     if x.dtype == torch.float32:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-        code = library().llm_gemm_simt(
+        code = _launch("llm_gemm_simt", 
             _ptr(x), _F32, _ptr(w), _F32, _ptr(out), _code(out_dtype), m, n, k, x.stride(0), k, n, _stream()
         )
         _check(code, "linear (float32)")
@@ -183,7 +203,7 @@ def rope_kv_write(
         _need(pool.dtype == qkv.dtype and pool.is_contiguous() and pool.dim() == 5, "the pool plane must be contiguous [pages, 2, kv_heads, page_size, head_dim] of the qkv type")
         _need(pool.shape[1] == 2 and pool.shape[2] == num_kv_heads and pool.shape[4] == head_dim, "the pool plane does not match the heads")
         page_size = pool.shape[3]
-    code = library().llm_rope_kv_write(
+    code = _launch("llm_rope_kv_write", 
         _ptr(qkv), _code(qkv.dtype), qkv.stride(0), _ptr(positions), _ptr(table), table_rows, _ptr(slot_map),
         _ptr(pool), n, num_heads, num_kv_heads if write_kv else 0, head_dim, page_size, int(write_kv), _stream(),
     )
@@ -225,7 +245,7 @@ def paged_attention(
     _need(head_dim % 16 == 0 and head_dim <= 256, f"head_dim {head_dim} is not supported (multiples of 16 up to 256)")
     _i32(page_table, "page_table")
     out = torch.empty((n, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    code = library().llm_attention_generic(
+    code = _launch("llm_attention_generic", 
         _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _code(qkv.dtype), _ptr(page_table),
         page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), n, num_heads,
         num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), _stream(),
@@ -239,7 +259,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     _need(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0, "gate_up must be a contiguous [N, 2 I] matrix")
     n, inter = gate_up.shape[0], gate_up.shape[1] // 2
     out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
-    _check(library().llm_swiglu(_ptr(gate_up), _ptr(out), _code(gate_up.dtype), n, inter, _stream()), "swiglu")
+    _check(_launch("llm_swiglu", _ptr(gate_up), _ptr(out), _code(gate_up.dtype), n, inter, _stream()), "swiglu")
     return out
 
 
@@ -247,7 +267,7 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     """Index of the largest logit of each row (the lowest index among equals) -> int32 ``[rows]``."""
     _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous float32 matrix")
     out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    _check(library().llm_argmax(_ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax")
+    _check(_launch("llm_argmax", _ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax")
     return out
 
 
@@ -268,7 +288,7 @@ def sample(
     for t, dt, name in ((temperature, torch.float32, "temperature"), (top_k, torch.int32, "top_k"), (top_p, torch.float32, "top_p"), (seeds, torch.int64, "seeds"), (counters, torch.int64, "counters")):
         _need(t.dtype == dt and t.numel() == rows and t.is_contiguous() and t.is_cuda, f"{name} must be {dt} [rows] on the device")
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    code = library().llm_sample(
+    code = _launch("llm_sample", 
         _ptr(logits), rows, logits.shape[1], _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seeds), _ptr(counters),
         _ptr(out), _stream(),
     )

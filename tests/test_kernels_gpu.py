@@ -74,7 +74,8 @@ def test_linear_float32_is_true_32_bit_and_row_independent(m, n, k):
     x, w = rnd(m, k, seed=5), rnd(n, k, seed=6)
     got = ops().linear(x, w)
     want = (x.double() @ w.double().t()).float()
-    torch.testing.assert_close(got, want, atol=2e-6 * k**0.5, rtol=1e-5)
+    # ~8 standard deviations of the rounding of a sum of K/16 partial sums of unit-variance terms
+    torch.testing.assert_close(got, want, atol=4e-6 * k**0.5, rtol=1e-5)
     # a row's result is bit-identical whatever else is in the batch
     alone = ops().linear(x[m - 1 : m].contiguous(), w)
     assert torch.equal(alone[0], got[m - 1])
