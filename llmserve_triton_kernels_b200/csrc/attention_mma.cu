@@ -1,0 +1,451 @@
+// Paged grouped-query attention on the tensor cores (bfloat16, head sizes 16/32/64/128) for
+// prefill portions and decode tokens of one step.
+//
+// Work is cut by (request, key/value head): the query rows of a CTA are (token, member of the
+// head group) pairs, so the G query heads that share a key/value head share every key and value
+// that is loaded.  Two shapes of CTA, both 4 warps:
+//   * ROWS: 64 rows (4 warps x 16); every warp walks the same keys.  Serves requests that bring
+//     more than 16 rows (portions of prompts).
+//   * KEYS: 16 rows; the 4 warps walk different keys of each tile and merge at the end.  Serves
+//     decode tokens and very short portions.
+// A launch of one shape skips the requests that belong to the other.  Keys and values are copied
+// page by page into shared memory with cp.async (two stages), the products are mma.sync
+// m16n8k16 with 32-bit accumulation, the softmax is the running (max, sum) form in 32-bit in the
+// base-2 domain.  Long contexts with few rows are cut over gridDim.x ("splits"); each split
+// writes an unnormalised 32-bit partial and its (max, sum) to scratch memory and a second kernel
+// merges them.  A split's share of the keys is worked out on the device from the request's
+// length, so the grid does not depend on the lengths (a CUDA graph replays it as captured).
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 128;
+constexpr int SMALL_ROWS = 16;  // requests with at most this many rows go to the KEYS shape
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct AttnParams {
+    const __nv_bfloat16* q;
+    int q_stride;
+    __nv_bfloat16* out;
+    int out_stride;
+    const __nv_bfloat16* pool;
+    const int* page_table;
+    int table_width;
+    const int* cu_tokens;
+    const int* ctx_lens;
+    int H, KV, G, page_size, window;
+    int tiles_per_request;  // gridDim.z = requests * tiles_per_request
+    float scale_log2;       // softmax scale * log2(e)
+    int splits;             // gridDim.x
+    float* part_o;          // [tokens, H, splits, D], relative to the split's max
+    float* part_ml;         // [tokens, H, splits, 2]: (max in the base-2 domain, sum)
+};
+
+// D: head size.  ROW_WARPS x KEY_WARPS = 4 warps.  BN: keys per warp and tile.
+template <int D, int ROW_WARPS, int KEY_WARPS, int BN>
+__global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams p) {
+    constexpr int BM = 16 * ROW_WARPS;   // rows of the CTA
+    constexpr int BNC = BN * KEY_WARPS;  // keys of one CTA tile
+    constexpr int CHUNKS = D / 8;        // 16-byte pieces of a key row
+    constexpr int SWZ = CHUNKS >= 8 ? 7 : CHUNKS - 1;
+    constexpr int KSTEPS = D / 16;
+    constexpr int NT_S = BN / 8;  // 8-key tiles of a warp's scores
+    constexpr int NT_O = D / 8;   // 8-wide tiles of the output
+    constexpr bool SMALL = KEY_WARPS > 1;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][BNC][D]
+    __nv_bfloat16* v_s = k_s + 2 * BNC * D;                           // [2][BNC][D]
+
+    const int split = blockIdx.x, kvh = blockIdx.y;
+    const int r = blockIdx.z / p.tiles_per_request, tile = blockIdx.z % p.tiles_per_request;
+    const int q_begin = p.cu_tokens[r], q_len = p.cu_tokens[r + 1] - q_begin;
+    const int G = p.G, rows_total = q_len * G;
+    if ((rows_total <= SMALL_ROWS) != SMALL) return;
+    const int row0 = tile * BM;
+    if (row0 >= rows_total) return;
+    const int ctx = p.ctx_lens[r], pos0 = ctx - q_len;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row_warp = warp % ROW_WARPS, key_warp = warp / ROW_WARPS;
+    const int qr = lane >> 2, qc = lane & 3;
+
+    // the two rows this thread holds pieces of
+    int row_tok[2], row_pos[2], row_lo[2], row_head[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int rho = row0 + row_warp * 16 + qr + 8 * i;
+        row_ok[i] = rho < rows_total;
+        const int tok = row_ok[i] ? rho / G : 0;
+        row_tok[i] = q_begin + tok;
+        row_head[i] = kvh * G + (row_ok[i] ? rho - tok * G : 0);
+        row_pos[i] = row_ok[i] ? pos0 + tok : -1;
+        row_lo[i] = p.window > 0 ? max(0, row_pos[i] - p.window + 1) : 0;
+    }
+    // keys this CTA needs: from the window's start of its first token to its last token's position
+    const int tok_first = row0 / G, tok_last = (min(rows_total, row0 + BM) - 1) / G;
+    const int key_hi = pos0 + tok_last;
+    const int key_lo = p.window > 0 ? max(0, pos0 + tok_first - p.window + 1) : 0;
+    const int tile_first = key_lo / BNC, tile_last = key_hi / BNC;
+    const int per_split = (tile_last - tile_first + 1 + p.splits - 1) / p.splits;
+    const int t_begin = tile_first + split * per_split;
+    const int t_end = min(tile_last + 1, t_begin + per_split);
+
+    // query fragments, straight from global memory
+    unsigned qa[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int which = i & 1;
+            const __nv_bfloat16* src = p.q + (size_t)row_tok[which] * p.q_stride + (size_t)row_head[which] * D +
+                                       ks * 16 + (i >> 1) * 8 + qc * 2;
+            qa[ks][i] = row_ok[which] ? *reinterpret_cast<const unsigned*>(src) : 0u;
+        }
+
+    const int* table = p.page_table + (size_t)r * p.table_width;
+    const size_t head_stride = (size_t)p.page_size * D;
+
+    auto load_tile = [&](int t, int stage) {
+        const int base = t * BNC;
+        for (int idx = tid; idx < BNC * CHUNKS; idx += THREADS) {
+            const int kk = idx / CHUNKS, c = idx - kk * CHUNKS;
+            const int j = base + kk;
+            const bool valid = j >= key_lo && j <= key_hi;
+            size_t off = 0;
+            if (valid) {
+                const int page = table[j / p.page_size], in_page = j % p.page_size;
+                off = ((size_t)(page * 2) * p.KV + kvh) * head_stride + (size_t)in_page * D + c * 8;
+            }
+            const int dst = (stage * BNC + kk) * D + ((c ^ (kk & SWZ)) * 8);
+            cp_async16(k_s + dst, p.pool + off, valid);
+            cp_async16(v_s + dst, p.pool + off + (size_t)p.KV * head_stride, valid);
+        }
+    };
+
+    float oacc[NT_O][4];
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    if (t_begin < t_end) {
+        load_tile(t_begin, 0);
+        cp_async_commit();
+    }
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) & 1;
+        if (t + 1 < t_end) {
+            load_tile(t + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const __nv_bfloat16* ks_tile = k_s + (stage * BNC + key_warp * BN) * D;
+        const __nv_bfloat16* vs_tile = v_s + (stage * BNC + key_warp * BN) * D;
+        const int key_base = t * BNC + key_warp * BN;
+
+        // scores: S = Q K^T
+        float sacc[NT_S][4];
+#pragma unroll
+        for (int i = 0; i < NT_S; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[i][e] = 0.f;
+        const int mi = lane >> 3, ri = lane & 7;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < NT_S / 2; ++np) {
+                const int key = np * 16 + (mi >> 1) * 8 + ri;  // row of the tile; key_warp*BN is a multiple of 8
+                const int chunk = ks * 2 + (mi & 1);
+                unsigned b[4];
+                ldmatrix_x4(b, ks_tile + key * D + ((chunk ^ (key & SWZ)) * 8));
+                mma_bf16(sacc[2 * np], qa[ks], b[0], b[1]);
+                mma_bf16(sacc[2 * np + 1], qa[ks], b[2], b[3]);
+            }
+        }
+        // mask, running max and sum
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int j = key_base + nt * 8 + qc * 2 + (e & 1);
+                const bool visible = j <= row_pos[i] && j >= row_lo[i];
+                sacc[nt][e] = visible ? sacc[nt][e] * p.scale_log2 : -INFINITY;
+                mx[i] = fmaxf(mx[i], sacc[nt][e]);
+            }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            m_use[i] = m_new == -INFINITY ? 0.f : m_new;
+            alpha[i] = exp2f(m_run[i] - m_use[i]);
+            m_run[i] = m_new;
+            l_run[i] *= alpha[i];
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = exp2f(sacc[nt][e] - m_use[e >> 1]);
+                sacc[nt][e] = pv;
+                l_run[e >> 1] += pv;
+            }
+#pragma unroll
+        for (int nt = 0; nt < NT_O; ++nt) {
+            oacc[nt][0] *= alpha[0];
+            oacc[nt][1] *= alpha[0];
+            oacc[nt][2] *= alpha[1];
+            oacc[nt][3] *= alpha[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+            unsigned pa[4];
+            pa[0] = pack_bf16(sacc[2 * kk][0], sacc[2 * kk][1]);
+            pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
+            pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+            pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < NT_O / 2; ++dp) {
+                const int key = kk * 16 + (mi & 1) * 8 + ri;
+                const int chunk = dp * 2 + (mi >> 1);
+                unsigned b[4];
+                ldmatrix_x4_trans(b, vs_tile + key * D + ((chunk ^ (key & SWZ)) * 8));
+                mma_bf16(oacc[2 * dp], pa, b[0], b[1]);
+                mma_bf16(oacc[2 * dp + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncthreads();  // the stage may be refilled
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+
+    if constexpr (!SMALL) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!row_ok[i]) continue;
+            if (p.splits == 1) {
+                const float inv = 1.f / l_run[i];
+                __nv_bfloat16* dst = p.out + (size_t)row_tok[i] * p.out_stride + (size_t)row_head[i] * D + qc * 2;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt)
+                    *reinterpret_cast<unsigned*>(dst + nt * 8) = pack_bf16(oacc[nt][2 * i] * inv, oacc[nt][2 * i + 1] * inv);
+            } else {
+                const size_t slot = ((size_t)row_tok[i] * p.H + row_head[i]) * p.splits + split;
+                float* dst = p.part_o + slot * D + qc * 2;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    dst[nt * 8] = oacc[nt][2 * i];
+                    dst[nt * 8 + 1] = oacc[nt][2 * i + 1];
+                }
+                if (qc == 0) {
+                    p.part_ml[slot * 2] = m_run[i];
+                    p.part_ml[slot * 2 + 1] = l_run[i];
+                }
+            }
+        }
+    } else {
+        // merge the four warps' shares of the keys through shared memory (the key tiles are done with)
+        float* o_sm = reinterpret_cast<float*>(smem_raw);    // [KEY_WARPS][16][D]
+        float* ml_sm = o_sm + KEY_WARPS * 16 * D;            // [KEY_WARPS][16][2]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = qr + 8 * i;
+            float* dst = o_sm + (key_warp * 16 + row) * D + qc * 2;
+#pragma unroll
+            for (int nt = 0; nt < NT_O; ++nt) {
+                dst[nt * 8] = oacc[nt][2 * i];
+                dst[nt * 8 + 1] = oacc[nt][2 * i + 1];
+            }
+            if (qc == 0) {
+                ml_sm[(key_warp * 16 + row) * 2] = m_run[i];
+                ml_sm[(key_warp * 16 + row) * 2 + 1] = l_run[i];
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < 16 * D; idx += THREADS) {
+            const int row = idx / D, d = idx - row * D;
+            if (row >= rows_total) continue;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < KEY_WARPS; ++w) m = fmaxf(m, ml_sm[(w * 16 + row) * 2]);
+            const float m_use = m == -INFINITY ? 0.f : m;
+            float o = 0.f, l = 0.f;
+#pragma unroll
+            for (int w = 0; w < KEY_WARPS; ++w) {
+                const float f = exp2f(ml_sm[(w * 16 + row) * 2] - m_use);
+                o += o_sm[(w * 16 + row) * D + d] * f;
+                l += ml_sm[(w * 16 + row) * 2 + 1] * f;
+            }
+            const int tok = row / G, head = kvh * G + (row - tok * G);
+            if (p.splits == 1) {
+                p.out[(size_t)(q_begin + tok) * p.out_stride + (size_t)head * D + d] = __float2bfloat16_rn(o / l);
+            } else {
+                const size_t slot = ((size_t)(q_begin + tok) * p.H + head) * p.splits + split;
+                p.part_o[slot * D + d] = o;
+                if (d == 0) {
+                    p.part_ml[slot * 2] = m;
+                    p.part_ml[slot * 2 + 1] = l;
+                }
+            }
+        }
+    }
+}
+
+// Merges the splits of every (token, head) whose request went through a launch with splits > 1.
+template <int D>
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
+                                       __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ token_request,
+                                       const int* __restrict__ cu_tokens, int n_tokens, int H, int G, int merge_small,
+                                       int merge_large) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_tokens * H) return;
+    const int tok = warp / H, head = warp - tok * H;
+    const int r = token_request[tok];
+    const bool small = (cu_tokens[r + 1] - cu_tokens[r]) * G <= SMALL_ROWS;
+    if (small ? !merge_small : !merge_large) return;
+    const size_t slot = ((size_t)tok * H + head) * splits;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(slot + s) * 2]);
+    const float m_use = m == -INFINITY ? 0.f : m;
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) l += part_ml[(slot + s) * 2 + 1] * exp2f(part_ml[(slot + s) * 2] - m_use);
+    const float inv = 1.f / l;
+    for (int d = lane; d < D; d += 32) {
+        float o = 0.f;
+        for (int s = 0; s < splits; ++s) o += part_o[(slot + s) * D + d] * exp2f(part_ml[(slot + s) * 2] - m_use);
+        out[(size_t)tok * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(o * inv);
+    }
+}
+
+template <int D, int ROW_WARPS, int KEY_WARPS, int BN>
+int launch_shape(const AttnParams& p, int requests, cudaStream_t stream) {
+    constexpr int BNC = BN * KEY_WARPS;
+    size_t smem = (size_t)2 * 2 * BNC * D * sizeof(__nv_bfloat16);
+    const size_t merge = (size_t)KEY_WARPS * 16 * (D + 2) * sizeof(float);
+    if (KEY_WARPS > 1 && merge > smem) smem = merge;
+    auto kernel = attention_mma_kernel<D, ROW_WARPS, KEY_WARPS, BN>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const long long z = (long long)requests * p.tiles_per_request;
+    if (z > 65535 || p.KV > 65535) return LLM_ERR_UNSUPPORTED;
+    dim3 grid(p.splits, p.KV, (unsigned)z);
+    kernel<<<grid, THREADS, smem, stream>>>(p);
+    return launch_status();
+}
+
+template <int D>
+int launch_all(AttnParams p, int requests, int n_tokens, const int* token_request, int max_rows_large, int splits_small,
+               int splits_large, int have_small, cudaStream_t stream) {
+    int code = 0;
+    if (max_rows_large > 0) {
+        p.splits = splits_large;
+        p.tiles_per_request = (max_rows_large + 63) / 64;
+        code = launch_shape<D, 4, 1, 64>(p, requests, stream);
+        if (code) return code;
+    }
+    if (have_small) {
+        p.splits = splits_small;
+        p.tiles_per_request = 1;
+        code = launch_shape<D, 1, 4, 32>(p, requests, stream);
+        if (code) return code;
+    }
+    const int merge_small = have_small && splits_small > 1, merge_large = max_rows_large > 0 && splits_large > 1;
+    if (merge_small || merge_large) {
+        if (merge_small && merge_large && splits_small != splits_large) return LLM_ERR_BAD_ARGUMENT;
+        const int splits = merge_small ? splits_small : splits_large;
+        const long long warps = (long long)n_tokens * p.H;
+        const int threads = 128;
+        const long long blocks = (warps * 32 + threads - 1) / threads;
+        attention_merge_kernel<D><<<(unsigned)blocks, threads, 0, stream>>>(p.part_o, p.part_ml, splits, p.out, p.out_stride,
+                                                                            token_request, p.cu_tokens, n_tokens, p.H, p.G,
+                                                                            merge_small, merge_large);
+        code = launch_status();
+    }
+    return code;
+}
+
+}  // namespace
+
+// One step's attention in bfloat16.  max_rows_large: the most rows (tokens x group) of any request
+// with more than 16 rows, 0 if there is none; have_small: some request has at most 16 rows.
+// scratch_o / scratch_ml: float32 [tokens, H, splits, D] and [tokens, H, splits, 2], needed when a
+// split count exceeds 1.  Returns LLM_ERR_UNSUPPORTED for head sizes other than 16/32/64/128.
+LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* pool,
+                                 const int* page_table, int table_width, const int* token_request, const int* cu_tokens,
+                                 const int* ctx_lens, int requests, int n_tokens, int H, int KV, int D, int page_size,
+                                 int window, float scale, int max_rows_large, int have_small, int splits_small,
+                                 int splits_large, float* scratch_o, float* scratch_ml, cudaStream_t stream) {
+    if (n_tokens <= 0 || requests <= 0) return 0;
+    if (H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0 || splits_small < 1 || splits_large < 1)
+        return LLM_ERR_BAD_ARGUMENT;
+    if ((q_stride & 1) || (out_stride & 1)) return LLM_ERR_BAD_ARGUMENT;
+    if ((splits_small > 1 || splits_large > 1) && (!scratch_o || !scratch_ml)) return LLM_ERR_BAD_ARGUMENT;
+    AttnParams p;
+    p.q = (const __nv_bfloat16*)q;
+    p.q_stride = q_stride;
+    p.out = (__nv_bfloat16*)out;
+    p.out_stride = out_stride;
+    p.pool = (const __nv_bfloat16*)pool;
+    p.page_table = page_table;
+    p.table_width = table_width;
+    p.cu_tokens = cu_tokens;
+    p.ctx_lens = ctx_lens;
+    p.H = H;
+    p.KV = KV;
+    p.G = H / KV;
+    p.page_size = page_size;
+    p.window = window;
+    p.tiles_per_request = 1;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.splits = 1;
+    p.part_o = scratch_o;
+    p.part_ml = scratch_ml;
+    switch (D) {
+        case 16: return launch_all<16>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
+        case 32: return launch_all<32>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
+        case 64: return launch_all<64>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
+        case 128: return launch_all<128>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
+        default: return LLM_ERR_UNSUPPORTED;
+    }
+}

@@ -1,0 +1,106 @@
+"""Decode steps as CUDA graphs.
+
+A step in which every request brings exactly one token and wants its logits has the same
+shapes every time, so the whole pass — some hundred and fifty launches for 22 layers — is
+captured once per batch size and replayed.  Only the step's integer arrays change: they are
+written into a pinned buffer of fixed layout and copied to the device with one copy before the
+replay.  The reference notes launch and host overhead as its next bottleneck and CUDA graphs as
+the cure (docs/PROFILING.md:19-20, docs/DESIGN.md:79-80) but does not build them.
+
+Page tables have the model's full width in a graph (``ceil(max_positions / page_size)``), and
+``StepContext.max_context_len`` is the model's limit, so no launch depends on how long the
+requests are at the time.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from .batch import StepContext
+
+
+def _pad4(n: int) -> int:
+    return -(-n // 4) * 4
+
+
+class DecodeGraph:
+    def __init__(self, model, cache, num_requests: int):
+        self.model, self.cache, self.R = model, cache, int(num_requests)
+        R = self.R
+        self.widths = [-(-model.plan.max_positions // g.page_size) for g in cache.groups]
+        sizes = [R, R, R, R + 1, R, R, R]  # ids, positions, token_request, cu, ctx_lens, logit_rows, state_slots
+        for w in self.widths:
+            sizes += [R * w, R]
+        self.offsets = np.concatenate(([0], np.cumsum([_pad4(s) for s in sizes]))).tolist()
+        self.sizes = sizes
+        total = self.offsets[-1]
+        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=cache.device)
+        self._piece_np(2)[:] = np.arange(R)
+        self._piece_np(3)[:] = np.arange(R + 1)
+        self._piece_np(5)[:] = np.arange(R)
+        self.copied = torch.cuda.Event()
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.launches = 0
+        d = self._piece
+        self.ctx = StepContext(
+            num_tokens=R, num_requests=R, num_logits=R,
+            token_ids=d(0), positions=d(1), token_request=d(2), cu_tokens=d(3), context_lens=d(4), logit_rows=d(5),
+            state_slots=d(6), host_cu_tokens=list(range(R + 1)), host_context_lens=None, host_state_slots=None,
+            max_query_len=1, max_context_len=model.plan.max_positions,
+        )
+        group_tensors = []
+        for g, w in enumerate(self.widths):
+            group_tensors.append((d(7 + 2 * g).view(R, w), d(8 + 2 * g)))
+        self.views = cache.views(group_tensors, self.ctx.state_slots, None)
+        self.h2d_bytes = total * 4
+
+    def _piece(self, i: int) -> torch.Tensor:
+        return self.dev[self.offsets[i] : self.offsets[i] + self.sizes[i]]
+
+    def _piece_np(self, i: int) -> np.ndarray:
+        return self.host_np[self.offsets[i] : self.offsets[i] + self.sizes[i]]
+
+    def fill(self, tokens: list[int], lengths: list[int], state_slots: np.ndarray, group_arrays) -> None:
+        """Write the step's arrays into the pinned buffer and start their copy to the device."""
+        self.copied.synchronize()  # the previous copy has left the pinned buffer
+        R = self.R
+        self._piece_np(0)[:] = tokens
+        self._piece_np(1)[:] = lengths
+        self._piece_np(4)[:] = np.asarray(lengths, dtype=np.int32) + 1
+        self._piece_np(6)[:] = state_slots
+        for g, (table, slot_map) in enumerate(group_arrays):
+            dst = self._piece_np(7 + 2 * g).reshape(R, self.widths[g])
+            dst[:, : table.shape[1]] = table
+            self._piece_np(8 + 2 * g)[:] = slot_map
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+
+    def run(self) -> torch.Tensor:
+        """Logits ``[R, vocab]`` of the step whose arrays were filled last.  The tensor is
+        the graph's own: the next replay overwrites it."""
+        if self.graph is None:
+            self._capture()
+        self.graph.replay()
+        ops.add_launches(self.launches)
+        return self.logits
+
+    def _capture(self) -> None:
+        current = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(current)
+        with torch.cuda.stream(side):  # once outside a capture: lazy set-up of libraries and kernels
+            self.model.forward(self.ctx, self.views)
+        current.wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(graph):
+            self.logits = self.model.forward(self.ctx, self.views)
+        self.launches = ops.launch_count() - before
+        ops.add_launches(-self.launches)  # a capture launches nothing
+        self.graph = graph

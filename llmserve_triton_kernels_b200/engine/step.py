@@ -15,18 +15,26 @@ import torch
 from ..cache import CacheManager
 from ..models.model import Model
 from .batch import StepContext, StepEntry, pack_step
+from .graph import DecodeGraph
 
 
 class StepFunction:
-    def __init__(self, model: Model, cache: CacheManager):
+    def __init__(self, model: Model, cache: CacheManager, use_graphs: bool | None = None):
+        """``use_graphs``: replay decode-only steps as CUDA graphs (default: on a CUDA device,
+        when every part of the model says it can be captured)."""
         self.model = model
         self.cache = cache
         self.h2d_bytes = 0  # bytes of the last step's descriptor copy
         self.last_context: StepContext | None = None
+        if use_graphs is None:
+            use_graphs = cache.device.type == "cuda" and model.graph_safe
+        self.use_graphs = bool(use_graphs)
+        self.graphs: dict[int, DecodeGraph] = {}
 
     def __call__(self, entries: list[StepEntry]) -> torch.Tensor:
         """Returns 32-bit logits ``[wanted places, vocab]`` on the device, in the order of the
-        entries and of each entry's ``want``."""
+        entries and of each entry's ``want``.  The tensor may be a buffer that the next call
+        overwrites: read or copy it before stepping again."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         cache, limit = self.cache, self.model.plan.max_positions
@@ -48,6 +56,15 @@ class StepFunction:
         cache.reserve(pairs)
         group_arrays, state_slots = cache.step_tables(pairs)
         lengths = [cache.lengths[req] for req, _ in pairs]
+        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            graph = self.graphs.get(len(entries))
+            if graph is None:
+                graph = self.graphs[len(entries)] = DecodeGraph(self.model, cache, len(entries))
+            graph.fill([e.tokens[0] for e in entries], lengths, state_slots, group_arrays)
+            logits = graph.run()
+            cache.commit(pairs)
+            self.h2d_bytes, self.last_context = graph.h2d_bytes, graph.ctx
+            return logits
         ctx, group_tensors, self.h2d_bytes = pack_step(entries, lengths, state_slots, group_arrays, cache.device)
         views = cache.views(group_tensors, ctx.state_slots, ctx.host_state_slots)
         logits = self.model.forward(ctx, views)

@@ -89,6 +89,13 @@ class Model:
         seen[self.head.data_ptr()] = self.head.numel() * self.head.element_size()
         return sum(seen.values())
 
+    @property
+    def graph_safe(self) -> bool:
+        """Every part launches the same kernels whatever the step's contents, so a decode step can be captured."""
+        return all(
+            getattr(b, "graph_safe", False) for b in self.blocks
+        ) and getattr(self.final_norm, "graph_safe", False)
+
     # ------------------------------------------------------------------ caches
     def cache_specs(self) -> list[PagedKVSpec | StateSpec | None]:
         """For each entry of the order: what its mixer keeps, or None if it keeps nothing of its

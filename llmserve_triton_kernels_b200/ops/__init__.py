@@ -27,6 +27,7 @@ _SIGNATURES = {
     "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_attention_generic": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+    "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp],
     "llm_argmax": [_vp, _i, _i, _vp, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -60,6 +61,11 @@ def library():
 
 
 _launches = 0
+_MMA_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention; others take the general kernel
+_SMALL_ROWS = 16  # requests with at most this many (token, group member) rows take the split-key shape
+_SMALL_TILE_KEYS = 128  # keys one CTA of that shape covers per tile
+_SM_COUNT = 148
+_FORCE_GENERIC_ATTENTION = False  # tests switch the tensor-core attention off to reach the general kernel in bfloat16
 
 
 def launch_count() -> int:
@@ -245,10 +251,36 @@ def paged_attention(
     _need(head_dim % 16 == 0 and head_dim <= 256, f"head_dim {head_dim} is not supported (multiples of 16 up to 256)")
     _i32(page_table, "page_table")
     out = torch.empty((n, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    code = _launch("llm_attention_generic", 
-        _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _code(qkv.dtype), _ptr(page_table),
-        page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), n, num_heads,
-        num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), _stream(),
+    if qkv.dtype == torch.bfloat16 and head_dim in _MMA_HEAD_DIMS and not _FORCE_GENERIC_ATTENTION:
+        group = num_heads // num_kv_heads
+        cu = getattr(ctx, "host_cu_tokens", None)
+        if cu is None:
+            cu = ctx.cu_tokens.tolist()
+        rows = [(b - a) * group for a, b in zip(cu, cu[1:])]
+        small = sum(1 for x in rows if x <= _SMALL_ROWS)
+        max_rows_large = max((x for x in rows if x > _SMALL_ROWS), default=0)
+        splits = 1
+        if small:
+            longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
+            useful = -(-longest // _SMALL_TILE_KEYS)
+            splits = max(1, min(useful, -(-2 * _SM_COUNT // (small * num_kv_heads)), 32))
+        scratch_o = scratch_ml = None
+        if splits > 1:
+            scratch_o = torch.empty((n * num_heads * splits * head_dim,), dtype=torch.float32, device=qkv.device)
+            scratch_ml = torch.empty((n * num_heads * splits * 2,), dtype=torch.float32, device=qkv.device)
+        code = _launch(
+            "llm_attention_mma", _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _ptr(page_table),
+            page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), len(rows), n,
+            num_heads, num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), max_rows_large,
+            int(small > 0), splits, 1, _ptr(scratch_o), _ptr(scratch_ml), _stream(),
+        )
+        add_launches((max_rows_large > 0) + (small > 0) + (splits > 1) - 1)
+        _check(code, "paged_attention (tensor cores)")
+        return out
+    code = _launch(
+        "llm_attention_generic", _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _code(qkv.dtype),
+        _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), n,
+        num_heads, num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), _stream(),
     )
     _check(code, "paged_attention")
     return out

@@ -18,6 +18,8 @@ from .base import Mixer, PagedKVSpec, PartSpec, TensorSpec, build_part, register
 
 
 class PagedAttention(Mixer):
+    graph_safe = True
+
     def __init__(
         self,
         hidden_size: int,

@@ -66,6 +66,10 @@ class StateSpec:
 
 class Part:
     category = "part"
+    # True if forward() launches the same device work for the same shapes whatever the step's
+    # contents (no reads of device data on the host, no host loops over lengths): then a decode
+    # step through this part can be captured in a CUDA graph.
+    graph_safe = False
 
     def tensors(self) -> dict[str, TensorSpec]:
         return {}

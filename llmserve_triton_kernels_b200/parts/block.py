@@ -18,6 +18,10 @@ class PreNormBlock(Block):
         self.ff_norm = ff_norm
         self.feed_forward = feed_forward
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward))
+
     def forward(self, resid, pending, ctx, cache):
         x = self.mixer_norm.add_forward(resid, pending)
         pending = self.mixer.forward(x, ctx, cache)

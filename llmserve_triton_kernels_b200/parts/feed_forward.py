@@ -16,6 +16,8 @@ _ACTIVATIONS = ("silu",)
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         if activation not in _ACTIVATIONS:
             raise ValueError(f"activation {activation!r} is not built; known: {_ACTIVATIONS}")

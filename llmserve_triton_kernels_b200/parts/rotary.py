@@ -16,6 +16,8 @@ from .base import PositionEncoding, register_part
 
 
 class RotaryEmbedding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim: int, theta: float, max_positions: int):
         if head_dim % 2:
             raise ValueError(f"rotary positions need an even head_dim, got {head_dim}")

@@ -145,6 +145,34 @@ def test_paged_attention_mixed_batch(dtype, H, KV, D, page_size, window):
     torch.testing.assert_close(got.float(), want.float(), **tol(dtype))
 
 
+@pytest.mark.parametrize(
+    "H,KV,D,page_size,window",
+    [(32, 4, 64, 16, None), (8, 2, 128, 16, None), (6, 2, 32, 8, 50), (4, 4, 16, 4, None), (16, 2, 64, 64, 130),
+     (3, 1, 128, 32, 700)],
+)
+@pytest.mark.parametrize("general_kernel", [False, True])
+def test_paged_attention_long_portions_bfloat16(H, KV, D, page_size, window, general_kernel, monkeypatch):
+    """Portions of hundreds of tokens beside decode tokens at contexts beyond a thousand: the
+    tensor-core kernel's 64-row tiles, its split keys and their merge; and the general kernel
+    on the same inputs."""
+    monkeypatch.setattr(ops(), "_FORCE_GENERIC_ATTENTION", general_kernel)
+    ctx_lens, q_lens = [500, 333, 64, 1200, 130], [300, 333, 3, 1, 2]
+    pool, table, keys, values = make_cache(ctx_lens, KV, D, page_size, torch.bfloat16, seed=21)
+    pool_filled = torch.zeros_like(pool)
+    for r, (k, v) in enumerate(zip(keys, values)):  # vectorised fill
+        n = k.shape[0]
+        j = torch.arange(n, device=DEV)
+        page = table[r].long()[j // page_size]
+        pool_filled[page, 0, :, j % page_size] = k.to(torch.bfloat16)
+        pool_filled[page, 1, :, j % page_size] = v.to(torch.bfloat16)
+    ctx = step_ctx(ctx_lens, q_lens)
+    q = rnd(sum(q_lens), (H + 2 * KV) * D, dtype=torch.bfloat16, seed=98)
+    kw = dict(num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5, window=window)
+    got = ops().paged_attention(q, pool_filled, table, ctx, **kw)
+    want = plain_ops.paged_attention(q, pool_filled, table, ctx, **kw)
+    torch.testing.assert_close(got.float(), want.float(), **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("far_key", [0, 15, 16, 511, 512, 700])
 def test_paged_attention_finds_one_far_key(dtype, far_key):
