@@ -12,8 +12,8 @@
 // page by page into shared memory with cp.async (two stages), the products are mma.sync
 // m16n8k16 with 32-bit accumulation, the softmax is the running (max, sum) form in 32-bit in the
 // base-2 domain.  Long contexts with few rows are cut over gridDim.x ("splits"); each split
-// writes an unnormalised 32-bit partial and its (max, sum) to scratch memory and a second kernel
-// merges them.  A split's share of the keys is worked out on the device from the request's
+// writes an unnormalised 32-bit partial and its (max, sum) to scratch memory, and the split that
+// finishes last (a counter per request and key/value head tells) merges them.  A split's share of the keys is worked out on the device from the request's
 // length, so the grid does not depend on the lengths (a CUDA graph replays it as captured).
 #include "common.cuh"
 
@@ -67,6 +67,7 @@ struct AttnParams {
     int splits;             // gridDim.x
     float* part_o;          // [tokens, H, splits, D], relative to the split's max
     float* part_ml;         // [tokens, H, splits, 2]: (max in the base-2 domain, sum)
+    int* counters;          // [requests * KV] zeros: how many splits of a (request, kv head) have finished
 };
 
 // D: head size.  ROW_WARPS x KEY_WARPS = 4 warps.  BN: keys per warp and tile.
@@ -114,9 +115,14 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
     const int key_hi = pos0 + tok_last;
     const int key_lo = p.window > 0 ? max(0, pos0 + tok_first - p.window + 1) : 0;
     const int tile_first = key_lo / BNC, tile_last = key_hi / BNC;
-    const int per_split = (tile_last - tile_first + 1 + p.splits - 1) / p.splits;
+    // a split takes at least two tiles when keys are split inside the CTA too, so short contexts use few
+    // splits however many the grid has; splits beyond the last active one have nothing to do
+    const int n_tiles = tile_last - tile_first + 1;
+    const int per_split = max(SMALL ? 2 : 1, (n_tiles + p.splits - 1) / p.splits);
+    const int active_splits = (n_tiles + per_split - 1) / per_split;
     const int t_begin = tile_first + split * per_split;
     const int t_end = min(tile_last + 1, t_begin + per_split);
+    if (SMALL && split >= active_splits) return;
 
     // query fragments, straight from global memory
     unsigned qa[KSTEPS][4];
@@ -133,20 +139,26 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
     const int* table = p.page_table + (size_t)r * p.table_width;
     const size_t head_stride = (size_t)p.page_size * D;
 
+    // one key row (or a fixed part of it) per thread: one page lookup and a few 16-byte copies per tile
+    constexpr int TPK = THREADS / BNC;        // threads per key
+    constexpr int CPT = CHUNKS / TPK;         // 16-byte pieces per thread
+    static_assert(THREADS % BNC == 0 && CHUNKS % TPK == 0, "a key row must split evenly over its threads");
+    const int load_key = tid / TPK, load_c0 = (tid % TPK) * CPT;
     auto load_tile = [&](int t, int stage) {
-        const int base = t * BNC;
-        for (int idx = tid; idx < BNC * CHUNKS; idx += THREADS) {
-            const int kk = idx / CHUNKS, c = idx - kk * CHUNKS;
-            const int j = base + kk;
-            const bool valid = j >= key_lo && j <= key_hi;
-            size_t off = 0;
-            if (valid) {
-                const int page = table[j / p.page_size], in_page = j % p.page_size;
-                off = ((size_t)(page * 2) * p.KV + kvh) * head_stride + (size_t)in_page * D + c * 8;
-            }
-            const int dst = (stage * BNC + kk) * D + ((c ^ (kk & SWZ)) * 8);
-            cp_async16(k_s + dst, p.pool + off, valid);
-            cp_async16(v_s + dst, p.pool + off + (size_t)p.KV * head_stride, valid);
+        const int j = t * BNC + load_key;
+        const bool valid = j >= key_lo && j <= key_hi;
+        size_t off = 0;
+        if (valid) {
+            const int lp = j / p.page_size;
+            off = ((size_t)(table[lp] * 2) * p.KV + kvh) * head_stride + (size_t)(j - lp * p.page_size) * D;
+        }
+        const int dst_row = (stage * BNC + load_key) * D;
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int c = load_c0 + i;
+            const int dst = dst_row + ((c ^ (load_key & SWZ)) * 8);
+            cp_async16(k_s + dst, p.pool + off + c * 8, valid);
+            cp_async16(v_s + dst, p.pool + off + (size_t)p.KV * head_stride + c * 8, valid);
         }
     };
 
@@ -316,7 +328,7 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
                 l += ml_sm[(w * 16 + row) * 2 + 1] * f;
             }
             const int tok = row / G, head = kvh * G + (row - tok * G);
-            if (p.splits == 1) {
+            if (active_splits == 1) {
                 p.out[(size_t)(q_begin + tok) * p.out_stride + (size_t)head * D + d] = __float2bfloat16_rn(o / l);
             } else {
                 const size_t slot = ((size_t)(q_begin + tok) * p.H + head) * p.splits + split;
@@ -326,6 +338,44 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
                     p.part_ml[slot * 2 + 1] = l;
                 }
             }
+        }
+        if (active_splits > 1) {
+            // the split that finishes last merges all of them: no second launch
+            __shared__ int ticket;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) ticket = atomicAdd(&p.counters[r * p.KV + kvh], 1);
+            __syncthreads();
+            if (ticket != active_splits - 1) return;
+            __threadfence();
+            // factors of every (row, split) first, side by side, then the weighted sums
+            float* f_sm = reinterpret_cast<float*>(smem_raw);  // [rows][splits] factor, then [rows] 1 / sum
+            float* inv_sm = f_sm + SMALL_ROWS * 32;
+            for (int row = tid; row < rows_total; row += THREADS) {
+                const int tok = row / G, head = kvh * G + (row - tok * G);
+                const size_t slot = ((size_t)(q_begin + tok) * p.H + head) * p.splits;
+                float m = -INFINITY;
+                for (int s2 = 0; s2 < active_splits; ++s2) m = fmaxf(m, __ldcg(&p.part_ml[(slot + s2) * 2]));
+                const float m_use = m == -INFINITY ? 0.f : m;
+                float l = 0.f;
+                for (int s2 = 0; s2 < active_splits; ++s2) {
+                    const float f = exp2f(__ldcg(&p.part_ml[(slot + s2) * 2]) - m_use);
+                    f_sm[row * 32 + s2] = f;
+                    l += __ldcg(&p.part_ml[(slot + s2) * 2 + 1]) * f;
+                }
+                inv_sm[row] = 1.f / l;
+            }
+            __syncthreads();
+            for (int idx = tid; idx < rows_total * D; idx += THREADS) {
+                const int row = idx / D, d = idx - row * D;
+                const int tok = row / G, head = kvh * G + (row - tok * G);
+                const size_t slot = ((size_t)(q_begin + tok) * p.H + head) * p.splits;
+                float o = 0.f;
+#pragma unroll 4
+                for (int s2 = 0; s2 < active_splits; ++s2) o += __ldcg(&p.part_o[(slot + s2) * D + d]) * f_sm[row * 32 + s2];
+                p.out[(size_t)(q_begin + tok) * p.out_stride + (size_t)head * D + d] = __float2bfloat16_rn(o * inv_sm[row]);
+            }
+            if (tid == 0) p.counters[r * p.KV + kvh] = 0;  // ready for the next launch
         }
     }
 }
@@ -390,7 +440,7 @@ int launch_all(AttnParams p, int requests, int n_tokens, const int* token_reques
         code = launch_shape<D, 1, 4, 32>(p, requests, stream);
         if (code) return code;
     }
-    const int merge_small = have_small && splits_small > 1, merge_large = max_rows_large > 0 && splits_large > 1;
+    const int merge_small = 0, merge_large = max_rows_large > 0 && splits_large > 1;  // the small shape merges in place
     if (merge_small || merge_large) {
         if (merge_small && merge_large && splits_small != splits_large) return LLM_ERR_BAD_ARGUMENT;
         const int splits = merge_small ? splits_small : splits_large;
@@ -410,17 +460,21 @@ int launch_all(AttnParams p, int requests, int n_tokens, const int* token_reques
 // One step's attention in bfloat16.  max_rows_large: the most rows (tokens x group) of any request
 // with more than 16 rows, 0 if there is none; have_small: some request has at most 16 rows.
 // scratch_o / scratch_ml: float32 [tokens, H, splits, D] and [tokens, H, splits, 2], needed when a
-// split count exceeds 1.  Returns LLM_ERR_UNSUPPORTED for head sizes other than 16/32/64/128.
+// split count exceeds 1; counters: int32 [requests * KV], all zero before the launch and again
+// after it, needed when splits_small exceeds 1.  Returns LLM_ERR_UNSUPPORTED for head sizes other than 16/32/64/128.
 LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* pool,
                                  const int* page_table, int table_width, const int* token_request, const int* cu_tokens,
                                  const int* ctx_lens, int requests, int n_tokens, int H, int KV, int D, int page_size,
                                  int window, float scale, int max_rows_large, int have_small, int splits_small,
-                                 int splits_large, float* scratch_o, float* scratch_ml, cudaStream_t stream) {
+                                 int splits_large, float* scratch_o, float* scratch_ml, int* counters,
+                                 cudaStream_t stream) {
     if (n_tokens <= 0 || requests <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0 || splits_small < 1 || splits_large < 1)
         return LLM_ERR_BAD_ARGUMENT;
     if ((q_stride & 1) || (out_stride & 1)) return LLM_ERR_BAD_ARGUMENT;
     if ((splits_small > 1 || splits_large > 1) && (!scratch_o || !scratch_ml)) return LLM_ERR_BAD_ARGUMENT;
+    if (splits_small > 1 && !counters) return LLM_ERR_BAD_ARGUMENT;
+    if (splits_small > 32) return LLM_ERR_BAD_ARGUMENT;
     AttnParams p;
     p.q = (const __nv_bfloat16*)q;
     p.q_stride = q_stride;
@@ -441,6 +495,7 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, void* out, int out
     p.splits = 1;
     p.part_o = scratch_o;
     p.part_ml = scratch_ml;
+    p.counters = counters;
     switch (D) {
         case 16: return launch_all<16>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
         case 32: return launch_all<32>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);

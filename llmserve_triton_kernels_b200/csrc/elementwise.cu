@@ -16,7 +16,15 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     if (id < 0 || id >= vocab) id = 0;  // launch-side checks reject such ids; never read out of range
     const T* src = table + (size_t)id * hidden;
     float* dst = out + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+    if ((hidden & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float v[4];
+            load4(src + i, v);
+            store4(dst + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]);
+    }
 }
 
 LLM_EXPORT int llm_embed(const int* ids, const void* table, int table_dtype, float* out, int n, int hidden,
@@ -47,20 +55,49 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
     float* x = resid + (size_t)r * hidden;
     const TD* d = delta ? delta + (size_t)r * hidden : nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = x[i];
-        if (d) v += to_float(d[i]);
-        row[i] = v;
-        ss += v * v;
+    const bool vec = (hidden & 3) == 0;
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float v[4];
+            load4(x + i, v);
+            if (d) {
+                float dv[4];
+                load4(d + i, dv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] += dv[e];
+            }
+            store4(row + i, v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = x[i];
+            if (d) v += to_float(d[i]);
+            row[i] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, scratch);
     const float scale = rsqrtf(ss / (float)hidden + eps);
     TO* y = out + (size_t)o * hidden;
     const bool write_back = d && !rows;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float v = row[i];
-        if (write_back) x[i] = v;
-        y[i] = from_float<TO>(v * scale * weight[i]);
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float v[4], wv[4];
+            load4(row + i, v);
+            load4(weight + i, wv);
+            if (write_back) store4(x + i, v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = v[e] * scale * wv[e];
+            store4(y + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = row[i];
+            if (write_back) x[i] = v;
+            y[i] = from_float<TO>(v * scale * weight[i]);
+        }
     }
 }
 
@@ -121,6 +158,38 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     }
     const size_t head_stride = (size_t)page_size * D;
 
+    if ((D & 7) == 0 && (row_stride & 3) == 0) {
+        // four pairs (j, j + D/2) at a time
+        const int quads = half >> 2;
+        for (int i = threadIdx.x; i < (H + (write_kv ? KV : 0)) * quads; i += blockDim.x) {
+            const int h = i / quads, j = (i - h * quads) * 4;
+            T* x = row + h * D;
+            float a[4], b[4], c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f}, lo[4], hi[4];
+            load4(x + j, a);
+            load4(x + j + half, b);
+            if (cs) {
+                load4(cs + j, c);
+                load4(cs + half + j, sn);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                lo[e] = a[e] * c[e] - b[e] * sn[e];
+                hi[e] = b[e] * c[e] + a[e] * sn[e];
+            }
+            T* dst = h < H ? x : pool + k_base + (h - H) * head_stride;
+            store4(dst + j, lo);
+            store4(dst + j + half, hi);
+        }
+        if (write_kv) {
+            for (int i = threadIdx.x; i < KV * (D >> 2); i += blockDim.x) {
+                const int h = i / (D >> 2), j = (i - h * (D >> 2)) * 4;
+                float v[4];
+                load4(row + (H + KV + h) * D + j, v);
+                store4(pool + v_base + h * head_stride + j, v);
+            }
+        }
+        return;
+    }
     // query heads, rotated in place
     for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
         const int h = i / half, j = i - h * half;
@@ -173,6 +242,19 @@ LLM_EXPORT int llm_rope_kv_write(void* qkv, int dtype, int row_stride, const int
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    if ((inter & 3) == 0) {
+        for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += stride * 4) {
+            const size_t t = i / inter;
+            const int j = (int)(i - t * inter);
+            float g[4], u[4];
+            load4(gate_up + t * 2 * inter + j, g);
+            load4(gate_up + t * 2 * inter + inter + j, u);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) g[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+            store4(out + i, g);
+        }
+        return;
+    }
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const size_t t = i / inter;
         const int j = (int)(i - t * inter);
@@ -186,7 +268,8 @@ LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int 
     if (n <= 0) return 0;
     const size_t total = (size_t)n * inter;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const size_t want = (total / 4 + threads - 1) / threads + 1;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (dtype == LLM_F32)
         swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
     else if (dtype == LLM_BF16)

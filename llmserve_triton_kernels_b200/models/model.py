@@ -111,8 +111,11 @@ class Model:
         of entry i's cache.  Returns 32-bit logits ``[len(ctx.logit_rows), vocab]``."""
         resid = ops.embed(ctx.token_ids, self.embedding)
         pending = None
-        for i, run in enumerate(self.plan.schedule):
-            pending = self.blocks[run.layer].forward(resid, pending, ctx, caches[i])
+        order = self.plan.schedule
+        for i, run in enumerate(order):
+            # the norm that meets the stream next, so that a block's last product may prepare for it
+            next_norm = self.blocks[order[i + 1].layer].mixer_norm if i + 1 < len(order) else None
+            pending = self.blocks[run.layer].forward(resid, pending, ctx, caches[i], next_norm=next_norm)
         if ctx.num_logits == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
         x = self.final_norm.add_forward(resid, pending, rows=ctx.logit_rows)

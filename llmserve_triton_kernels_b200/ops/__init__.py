@@ -26,8 +26,9 @@ _SIGNATURES = {
     "llm_rope_kv_write": [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_attention_generic": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
-    "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp],
+    "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "llm_argmax": [_vp, _i, _i, _vp, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -65,6 +66,7 @@ _MMA_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention; o
 _SMALL_ROWS = 16  # requests with at most this many (token, group member) rows take the split-key shape
 _SMALL_TILE_KEYS = 128  # keys one CTA of that shape covers per tile
 _SM_COUNT = 148
+_DECODE_LINEAR_MAX_ROWS = 16  # up to this many rows a bfloat16 matrix product streams the weights once (own kernel)
 _FORCE_GENERIC_ATTENTION = False  # tests switch the tensor-core attention off to reach the general kernel in bfloat16
 
 
@@ -158,9 +160,103 @@ def rmsnorm(
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+_error_flag: torch.Tensor | None = None
+
+
+def _error_flag_ptr() -> int:
+    """Address of a pinned host word that kernels set when one of their bounded waits gives up."""
+    global _error_flag
+    if _error_flag is None:
+        _error_flag = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _error_flag.data_ptr()
+
+
+def check_device_errors() -> None:
+    """Raise if a kernel reported that a bounded wait gave up (call after a synchronisation)."""
+    if _error_flag is not None and int(_error_flag[0]) != 0:
+        _error_flag[0] = 0
+        raise KernelError("a kernel's wait for an asynchronous copy gave up; its results are not valid")
+
+
+class NormedInput:
+    """A normalised activation in factored form, as the fused decode kernels hand it on:
+    ``xw [M, hidden]`` holds ``v * norm_weight`` (``v`` the residual stream after the last sum) and
+    ``ss [parts, M]`` partial sums of ``v^2`` per row, so that
+    ``normalised = xw * rsqrt(ss.sum(0) / hidden + eps)``.  ``ops.linear`` and ``ops.linear_swiglu``
+    take it in place of a tensor and apply the row scale to their result; anything else calls
+    :meth:`materialize`."""
+
+    def __init__(self, xw: torch.Tensor, ss: torch.Tensor, eps: float, norm=None):
+        self.xw, self.ss, self.eps, self.norm = xw, ss, float(eps), norm
+        self.shape, self.dtype, self.device = xw.shape, xw.dtype, xw.device
+
+    def materialize(self) -> torch.Tensor:
+        scale = torch.rsqrt(self.ss.sum(0) / self.xw.shape[1] + self.eps)
+        return (self.xw.float() * scale[:, None]).to(self.xw.dtype)
+
+
+class ResidualSink:
+    """Where a part's last matrix product may put its result: added to the 32-bit residual
+    stream ``resid`` in place, which is then handed on normalised for ``norm`` (an RMS norm's
+    ``weight`` and ``eps``) as a :class:`NormedInput`.  Built by a block when the step is small
+    enough for the fused decode kernels."""
+
+    def __init__(self, resid: torch.Tensor, weight: torch.Tensor, eps: float, norm=None):
+        self.resid, self.weight, self.eps, self.norm = resid, weight, float(eps), norm
+
+    @staticmethod
+    def usable(num_tokens: int, dtype: torch.dtype) -> bool:
+        return dtype == torch.bfloat16 and num_tokens <= _DECODE_LINEAR_MAX_ROWS
+
+    def linear(self, x: torch.Tensor, w: torch.Tensor) -> "NormedInput | None":
+        """``resid += x @ w^T``; returns the stream normalised for ``norm``, or None if the
+        fused kernel refuses the shape (then nothing was changed)."""
+        m, k = x.shape
+        n = w.shape[0]
+        if not (x.dtype == torch.bfloat16 and m <= _DECODE_LINEAR_MAX_ROWS and x.stride(1) == 1 and w.is_contiguous()):
+            return None
+        parts = -(-n // 16)
+        xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+        ss = torch.empty((parts, m), dtype=torch.float32, device=x.device)
+        code = _launch(
+            "llm_linear_decode", _ptr(x), _ptr(w), None, _BF16, m, n, k, x.stride(0), n, None, 0, 0.0, 2, 0,
+            _ptr(self.resid), _ptr(self.weight), _ptr(xw), _ptr(ss), _error_flag_ptr(), _stream(),
+        )
+        if code == 10002:
+            add_launches(-1)
+            return None
+        _check(code, "linear into the residual stream")
+        return NormedInput(xw, ss, self.eps, self.norm)
+
+
+def _decode_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):
+    """The weight-streaming product for few rows; None if it refuses the shape."""
+    scaled = isinstance(x, NormedInput)
+    xt = x.xw if scaled else x
+    m, k = xt.shape
+    if not (xt.dtype == torch.bfloat16 and m <= _DECODE_LINEAR_MAX_ROWS and xt.stride(1) == 1 and w.is_contiguous()):
+        return None
+    out = torch.empty((m, n_out), dtype=out_dtype, device=xt.device)
+    code = _launch(
+        "llm_linear_decode", _ptr(xt), _ptr(w), _ptr(out), _code(out_dtype), m, n_out, k, xt.stride(0), n_out,
+        _ptr(x.ss) if scaled else None, x.ss.shape[0] if scaled else 0, x.eps if scaled else 0.0, mode, up_offset,
+        None, None, None, None, _error_flag_ptr(), _stream(),
+    )
+    if code == 10002:  # a shape the kernel refuses
+        add_launches(-1)
+        return None
+    _check(code, "linear (decode)")
+    return out
+
+
+def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x [M, K] @ w [N, K]^T -> [M, N]``.  float32 operands run on the CUDA cores in true 32-bit
-    (fixed summation order); bfloat16 operands accumulate in 32-bit on the tensor cores."""
+    (fixed summation order); bfloat16 operands accumulate in 32-bit on the tensor cores: few rows
+    through the weight-streaming kernel, many through the vendor's library.  ``x`` may be a
+    :class:`NormedInput`."""
+    if isinstance(x, NormedInput):
+        out = _decode_linear(x, w, out_dtype or x.dtype, 0, w.shape[0])
+        return out if out is not None else linear(x.materialize(), w, out_dtype)
     _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not match")
     _need(x.dtype == w.dtype, f"linear: operand types differ ({x.dtype}, {w.dtype})")
     _need(x.stride(1) == 1 and w.is_contiguous(), "linear: operands must have unit inner stride")
@@ -169,16 +265,30 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     n = w.shape[0]
     if x.dtype == torch.float32:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-        code = _launch("llm_gemm_simt", 
-            _ptr(x), _F32, _ptr(w), _F32, _ptr(out), _code(out_dtype), m, n, k, x.stride(0), k, n, _stream()
-        )
+        code = _launch("llm_gemm_simt", _ptr(x), _F32, _ptr(w), _F32, _ptr(out), _code(out_dtype), m, n, k, x.stride(0), k, n, _stream())
         _check(code, "linear (float32)")
         return out
     _need(x.dtype == torch.bfloat16, f"linear: element type {x.dtype} is not supported")
+    if m <= _DECODE_LINEAR_MAX_ROWS:
+        out = _decode_linear(x, w, out_dtype, 0, n)
+        if out is not None:
+            return out
     library()  # the engine never runs without its kernels, even where a matrix product is the vendor's
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())
     return torch.matmul(x, w.t()).to(out_dtype)
+
+
+def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(x @ gate^T) * (x @ up^T)`` for ``w_gate_up = [gate rows | up rows]``: one kernel for
+    few bfloat16 rows, else a product followed by the activation kernel."""
+    inter = w_gate_up.shape[0] // 2
+    xt = x.xw if isinstance(x, NormedInput) else x
+    if xt.dtype == torch.bfloat16 and xt.shape[0] <= _DECODE_LINEAR_MAX_ROWS:
+        out = _decode_linear(x, w_gate_up, torch.bfloat16, 1, inter, up_offset=inter)
+        if out is not None:
+            return out
+    return swiglu(linear(x, w_gate_up))
 
 
 def rope_kv_write(
@@ -264,17 +374,18 @@ def paged_attention(
             longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
             useful = -(-longest // _SMALL_TILE_KEYS)
             splits = max(1, min(useful, -(-2 * _SM_COUNT // (small * num_kv_heads)), 32))
-        scratch_o = scratch_ml = None
+        scratch_o = scratch_ml = counters = None
         if splits > 1:
+            counters = _split_counters(qkv.device, len(rows) * num_kv_heads)
             scratch_o = torch.empty((n * num_heads * splits * head_dim,), dtype=torch.float32, device=qkv.device)
             scratch_ml = torch.empty((n * num_heads * splits * 2,), dtype=torch.float32, device=qkv.device)
         code = _launch(
             "llm_attention_mma", _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _ptr(page_table),
             page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), len(rows), n,
             num_heads, num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), max_rows_large,
-            int(small > 0), splits, 1, _ptr(scratch_o), _ptr(scratch_ml), _stream(),
+            int(small > 0), splits, 1, _ptr(scratch_o), _ptr(scratch_ml), _ptr(counters), _stream(),
         )
-        add_launches((max_rows_large > 0) + (small > 0) + (splits > 1) - 1)
+        add_launches((max_rows_large > 0) + (small > 0) - 1)
         _check(code, "paged_attention (tensor cores)")
         return out
     code = _launch(
@@ -284,6 +395,19 @@ def paged_attention(
     )
     _check(code, "paged_attention")
     return out
+
+
+_counters: dict = {}
+
+
+def _split_counters(device, n: int) -> torch.Tensor:
+    """Zeroed int32 counters that the split-key attention uses and leaves zeroed; one buffer per
+    device, made on first use (outside any graph capture: the first step of a shape runs eagerly)."""
+    buf = _counters.get(device)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros(max(n, 16384), dtype=torch.int32, device=device)
+        _counters[device] = buf
+    return buf
 
 
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:

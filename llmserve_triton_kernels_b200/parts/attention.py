@@ -67,7 +67,9 @@ class PagedAttention(Mixer):
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, x, ctx, cache):
+    accepts_sink = True
+
+    def forward(self, x, ctx, cache, sink=None):
         H, KV, D = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = ops.linear(x, self.w_in)
         table = getattr(self.position, "rotary_table", None)
@@ -91,6 +93,10 @@ class PagedAttention(Mixer):
             scale=self.scale,
             window=self.window,
         )
+        if sink is not None:
+            handed_on = sink.linear(out, self.w_out)
+            if handed_on is not None:
+                return handed_on
         return ops.linear(out, self.w_out)
 
 

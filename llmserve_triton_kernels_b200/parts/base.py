@@ -131,9 +131,12 @@ class Block(Part):
 
     category = "block"
 
-    def forward(self, resid: torch.Tensor, pending: torch.Tensor | None, ctx, cache) -> torch.Tensor:
+    def forward(self, resid: torch.Tensor, pending, ctx, cache, next_norm=None):
         """``resid [N, hidden]`` is the 32-bit residual stream, updated in place; ``pending`` a
-        contribution not yet added to it.  Returns the new pending contribution."""
+        contribution not yet added to it.  Returns the new pending contribution.  ``next_norm`` is
+        the norm that the stream meets after this block (None after the last); a block may use it
+        to fuse that norm into its last product, and must expose its own first norm as
+        ``mixer_norm`` and its mixer as ``mixer``."""
         raise NotImplementedError
 
 

@@ -3,11 +3,14 @@
 Parity: src/llmserve/model/llama.py:131-135 — ``x += mixer(norm(x)); x += ff(norm(x))``.
 The residual stream is a 32-bit tensor that the norms update in place: each part returns its
 contribution, and the next norm adds it before normalising (one pass over the row instead of
-three).
+three).  For small steps the last product of a part adds into the stream itself and hands it on
+already normalised for the next norm (see ``ops.ResidualSink``), so a decode step has no norm
+launches of its own.
 """
 
 from __future__ import annotations
 
+from .. import ops
 from .base import Block, FeedForward, Mixer, Norm, register_part
 
 
@@ -22,11 +25,35 @@ class PreNormBlock(Block):
     def graph_safe(self) -> bool:
         return all(p.graph_safe for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward))
 
-    def forward(self, resid, pending, ctx, cache):
-        x = self.mixer_norm.add_forward(resid, pending)
-        pending = self.mixer.forward(x, ctx, cache)
-        x = self.ff_norm.add_forward(resid, pending)
-        return self.feed_forward.forward(x, ctx)
+    def forward(self, resid, pending, ctx, cache, next_norm=None):
+        x = self._normed(self.mixer_norm, resid, pending)
+        sink = self._sink(self.mixer, self.ff_norm, resid, ctx)
+        pending = self.mixer.forward(x, ctx, cache, sink=sink) if sink else self.mixer.forward(x, ctx, cache)
+        x = self._normed(self.ff_norm, resid, pending)
+        sink = self._sink(self.feed_forward, next_norm, resid, ctx)
+        return self.feed_forward.forward(x, ctx, sink=sink) if sink else self.feed_forward.forward(x, ctx)
+
+    @staticmethod
+    def _normed(norm, resid, pending):
+        """``pending`` is a contribution still to be added, or the stream already summed and
+        normalised for ``norm`` by the part before (a fused decode kernel did both)."""
+        if isinstance(pending, ops.NormedInput):
+            if pending.norm is not norm:
+                raise RuntimeError("a part handed the residual stream on normalised for another norm")
+            return pending
+        return norm.add_forward(resid, pending)
+
+    @staticmethod
+    def _sink(part, norm, resid, ctx):
+        """A sink for the part's last product, if the step is small, the part takes one and the
+        norm after it is an RMS norm that can be folded into the product's ends."""
+        fused = getattr(norm, "fused_params", None)
+        if norm is None or fused is None or not getattr(part, "accepts_sink", False):
+            return None
+        if not ops.ResidualSink.usable(ctx.num_tokens, norm.out_dtype):
+            return None
+        weight, eps = fused()
+        return ops.ResidualSink(resid, weight, eps, norm)
 
 
 register_part("block", "pre_norm", PreNormBlock)

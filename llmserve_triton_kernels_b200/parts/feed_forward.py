@@ -40,9 +40,15 @@ class GatedMLP(FeedForward):
         self.w_gate_up = fused.to(device).contiguous()
         self.w_down = tensors["down_proj.weight"].to(device=device, dtype=dtype).contiguous()
 
-    def forward(self, x, ctx):
-        gate_up = ops.linear(x, self.w_gate_up)
-        return ops.linear(ops.swiglu(gate_up), self.w_down)
+    accepts_sink = True
+
+    def forward(self, x, ctx, sink=None):
+        act = ops.linear_swiglu(x, self.w_gate_up)
+        if sink is not None:
+            handed_on = sink.linear(act, self.w_down)
+            if handed_on is not None:
+                return handed_on
+        return ops.linear(act, self.w_down)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -29,6 +29,10 @@ class RMSNorm(Norm):
         self.weight = tensors["weight"].to(device=device, dtype=torch.float32).contiguous()
         self.out_dtype = dtype
 
+    def fused_params(self):
+        """``(weight, eps)``: what a product needs to fold this norm into its ends."""
+        return self.weight, self.eps
+
     def forward(self, x, rows=None):
         return ops.rmsnorm(x, self.weight, self.eps, delta=None, rows=rows, out_dtype=self.out_dtype)
 

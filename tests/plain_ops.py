@@ -99,6 +99,10 @@ def swiglu(gate_up):
     return (g * torch.sigmoid(g) * u).to(gate_up.dtype)
 
 
+def linear_swiglu(x, w_gate_up):
+    return swiglu(linear(x, w_gate_up))
+
+
 def argmax(logits):
     return torch.argmax(logits, dim=-1).to(torch.int32)
 
@@ -121,6 +125,7 @@ ALL = (
     "rope_inplace",
     "paged_attention",
     "swiglu",
+    "linear_swiglu",
     "argmax",
     "sample",
 )

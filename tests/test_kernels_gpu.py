@@ -81,7 +81,11 @@ def test_linear_float32_is_true_32_bit_and_row_independent(m, n, k):
     assert torch.equal(alone[0], got[m - 1])
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 48, 64), (9, 344, 96), (130, 2560, 2048), (64, 100, 172)])
+@pytest.mark.parametrize(
+    "m,n,k",
+    [(1, 48, 64), (9, 344, 96), (130, 2560, 2048), (64, 100, 172), (8, 2560, 2048), (64, 11264, 2048), (33, 2048, 5632),
+     (5, 40, 72), (17, 100, 48), (3, 64, 88), (16, 17, 8), (1, 32000, 2048)],
+)
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_linear_bfloat16(m, n, k, out_dtype):
     x, w = rnd(m, k, dtype=torch.bfloat16, seed=7), rnd(n, k, dtype=torch.bfloat16, seed=8, std=0.05)
@@ -89,6 +93,47 @@ def test_linear_bfloat16(m, n, k, out_dtype):
     assert got.dtype == out_dtype
     want = x.double() @ w.double().t()
     torch.testing.assert_close(got.double(), want, atol=2e-2 * 0.05 * k**0.5, rtol=1e-2)
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 5632, 2048), (8, 172 * 8, 64), (16, 100, 96), (5, 16, 8)])
+def test_linear_swiglu_fused_for_few_rows(m, inter, k):
+    x = rnd(m, k, dtype=torch.bfloat16, seed=31)
+    w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=32, std=0.05)
+    got = ops().linear_swiglu(x, w)
+    gate_up = x.double() @ w.double().t()
+    want = torch.nn.functional.silu(gate_up[:, :inter]) * gate_up[:, inter:]
+    torch.testing.assert_close(got.double(), want, atol=2e-2 * 0.05 * k**0.5, rtol=2e-2)
+
+
+@pytest.mark.parametrize("m,hidden,k,n_next", [(1, 2048, 5632, 2560), (8, 2048, 2048, 11264), (16, 96, 256, 40), (3, 72, 24, 172)])
+def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
+    """A product that adds into the residual stream and hands it on in factored normalised form,
+    and the next product that consumes that form: together they must equal
+    ``resid += x w^T``, the RMS norm of it, and the next product, done plainly."""
+    o = ops()
+    x = rnd(m, k, dtype=torch.bfloat16, seed=41)
+    w = rnd(hidden, k, dtype=torch.bfloat16, seed=42, std=0.05)
+    resid = rnd(m, hidden, seed=43)
+    norm_w = 1 + rnd(hidden, seed=44, std=0.1)
+    w_next = rnd(n_next, hidden, dtype=torch.bfloat16, seed=45, std=0.05)
+    eps = 1e-5
+    want_resid = resid.double() + x.double() @ w.double().t()
+    want_norm = want_resid * torch.rsqrt(want_resid.pow(2).mean(-1, keepdim=True) + eps) * norm_w.double()
+    want_next = want_norm @ w_next.double().t()
+
+    handed = o.ResidualSink(resid, norm_w, eps).linear(x, w)
+    assert handed is not None
+    torch.testing.assert_close(resid.double(), want_resid, atol=2e-2 * 0.05 * k**0.5, rtol=1e-2)
+    torch.testing.assert_close(handed.materialize().double(), want_norm, atol=3e-2, rtol=2e-2)
+    got_next = o.linear(handed, w_next, out_dtype=torch.float32)
+    torch.testing.assert_close(got_next.double(), want_next, atol=3e-2 * 0.05 * hidden**0.5, rtol=2e-2)
+    if n_next % 2 == 0:
+        got_act = o.linear_swiglu(handed, w_next)
+        half = n_next // 2
+        want_act = torch.nn.functional.silu(want_next[:, :half]) * want_next[:, half:]
+        # d(silu(g) u) <= |u| dg + |silu(g)| du, with dg and du bounded as for got_next above
+        bound = 3e-2 * 0.05 * hidden**0.5 * (1 + float(want_next.abs().max()))
+        torch.testing.assert_close(got_act.double(), want_act, atol=bound, rtol=3e-2)
 
 
 def make_cache(requests, KV, D, page_size, dtype, seed=0, shuffle=True):
