@@ -124,6 +124,11 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
     const int t_end = min(tile_last + 1, t_begin + per_split);
     if (SMALL && split >= active_splits) return;
 
+    // up to here only the step's descriptor arrays were read, which no kernel writes; the queries and the
+    // cache come from the kernels before this one
+    pdl_trigger();
+    pdl_wait();
+
     // query fragments, straight from global memory
     unsigned qa[KSTEPS][4];
 #pragma unroll
@@ -420,8 +425,7 @@ int launch_shape(const AttnParams& p, int requests, cudaStream_t stream) {
     const long long z = (long long)requests * p.tiles_per_request;
     if (z > 65535 || p.KV > 65535) return LLM_ERR_UNSUPPORTED;
     dim3 grid(p.splits, p.KV, (unsigned)z);
-    kernel<<<grid, THREADS, smem, stream>>>(p);
-    return launch_status();
+    return launch_pdl(kernel, grid, dim3(THREADS), smem, stream, p);
 }
 
 template <int D>

@@ -80,3 +80,26 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch: a kernel launched through launch_pdl may start while the kernel
+// before it on the stream is still running.  It may set itself up (indices, barriers, loads of
+// weights and of the step's descriptor arrays, which no kernel writes) but must call pdl_wait()
+// before it reads or writes anything another kernel of the step touches; pdl_wait() returns once the
+// kernel before has completed and its writes are visible.  pdl_trigger() lets the next kernel start.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

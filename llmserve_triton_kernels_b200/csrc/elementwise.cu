@@ -11,6 +11,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                              int hidden, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) id = 0;  // launch-side checks reject such ids; never read out of range
@@ -32,12 +34,10 @@ LLM_EXPORT int llm_embed(const int* ids, const void* table, int table_dtype, flo
     if (n <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == LLM_F32)
-        embed_kernel<float><<<n, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab);
-    else if (table_dtype == LLM_BF16)
-        embed_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab);
-    else
-        return LLM_ERR_BAD_ARGUMENT;
-    return launch_status();
+        return launch_pdl(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, ids, (const float*)table, out, hidden, vocab);
+    if (table_dtype == LLM_BF16)
+        return launch_pdl(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, out, hidden, vocab);
+    return LLM_ERR_BAD_ARGUMENT;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -50,6 +50,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
                                float eps, const int* __restrict__ rows, TO* __restrict__ out, int hidden) {
     extern __shared__ float row[];  // hidden floats, then 33 for the reduction
     float* scratch = row + hidden;
+    pdl_trigger();
+    pdl_wait();
     const int o = blockIdx.x;
     const int r = rows ? rows[o] : o;
     float* x = resid + (size_t)r * hidden;
@@ -112,8 +114,7 @@ static int rmsnorm_launch(float* resid, const void* delta, const float* weight, 
         if (e != cudaSuccess) return (int)e;
     }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    kernel<<<n_out, threads, smem, stream>>>(resid, (const TD*)delta, weight, eps, rows, (TO*)out, hidden);
-    return launch_status();
+    return launch_pdl(kernel, dim3(n_out), dim3(threads), smem, stream, resid, (const TD*)delta, weight, eps, rows, (TO*)out, hidden);
 }
 
 LLM_EXPORT int llm_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* weight, float eps,
@@ -141,6 +142,8 @@ template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
                                      const float* __restrict__ table, int table_rows, const int* __restrict__ slot_map,
                                      T* __restrict__ pool, int H, int KV, int D, int page_size, int write_kv) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     T* row = qkv + (size_t)t * row_stride;
     const int half = D >> 1;
@@ -225,15 +228,12 @@ LLM_EXPORT int llm_rope_kv_write(void* qkv, int dtype, int row_stride, const int
     const int work = H * (D / 2);
     const int threads = work >= 512 ? 256 : 128;
     if (dtype == LLM_F32)
-        rope_kv_write_kernel<float><<<n, threads, 0, stream>>>((float*)qkv, row_stride, positions, table, table_rows,
-                                                               slot_map, (float*)pool, H, KV, D, page_size, write_kv);
-    else if (dtype == LLM_BF16)
-        rope_kv_write_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>((__nv_bfloat16*)qkv, row_stride, positions, table,
-                                                                       table_rows, slot_map, (__nv_bfloat16*)pool, H, KV,
-                                                                       D, page_size, write_kv);
-    else
-        return LLM_ERR_BAD_ARGUMENT;
-    return launch_status();
+        return launch_pdl(rope_kv_write_kernel<float>, dim3(n), dim3(threads), 0, stream, (float*)qkv, row_stride, positions,
+                          table, table_rows, slot_map, (float*)pool, H, KV, D, page_size, write_kv);
+    if (dtype == LLM_BF16)
+        return launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, (__nv_bfloat16*)qkv, row_stride,
+                          positions, table, table_rows, slot_map, (__nv_bfloat16*)pool, H, KV, D, page_size, write_kv);
+    return LLM_ERR_BAD_ARGUMENT;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -241,6 +241,8 @@ LLM_EXPORT int llm_rope_kv_write(void* qkv, int dtype, int row_stride, const int
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+    pdl_trigger();
+    pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     if ((inter & 3) == 0) {
         for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total; i += stride * 4) {
@@ -271,11 +273,9 @@ LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int 
     const size_t want = (total / 4 + threads - 1) / threads + 1;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (dtype == LLM_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
-    else if (dtype == LLM_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
-                                                                     inter, total);
-    else
-        return LLM_ERR_BAD_ARGUMENT;
-    return launch_status();
+        return launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total);
+    if (dtype == LLM_BF16)
+        return launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up,
+                          (__nv_bfloat16*)out, inter, total);
+    return LLM_ERR_BAD_ARGUMENT;
 }

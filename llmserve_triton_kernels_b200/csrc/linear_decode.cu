@@ -56,6 +56,8 @@ struct LinearParams {
     float* ss_out;          // MODE_RESIDUAL: [tiles of 16 features, M]
     int* error_flag;        // set to 1 if a wait for a copy gave up (host-visible memory), or null
     int group;              // warps that share a tile: 1, 2, 4 or 8
+    const void* prefetch;   // weights that a later product will stream: pulled into L2 meanwhile (or null)
+    unsigned long long prefetch_bytes;
 };
 
 constexpr int SLOTS = 4;   // boxes per warp: three in flight while one is being used
@@ -124,9 +126,23 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
             ++a_ti;
         }
     };
-    // the weights do not depend on what ran before: their first boxes are asked for at once
+    // the weights do not depend on what ran before: their first boxes are asked for at once, while the
+    // kernel before this one may still be running; everything else waits for it
     if (lane == 0)
         while (armed < SLOTS - 1 && armed < units) arm();
+    // and the weights of a later product start their way into L2, a slice per CTA, 4 KB per instruction
+    if (p.prefetch && warp == WARPS - 1) {
+        const unsigned long long per_cta = ((p.prefetch_bytes / gridDim.x) + 4095) & ~4095ull;
+        const unsigned long long begin = per_cta * blockIdx.x;
+        const unsigned long long end = begin + per_cta < p.prefetch_bytes ? begin + per_cta : p.prefetch_bytes;
+        for (unsigned long long off = begin + (unsigned long long)lane * 4096; off < end; off += 32ull * 4096) {
+            const unsigned bytes = (unsigned)((end - off < 4096 ? end - off : 4096) & ~15ull);
+            if (bytes)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"((const char*)p.prefetch + off), "r"(bytes) : "memory");
+        }
+    }
+    pdl_trigger();
+    pdl_wait();
 
     // x into shared memory (rows beyond M as zeros), and the input rows' RMS scale from the partial sums of
     // squares: warp w sums rows w, w + 8, ...; its lanes take the parts in strides of 32 (a fixed order)
@@ -317,8 +333,7 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     LinearParams q = p;
     q.group = 1;  // the most warps per tile (a power of two) that still leaves every warp of the grid a tile
     while (q.group < WARPS && (long long)tiles * q.group * 2 <= (long long)grid * WARPS) q.group *= 2;
-    kernel<<<grid, THREADS, smem, stream>>>(q, *map);
-    return launch_status();
+    return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, *map);
 }
 
 template <int MODE, typename TO>
@@ -342,11 +357,12 @@ LLM_EXPORT int llm_linear_decode_parts(int N) { return (N + 15) / 16; }
 // in_ss (or null): [in_parts, M] partial sums of squares; the product is scaled by
 // rsqrt(sum / K + in_eps) per row.  Needs M <= 16, K a multiple of 8, 16-byte aligned rows;
 // otherwise it returns LLM_ERR_UNSUPPORTED and the caller takes another route.  error_flag (host-visible
-// int, or null) is set to 1 if a bounded wait inside the kernel ever gives up.
+// int, or null) is set to 1 if a bounded wait inside the kernel ever gives up.  prefetch (or null): 16-byte
+// aligned weights of a later product, pulled into L2 while this one runs.
 LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldx,
                                  int ldo, const float* in_ss, int in_parts, float in_eps, int mode, int up_offset,
                                  float* resid, const float* norm_w, void* xw_out, float* ss_out, int* error_flag,
-                                 cudaStream_t stream) {
+                                 const void* prefetch, unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return LLM_ERR_UNSUPPORTED;
     LinearParams p;
@@ -367,6 +383,8 @@ LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int ou
     p.xw_out = (__nv_bfloat16*)xw_out;
     p.ss_out = ss_out;
     p.error_flag = error_flag;
+    p.prefetch = prefetch;
+    p.prefetch_bytes = prefetch ? prefetch_bytes : 0;
     if (mode == MODE_RESIDUAL) {
         if (!resid || !norm_w || !xw_out || !ss_out) return LLM_ERR_BAD_ARGUMENT;
         return dispatch<MODE_RESIDUAL, __nv_bfloat16>(p, stream);

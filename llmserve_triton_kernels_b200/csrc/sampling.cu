@@ -72,6 +72,8 @@ __device__ MaxIdx row_argmax(const float* row, int vocab, MaxIdx* scratch) {
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
     __shared__ MaxIdx scratch[33];
+    pdl_trigger();
+    pdl_wait();
     const MaxIdx best = row_argmax(logits + (size_t)blockIdx.x * vocab, vocab, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = best.i;
 }
@@ -195,8 +197,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 LLM_EXPORT int llm_argmax(const float* logits, int rows, int vocab, int* out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return LLM_ERR_BAD_ARGUMENT;
-    argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, out);
-    return launch_status();
+    return launch_pdl(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, out);
 }
 
 LLM_EXPORT int llm_sample(const float* logits, int rows, int vocab, const float* temperature, const int* top_k,

@@ -42,6 +42,10 @@ class GatedMLP(FeedForward):
 
     accepts_sink = True
 
+    def streamed_weights(self):
+        """The matrices a step reads, in the order it reads them."""
+        return [self.w_gate_up, self.w_down]
+
     def forward(self, x, ctx, sink=None):
         act = ops.linear_swiglu(x, self.w_gate_up)
         if sink is not None:
