@@ -26,21 +26,22 @@ class PreNormBlock(Block):
         return all(p.graph_safe for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward))
 
     def forward(self, resid, pending, ctx, cache, next_norm=None):
-        x = self._normed(self.mixer_norm, resid, pending)
+        x = self._normed(self.mixer_norm, resid, pending, self.mixer)
         sink = self._sink(self.mixer, self.ff_norm, resid, ctx)
         pending = self.mixer.forward(x, ctx, cache, sink=sink) if sink else self.mixer.forward(x, ctx, cache)
-        x = self._normed(self.ff_norm, resid, pending)
+        x = self._normed(self.ff_norm, resid, pending, self.feed_forward)
         sink = self._sink(self.feed_forward, next_norm, resid, ctx)
         return self.feed_forward.forward(x, ctx, sink=sink) if sink else self.feed_forward.forward(x, ctx)
 
     @staticmethod
-    def _normed(norm, resid, pending):
+    def _normed(norm, resid, pending, consumer):
         """``pending`` is a contribution still to be added, or the stream already summed and
-        normalised for ``norm`` by the part before (a fused decode kernel did both)."""
+        normalised for ``norm`` by the part before (a fused decode kernel did both).  A consumer
+        that does not say it takes the factored form gets a plain tensor."""
         if isinstance(pending, ops.NormedInput):
             if pending.norm is not norm:
                 raise RuntimeError("a part handed the residual stream on normalised for another norm")
-            return pending
+            return pending if getattr(consumer, "accepts_sink", False) else pending.materialize()
         return norm.add_forward(resid, pending)
 
     @staticmethod

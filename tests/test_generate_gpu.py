@@ -1,0 +1,168 @@
+"""Generation through the Python entry point and the command line on the GPU, against the plain
+implementation: greedy tokens in 32-bit (exact) and bfloat16 (first tokens, then closeness of
+logits), long decoding up to the model's last position, the first tokens of a sequence,
+temperature sampling, and a model of TinyLlama's layer sizes in true 32-bit."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_llama
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def engine(folder, dtype, **opts):
+    from llmserve_triton_kernels_b200 import LLM
+
+    kw = dict(dtype=dtype, device="cuda:0", block_size=8, num_blocks=64, max_batch_size=4, max_num_batched_tokens=48, chunk_size=16)
+    kw.update(opts)
+    return LLM(folder, **kw)
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_greedy_generation_float32_is_token_exact(name, model_folder):
+    from llmserve_triton_kernels_b200 import SamplingParams
+
+    cfg, seed, _, _ = tiny_configs.TINY[name]
+    folder = model_folder(cfg, seed, torch.float32)
+    plain_cfg, w = plain_llama.read_model(folder)
+    prompts = tiny_configs.prompts(name)
+    llm = engine(folder, "float32")
+    outs = llm.generate(prompts, SamplingParams(max_new_tokens=16))
+    for out, prompt in zip(outs, prompts):
+        assert out.token_ids == plain_llama.generate(plain_cfg, w, prompt, 16)
+    # and again under pressure: so few pages that requests are preempted and recomputed
+    tight = engine(folder, "float32", block_size=4, num_blocks=max(16, (max(map(len, prompts)) + 16) // 4 + 3))
+    outs = tight.generate(prompts, SamplingParams(max_new_tokens=16))
+    assert tight.scheduler.stats.preemptions > 0
+    for out, prompt in zip(outs, prompts):
+        assert out.token_ids == plain_llama.generate(plain_cfg, w, prompt, 16)
+    assert tight.cache.num_free_pages == tight.cache.num_pages
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_temperature_sampling_matches_the_plain_sampler(name, model_folder):
+    from llmserve_triton_kernels_b200 import SamplingParams
+
+    cfg, seed, _, _ = tiny_configs.TINY[name]
+    folder = model_folder(cfg, seed, torch.float32)
+    plain_cfg, w = plain_llama.read_model(folder)
+    prompts = tiny_configs.prompts(name)
+    llm = engine(folder, "float32")
+    outs = llm.generate(prompts, SamplingParams(max_new_tokens=16, temperature=0.8, seed=31))
+    for out, prompt in zip(outs, prompts):
+        assert out.token_ids == plain_llama.generate(plain_cfg, w, prompt, 16, temperature=0.8, seed=31)
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_bfloat16_generation_follows_the_plain_one(name, model_folder):
+    """bfloat16 may flip a near-tie, after which the continuations differ; so the engine's own
+    tokens are fed to the plain implementation and the logits compared along them."""
+    from llmserve_triton_kernels_b200 import SamplingParams
+    from llmserve_triton_kernels_b200.engine.batch import StepEntry
+
+    cfg, seed, _, _ = tiny_configs.TINY[name]
+    folder = model_folder(cfg, seed, torch.bfloat16)
+    plain_cfg, w = plain_llama.read_model(folder)
+    prompts = tiny_configs.prompts(name)
+    llm = engine(folder, "bfloat16")
+    outs = llm.generate(prompts, SamplingParams(max_new_tokens=16))
+    for out, prompt in zip(outs, prompts):
+        ref = plain_llama.forward(plain_cfg, w, prompt + out.token_ids)
+        for i, tok in enumerate(out.token_ids):
+            row = ref[len(prompt) - 1 + i]
+            # the chosen token's logit is within bfloat16 error of the plain maximum
+            assert float(row.max() - row[tok]) <= 2e-2 * float(row.abs().max())
+    # decode-only steps ran as CUDA graphs
+    assert llm.step_function.graphs, "no decode step was captured"
+
+
+def test_long_decoding_to_the_last_position(model_folder):
+    """One token at a time from position 1 to the model's limit, in both dtypes."""
+    from llmserve_triton_kernels_b200.engine.batch import StepEntry
+
+    cfg, seed, _, _ = tiny_configs.TINY["a"]
+    limit = cfg["max_position_embeddings"]
+    tokens = tiny_configs.seeded_tokens(cfg["vocab_size"], [limit], 41)[0]
+    for dtype, storage, rtol in (("float32", torch.float32, 2e-5), ("bfloat16", torch.bfloat16, 2e-2)):
+        folder = model_folder(cfg, seed, storage)
+        plain_cfg, w = plain_llama.read_model(folder)
+        ref = plain_llama.forward(plain_cfg, w, tokens)
+        llm = engine(folder, dtype, block_size=16, num_blocks=limit // 16 + 1)
+        for i, tok in enumerate(tokens):
+            logits = llm.step_function([StepEntry("long", [tok], [0])]).float().cpu()[0]
+            tol = rtol * float(ref[i].abs().max())
+            assert float((logits - ref[i]).abs().max()) <= tol, f"{dtype}: position {i}"
+        with pytest.raises(ValueError, match="positions"):
+            llm.step_function([StepEntry("long", [1], [0])])
+
+
+def test_first_tokens_of_a_sequence(model_folder):
+    """Positions 0, 1, 2 alone and together: the smallest contexts a kernel sees."""
+    from llmserve_triton_kernels_b200.engine.batch import StepEntry
+
+    cfg, seed, _, _ = tiny_configs.TINY["b"]
+    tokens = tiny_configs.seeded_tokens(cfg["vocab_size"], [3], 42)[0]
+    for dtype, storage, rtol in (("float32", torch.float32, 2e-5), ("bfloat16", torch.bfloat16, 2e-2)):
+        folder = model_folder(cfg, seed, storage)
+        plain_cfg, w = plain_llama.read_model(folder)
+        ref = plain_llama.forward(plain_cfg, w, tokens)
+        llm = engine(folder, dtype)
+        together = llm.step_function([StepEntry("t", tokens, [0, 1, 2])]).float().cpu()
+        singly = torch.cat([llm.step_function([StepEntry("s", [t], [0])]).float().cpu() for t in tokens])
+        for got in (together, singly):
+            assert float((got - ref).abs().max()) <= rtol * float(ref.abs().max())
+
+
+def test_model_of_tinyllama_layer_sizes_in_true_32_bit(model_folder):
+    """Two layers of TinyLlama 1.1B's sizes (hidden 2048, 32 heads, 4 key/value heads, head size 64,
+    feed-forward 5632, vocabulary 32000): whole, and the last tokens one by one."""
+    from llmserve_triton_kernels_b200.config.presets import PRESETS
+    from llmserve_triton_kernels_b200.engine.batch import StepEntry
+
+    cfg = {**PRESETS["tinyllama-1.1b"], "num_hidden_layers": 2}
+    folder = model_folder(cfg, 0, torch.bfloat16)
+    plain_cfg, w = plain_llama.read_model(folder)
+    tokens = tiny_configs.seeded_tokens(cfg["vocab_size"], [150], 43)[0]
+    ref = plain_llama.forward(plain_cfg, w, tokens)
+    llm = engine(folder, "float32", block_size=16, num_blocks=16, max_num_batched_tokens=256)
+    whole = llm.step_function([StepEntry("w", tokens, list(range(150)))]).float().cpu()
+    assert float((whole - ref).abs().max()) <= 2e-5 * float(ref.abs().max())
+    llm.cache.free_request("w")
+    head = llm.step_function([StepEntry("d", tokens[:140], [139])]).float().cpu()
+    tail = [llm.step_function([StepEntry("d", [t], [0])]).float().cpu() for t in tokens[140:]]
+    got = torch.cat([head] + tail)
+    assert float((got - ref[139:]).abs().max()) <= 2e-5 * float(ref.abs().max())
+    # the same in bfloat16, through the tensor-core kernels and the decode graphs
+    llm16 = engine(folder, "bfloat16", block_size=16, num_blocks=16, max_num_batched_tokens=256)
+    whole16 = llm16.step_function([StepEntry("w", tokens, list(range(150)))]).float().cpu()
+    assert float((whole16 - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+    llm16.cache.free_request("w")
+    head16 = llm16.step_function([StepEntry("d", tokens[:140], [139])]).float().cpu()
+    tail16 = [llm16.step_function([StepEntry("d", [t], [0])]).float().cpu().clone() for t in tokens[140:]]
+    got16 = torch.cat([head16] + tail16)
+    assert float((got16 - ref[139:]).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
+def test_command_line(model_folder):
+    cfg, seed, _, _ = tiny_configs.TINY["a"]
+    folder = model_folder(cfg, seed, torch.float32)
+    plain_cfg, w = plain_llama.read_model(folder)
+    prompt = [t % cfg["vocab_size"] for t in range(10, 26)]  # what the command line feeds when there is no tokenizer
+    out = subprocess.run(
+        [sys.executable, "-m", "llmserve_triton_kernels_b200.cli", "--model", str(folder), "--dtype", "float32",
+         "--max-new-tokens", "12", "--block-size", "8", "--num-blocks", "16"],
+        cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.strip()]
+    assert json.loads(lines[0]) == plain_llama.generate(plain_cfg, w, prompt, 12)
+    assert lines[-1].startswith("[kv_cache] ttft=") and "tok/s" in lines[-1] and "peak mem=" in lines[-1]
