@@ -1,0 +1,316 @@
+// y[M, N] = x[M, K] * w[N, K]^T in bfloat16 on the fifth-generation tensor cores (tcgen05) for
+// many rows (prompt portions): operands staged in shared memory by TMA, accumulators in tensor
+// memory, read back with tcgen05.ld for the epilogue.
+//
+// One CTA computes one 128 x BN tile of y.  Three roles, chosen by warp:
+//   warp 0, one thread : TMA producer — fills a ring of STAGES slots with a 128 x 64 tile of x and a
+//                        BN x 64 tile of w (two of them in MODE_SWIGLU: the gate's and the up's rows
+//                        of the same features), 128-byte swizzled, and arms the slot's mbarrier;
+//   warp 1, one thread : issues tcgen05.mma (M = 128, N = BN, K = 16, four per slot) into tensor
+//                        memory and commits to the slot's "empty" mbarrier, so that the slot is
+//                        refilled as soon as the tensor cores have read it; warp 1 also owns the
+//                        allocation of tensor memory;
+//   warps 2-5          : epilogue — each warp reads its 32 lanes of the accumulator, 32 columns at a
+//                        time, and writes bfloat16 or float32 rows (MODE_SWIGLU: silu(gate) * up).
+// Rows and columns beyond the matrices arrive as zeros from TMA and are masked at the store; K may
+// be any multiple of 8.  Every mbarrier wait is bounded; a wait that gives up sets *error_flag, the
+// roles leave their loops, tensor memory is freed and the kernel returns.
+#include "common.cuh"
+#include "tma.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int MODE_PLAIN = 0, MODE_SWIGLU = 1;
+
+struct GemmParams {
+    void* out;
+    int M, N, K, ldo;
+    int up_offset;  // MODE_SWIGLU: row of w where the up matrix starts
+    int* error_flag;
+};
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, atoms of 8 rows (1024 bytes) one after another
+__device__ __forceinline__ unsigned long long umma_desc(const void* smem) {
+    const unsigned addr = tma::smem_addr(smem);
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr >> 4) & 0x3fff);       // start address, 16-byte units
+    d |= (unsigned long long)1 << 16;                      // leading byte offset (not used by swizzled K-major)
+    d |= (unsigned long long)(1024 >> 4) << 32;            // stride byte offset: 8 rows of 128 bytes
+    d |= (unsigned long long)1 << 46;                      // descriptor version of this architecture
+    d |= (unsigned long long)2 << 61;                      // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a, unsigned long long b, unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"((unsigned)accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tma::smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename TO>
+__device__ __forceinline__ void store32(TO* dst, const float (&v)[32], int valid);
+template <>
+__device__ __forceinline__ void store32<float>(float* dst, const float (&v)[32], int valid) {
+    if (valid == 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < valid) dst[i] = v[i];
+    }
+}
+template <>
+__device__ __forceinline__ void store32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[32], int valid) {
+    if (valid == 32 && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+            uint4 u;
+            __nv_bfloat162 a = __floats2bfloat162_rn(v[i], v[i + 1]), b = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+            __nv_bfloat162 c = __floats2bfloat162_rn(v[i + 4], v[i + 5]), d = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+            u.x = *reinterpret_cast<unsigned*>(&a);
+            u.y = *reinterpret_cast<unsigned*>(&b);
+            u.z = *reinterpret_cast<unsigned*>(&c);
+            u.w = *reinterpret_cast<unsigned*>(&d);
+            *reinterpret_cast<uint4*>(dst + i) = u;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < valid) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+
+template <int BN, int MODE, int STAGES, typename TO>
+__global__ void __launch_bounds__(THREADS)
+gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap) {
+    constexpr int NB = MODE == MODE_SWIGLU ? 2 : 1;           // w tiles per slot
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr int SLOT_BYTES = A_BYTES + NB * B_BYTES;
+    constexpr int TMEM_COLS = NB * BN <= 32 ? 32 : NB * BN <= 64 ? 64 : NB * BN <= 128 ? 128 : 256;  // a power of two
+    // MODE_SWIGLU: the gate's and the up's tiles lie one after the other in the slot, which is one K-major tile of
+    // 2 BN rows: one product of N = 2 BN fills columns [0, BN) with the gate's sums and [BN, 2 BN) with the up's
+    constexpr int UMMA_N = NB * BN;
+    static_assert(UMMA_N % 16 == 0 && UMMA_N >= 16 && UMMA_N <= 256, "tcgen05.mma with M = 128 takes N in steps of 16 up to 256");
+    constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(UMMA_N >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) unsigned long long full[STAGES], empty[STAGES], acc_ready;
+    __shared__ unsigned tmem_base;
+    __shared__ int gave_up;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int kblocks = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) {
+            tma::mbar_init(&full[s], 1);
+            tma::mbar_init(&empty[s], 1);
+        }
+        tma::mbar_init(&acc_ready, 1);
+        gave_up = 0;
+        tma::mbar_fence_init();
+        tma::prefetch_map(&xmap);
+        tma::prefetch_map(&wmap);
+    }
+    if (warp == 1) {  // one warp allocates the accumulators' columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tma::smem_addr(&tmem_base)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    pdl_trigger();
+    pdl_wait();  // x comes from the kernel before
+
+    auto fail = [&]() {
+        gave_up = 1;
+        if (p.error_flag) atomicExch(p.error_flag, 1);
+    };
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer ----
+        for (int kb = 0; kb < kblocks && !gave_up; ++kb) {
+            const int s = kb % STAGES;
+            if (kb >= STAGES && !tma::mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) {
+                fail();
+                break;
+            }
+            unsigned char* slot = ring + (size_t)s * SLOT_BYTES;
+            tma::mbar_expect_tx(&full[s], SLOT_BYTES);
+            tma::load_2d(slot, &xmap, kb * BK, m0, &full[s]);
+            tma::load_2d(slot + A_BYTES, &wmap, kb * BK, n0, &full[s]);
+            if (NB == 2) tma::load_2d(slot + A_BYTES + B_BYTES, &wmap, kb * BK, p.up_offset + n0, &full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- tensor-core issuer ----
+        const unsigned d_tmem = tmem_base;
+        for (int kb = 0; kb < kblocks && !gave_up; ++kb) {
+            const int s = kb % STAGES;
+            if (!tma::mbar_wait(&full[s], (kb / STAGES) & 1)) {
+                fail();
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const unsigned char* slot = ring + (size_t)s * SLOT_BYTES;
+            const unsigned long long a = umma_desc(slot), b = umma_desc(slot + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+                // 16 k = 32 bytes further along the 128-byte rows: the start address moves by two 16-byte units
+                umma_bf16(d_tmem, a + 2 * k, b + 2 * k, IDESC, (kb | k) != 0);
+            }
+            umma_commit(&empty[s]);  // arrives when the products above have read the slot
+        }
+        umma_commit(&acc_ready);  // arrives when every product has landed in tensor memory
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w may touch the 32 lanes (warp % 4) * 32 .. of tensor memory ----
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        const bool ok = __all_sync(0xffffffffu, tma::mbar_wait(&acc_ready, 0));
+        if (!ok) {
+            if (lane == 0) fail();
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                float v[32];
+                tmem_ld32(lane_base + c, v);
+                if (MODE == MODE_SWIGLU) {
+                    float u[32];
+                    tmem_ld32(lane_base + BN + c, u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * u[i];
+                }
+                const int col = n0 + c;
+                if (row < p.M && col < p.N)
+                    store32<TO>(reinterpret_cast<TO*>(p.out) + (size_t)row * p.ldo + col, v, min(32, p.N - col));
+            }
+        }
+    }
+    // everyone is done with tensor memory: the allocating warp gives it back
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+    }
+}
+
+struct MapKey {
+    const void* p;
+    int rows, cols, ld, box_rows;
+    bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.p) ^ ((size_t)k.rows << 24) ^ ((size_t)k.cols << 8) ^ (size_t)k.box_rows ^ ((size_t)k.ld << 40);
+    }
+};
+
+// Maps are cached by (address, shape): weights live for the life of the model, and activations
+// of a shape come back to the same addresses from the caching allocator.
+const CUtensorMap* map_of(const void* base, int rows, int cols, int ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> maps;
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    const MapKey key{base, rows, cols, ld, box_rows};
+    auto it = maps.find(key);
+    if (it != maps.end()) return &it->second;
+    if (maps.size() > 4096) maps.clear();
+    CUtensorMap map;
+    if (!tma::make_map_2d_bf16(&map, base, rows, cols, ld, box_rows, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return nullptr;
+    return &maps.emplace(key, map).first->second;
+}
+
+template <int BN, int MODE, int STAGES, typename TO>
+int launch(const void* x, int ldx, const void* w, int w_rows, const GemmParams& p, cudaStream_t stream) {
+    constexpr int NB = MODE == MODE_SWIGLU ? 2 : 1;
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + NB * BN * BK * 2) + 1024;
+    auto kernel = gemm_tcgen05_kernel<BN, MODE, STAGES, TO>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const CUtensorMap* xmap = map_of(x, p.M, p.K, ldx, BM);
+    const CUtensorMap* wmap = map_of(w, w_rows, p.K, p.K, BN);
+    if (!xmap || !wmap) return LLM_ERR_UNSUPPORTED;
+    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM);
+    if (grid.y > 65535) return LLM_ERR_UNSUPPORTED;
+    return launch_pdl(kernel, grid, dim3(THREADS), smem, stream, p, *xmap, *wmap);
+}
+
+}  // namespace
+
+// bfloat16 x [M, K] (row stride ldx, a multiple of 8) times w^T (w contiguous [N or up_offset + N, K]).
+//   mode 0: out [M, N] (row stride ldo) in bfloat16 or float32.
+//   mode 1: w = [gate | up], the up rows starting at row up_offset; out [M, N] bfloat16 = silu(gate) * up.
+// Needs K a multiple of 8 and 16-byte aligned bases; otherwise LLM_ERR_UNSUPPORTED.
+LLM_EXPORT int llm_gemm_tcgen05(const void* x, int ldx, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
+                                int mode, int up_offset, int* error_flag, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return LLM_ERR_UNSUPPORTED;
+    GemmParams p;
+    p.out = out;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.ldo = ldo;
+    p.up_offset = up_offset;
+    p.error_flag = error_flag;
+    if (mode == MODE_SWIGLU) {
+        if (out_dtype != LLM_BF16) return LLM_ERR_BAD_ARGUMENT;
+        return launch<128, MODE_SWIGLU, 4, __nv_bfloat16>(x, ldx, w, up_offset + N, p, stream);
+    }
+    if (mode != MODE_PLAIN) return LLM_ERR_BAD_ARGUMENT;
+    // the tile width that wastes the fewest SM-rounds: wide tiles re-read x less often, but the last round of
+    // CTAs should not be nearly empty
+    const int row_tiles = (M + BM - 1) / BM, sms = 148;
+    int best = 128;
+    double best_cost = 1e30;
+    for (int bn : {256, 192, 160, 128}) {
+        const long long tiles = (long long)((N + bn - 1) / bn) * row_tiles;
+        const double rounds = (double)((tiles + sms - 1) / sms);
+        const double cost = rounds * bn * (bn == 256 ? 1.0 : bn == 192 ? 1.03 : bn == 160 ? 1.06 : 1.12);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    if (out_dtype == LLM_BF16) {
+        if (best == 256) return launch<256, MODE_PLAIN, 4, __nv_bfloat16>(x, ldx, w, N, p, stream);
+        if (best == 192) return launch<192, MODE_PLAIN, 5, __nv_bfloat16>(x, ldx, w, N, p, stream);
+        if (best == 160) return launch<160, MODE_PLAIN, 5, __nv_bfloat16>(x, ldx, w, N, p, stream);
+        return launch<128, MODE_PLAIN, 6, __nv_bfloat16>(x, ldx, w, N, p, stream);
+    }
+    if (out_dtype == LLM_F32) {
+        if (best >= 192) return launch<256, MODE_PLAIN, 4, float>(x, ldx, w, N, p, stream);
+        return launch<128, MODE_PLAIN, 6, float>(x, ldx, w, N, p, stream);
+    }
+    return LLM_ERR_BAD_ARGUMENT;
+}

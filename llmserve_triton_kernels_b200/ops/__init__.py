@@ -27,6 +27,7 @@ _SIGNATURES = {
     "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_ulonglong, _vp],
+    "llm_gemm_tcgen05": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_attention_generic": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "llm_argmax": [_vp, _i, _i, _vp, _vp],
@@ -66,6 +67,7 @@ _MMA_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention; o
 _SMALL_ROWS = 16  # requests with at most this many (token, group member) rows take the split-key shape
 _SMALL_TILE_KEYS = 128  # keys one CTA of that shape covers per tile
 _SM_COUNT = 148
+_TCGEN05_MIN_ROWS = 128  # from this many rows a bfloat16 product runs on tcgen05 with TMA-fed tiles (own kernel)
 _DECODE_LINEAR_MAX_ROWS = 16  # up to this many rows a bfloat16 matrix product streams the weights once (own kernel)
 _FORCE_GENERIC_ATTENTION = False  # tests switch the tensor-core attention off to reach the general kernel in bfloat16
 
@@ -299,10 +301,31 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Te
         out = _decode_linear(x, w, out_dtype, 0, n)
         if out is not None:
             return out
+    if m >= _TCGEN05_MIN_ROWS:
+        out = _tcgen05_linear(x, w, out_dtype, 0, n)
+        if out is not None:
+            return out
     library()  # the engine never runs without its kernels, even where a matrix product is the vendor's
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())
     return torch.matmul(x, w.t()).to(out_dtype)
+
+
+def _tcgen05_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):
+    """The tcgen05 + TMA product for many rows; None if it refuses the shape."""
+    m, k = x.shape
+    if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()):
+        return None
+    out = torch.empty((m, n_out), dtype=out_dtype, device=x.device)
+    code = _launch(
+        "llm_gemm_tcgen05", _ptr(x), x.stride(0), _ptr(w), _ptr(out), _code(out_dtype), m, n_out, k, n_out, mode, up_offset,
+        _error_flag_ptr(), _stream(),
+    )
+    if code == 10002:
+        add_launches(-1)
+        return None
+    _check(code, "linear (tcgen05)")
+    return out
 
 
 def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
@@ -312,6 +335,10 @@ def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
     xt = x.xw if isinstance(x, NormedInput) else x
     if xt.dtype == torch.bfloat16 and xt.shape[0] <= _DECODE_LINEAR_MAX_ROWS:
         out = _decode_linear(x, w_gate_up, torch.bfloat16, 1, inter, up_offset=inter)
+        if out is not None:
+            return out
+    if xt.dtype == torch.bfloat16 and xt.shape[0] >= _TCGEN05_MIN_ROWS and not isinstance(x, NormedInput):
+        out = _tcgen05_linear(x, w_gate_up, torch.bfloat16, 1, inter, up_offset=inter)
         if out is not None:
             return out
     return swiglu(linear(x, w_gate_up))

@@ -84,7 +84,8 @@ def test_linear_float32_is_true_32_bit_and_row_independent(m, n, k):
 @pytest.mark.parametrize(
     "m,n,k",
     [(1, 48, 64), (9, 344, 96), (130, 2560, 2048), (64, 100, 172), (8, 2560, 2048), (64, 11264, 2048), (33, 2048, 5632),
-     (5, 40, 72), (17, 100, 48), (3, 64, 88), (16, 17, 8), (1, 32000, 2048)],
+     (5, 40, 72), (17, 100, 48), (3, 64, 88), (16, 17, 8), (1, 32000, 2048), (2048, 2048, 5632), (257, 129, 8), (128, 128, 64),
+     (1000, 3000, 1096)],
 )
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_linear_bfloat16(m, n, k, out_dtype):
@@ -95,7 +96,8 @@ def test_linear_bfloat16(m, n, k, out_dtype):
     torch.testing.assert_close(got.double(), want, atol=2e-2 * 0.05 * k**0.5, rtol=1e-2)
 
 
-@pytest.mark.parametrize("m,inter,k", [(1, 5632, 2048), (8, 172 * 8, 64), (16, 100, 96), (5, 16, 8)])
+@pytest.mark.parametrize("m,inter,k", [(1, 5632, 2048), (8, 172 * 8, 64), (16, 100, 96), (5, 16, 8), (17, 100, 96), (300, 5632, 2048),
+                                       (129, 200, 72), (2048, 1000, 256)])
 def test_linear_swiglu_fused_for_few_rows(m, inter, k):
     x = rnd(m, k, dtype=torch.bfloat16, seed=31)
     w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=32, std=0.05)
