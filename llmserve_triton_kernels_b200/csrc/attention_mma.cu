@@ -9,7 +9,7 @@
 //   * KEYS: 16 rows; the 4 warps walk different keys of each tile and merge at the end.  Serves
 //     decode tokens and very short portions.
 // A launch of one shape skips the requests that belong to the other.  Keys and values are copied
-// page by page into shared memory with cp.async (two stages), the products are mma.sync
+// page by page into shared memory with cp.async (a ring of three or four tiles), the products are mma.sync
 // m16n8k16 with 32-bit accumulation, the softmax is the running (max, sum) form in 32-bit in the
 // base-2 domain.  Long contexts with few rows are cut over gridDim.x ("splits"); each split
 // writes an unnormalised 32-bit partial and its (max, sum) to scratch memory, and the split that
@@ -70,6 +70,9 @@ struct AttnParams {
     int* counters;          // [requests * KV] zeros: how many splits of a (request, kv head) have finished
 };
 
+// Stages of the key/value ring: four where shared memory allows, three for the largest tiles.
+__host__ __device__ constexpr int stages_of(int D, int key_warps) { return key_warps > 1 ? (D <= 64 ? 4 : 3) : (D <= 64 ? 4 : 3); }
+
 // D: head size.  ROW_WARPS x KEY_WARPS = 4 warps.  BN: keys per warp and tile.
 template <int D, int ROW_WARPS, int KEY_WARPS, int BN>
 __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams p) {
@@ -81,9 +84,10 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
     constexpr int NT_S = BN / 8;  // 8-key tiles of a warp's scores
     constexpr int NT_O = D / 8;   // 8-wide tiles of the output
     constexpr bool SMALL = KEY_WARPS > 1;
+    constexpr int STAGES = stages_of(D, KEY_WARPS);  // tiles in flight: a tile's latency is a page lookup plus a trip to HBM
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][BNC][D]
-    __nv_bfloat16* v_s = k_s + 2 * BNC * D;                           // [2][BNC][D]
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][BNC][D]
+    __nv_bfloat16* v_s = k_s + STAGES * BNC * D;                      // [STAGES][BNC][D]
 
     const int split = blockIdx.x, kvh = blockIdx.y;
     const int r = blockIdx.z / p.tiles_per_request, tile = blockIdx.z % p.tiles_per_request;
@@ -115,10 +119,10 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
     const int key_hi = pos0 + tok_last;
     const int key_lo = p.window > 0 ? max(0, pos0 + tok_first - p.window + 1) : 0;
     const int tile_first = key_lo / BNC, tile_last = key_hi / BNC;
-    // a split takes at least two tiles when keys are split inside the CTA too, so short contexts use few
-    // splits however many the grid has; splits beyond the last active one have nothing to do
+    // merging splits costs a few trips to L2, more than walking eight tiles (1024 keys) one after the other:
+    // short contexts use one split however many the grid has; splits beyond the last active one do nothing
     const int n_tiles = tile_last - tile_first + 1;
-    const int per_split = max(SMALL ? 2 : 1, (n_tiles + p.splits - 1) / p.splits);
+    const int per_split = max(SMALL ? 8 : 1, (n_tiles + p.splits - 1) / p.splits);
     const int active_splits = (n_tiles + per_split - 1) / per_split;
     const int t_begin = tile_first + split * per_split;
     const int t_end = min(tile_last + 1, t_begin + per_split);
@@ -174,20 +178,18 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
         for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    if (t_begin < t_end) {
-        load_tile(t_begin, 0);
+    // one commit group per tile, empty past the end, so that the wait below counts tiles
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        if (t_begin + i < t_end) load_tile(t_begin + i, i);
         cp_async_commit();
     }
     for (int t = t_begin; t < t_end; ++t) {
-        const int stage = (t - t_begin) & 1;
-        if (t + 1 < t_end) {
-            load_tile(t + 1, stage ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        const int stage = (t - t_begin) % STAGES;
+        cp_async_wait<STAGES - 2>();  // tile t has landed (this thread's copies) ...
+        __syncthreads();              // ... everyone's; and the stage refilled next is no longer read
+        if (t + STAGES - 1 < t_end) load_tile(t + STAGES - 1, (t - t_begin + STAGES - 1) % STAGES);
+        cp_async_commit();
         const __nv_bfloat16* ks_tile = k_s + (stage * BNC + key_warp * BN) * D;
         const __nv_bfloat16* vs_tile = v_s + (stage * BNC + key_warp * BN) * D;
         const int key_base = t * BNC + key_warp * BN;
@@ -267,8 +269,9 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
                 mma_bf16(oacc[2 * dp + 1], pa, b[2], b[3]);
             }
         }
-        __syncthreads();  // the stage may be refilled
     }
+    cp_async_wait<0>();
+    __syncthreads();  // the ring is free (the small shape merges its warps through it)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
@@ -414,7 +417,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 template <int D, int ROW_WARPS, int KEY_WARPS, int BN>
 int launch_shape(const AttnParams& p, int requests, cudaStream_t stream) {
     constexpr int BNC = BN * KEY_WARPS;
-    size_t smem = (size_t)2 * 2 * BNC * D * sizeof(__nv_bfloat16);
+    size_t smem = (size_t)stages_of(D, KEY_WARPS) * 2 * BNC * D * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)KEY_WARPS * 16 * (D + 2) * sizeof(float);
     if (KEY_WARPS > 1 && merge > smem) smem = merge;
     auto kernel = attention_mma_kernel<D, ROW_WARPS, KEY_WARPS, BN>;

@@ -221,11 +221,13 @@ def test_paged_attention_long_portions_bfloat16(H, KV, D, page_size, window, gen
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("far_key", [0, 15, 16, 511, 512, 700])
-def test_paged_attention_finds_one_far_key(dtype, far_key):
-    """One key among 701 is made to match the query: the output must be that key's value.  A
-    kernel that loses a key at a page's edge or at a chunk's edge would return an average."""
-    H, KV, D, page_size, n = 4, 2, 64, 16, 701
+@pytest.mark.parametrize("far_key,n", [(0, 701), (15, 701), (16, 701), (511, 701), (512, 701), (700, 701), (0, 2101), (1023, 2101),
+                                       (1024, 2101), (2100, 2101)])
+def test_paged_attention_finds_one_far_key(dtype, far_key, n):
+    """One key among hundreds (or two thousand: several splits of the keys, merged) is made to match
+    the query: the output must be that key's value.  A kernel that loses a key at a page's edge,
+    a chunk's edge or a split's edge would return an average."""
+    H, KV, D, page_size = 4, 2, 64, 16
     pool, table, keys, values = make_cache([n], KV, D, page_size, dtype, seed=3)
     q = rnd(1, H * D, dtype=dtype, seed=5, std=0.1)
     direction = torch.nn.functional.normalize(rnd(D, seed=6), dim=0)
