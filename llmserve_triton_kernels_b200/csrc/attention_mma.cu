@@ -46,6 +46,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {  // 2^x by the special-function unit: exp2(-inf) = 0, relative error about 2^-22
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -118,11 +123,14 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
     const int tok_first = row0 / G, tok_last = (min(rows_total, row0 + BM) - 1) / G;
     const int key_hi = pos0 + tok_last;
     const int key_lo = p.window > 0 ? max(0, pos0 + tok_first - p.window + 1) : 0;
+    // a key tile needs no mask if every row of the CTA sees all of it (rows past the end are never written)
+    const int tile_pos_min = pos0 + tok_first;
+    const int tile_lo_max = p.window > 0 ? max(0, pos0 + tok_last - p.window + 1) : 0;
     const int tile_first = key_lo / BNC, tile_last = key_hi / BNC;
-    // merging splits costs a few trips to L2, more than walking eight tiles (1024 keys) one after the other:
-    // short contexts use one split however many the grid has; splits beyond the last active one do nothing
+    // a split takes at least two tiles, so short contexts use few splits however many the grid has; splits
+    // beyond the last active one do nothing
     const int n_tiles = tile_last - tile_first + 1;
-    const int per_split = max(SMALL ? 8 : 1, (n_tiles + p.splits - 1) / p.splits);
+    const int per_split = max(SMALL ? 2 : 1, (n_tiles + p.splits - 1) / p.splits);
     const int active_splits = (n_tiles + per_split - 1) / per_split;
     const int t_begin = tile_first + split * per_split;
     const int t_end = min(tile_last + 1, t_begin + per_split);
@@ -213,18 +221,29 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
                 mma_bf16(sacc[2 * np + 1], qa[ks], b[2], b[3]);
             }
         }
-        // mask, running max and sum
+        // mask (only in tiles that some row does not see whole), running max and sum
         float mx[2] = {-INFINITY, -INFINITY};
+        const bool whole = key_base + BN - 1 <= tile_pos_min && key_base >= tile_lo_max;
+        if (whole) {
 #pragma unroll
-        for (int nt = 0; nt < NT_S; ++nt)
+            for (int nt = 0; nt < NT_S; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = e >> 1;
-                const int j = key_base + nt * 8 + qc * 2 + (e & 1);
-                const bool visible = j <= row_pos[i] && j >= row_lo[i];
-                sacc[nt][e] = visible ? sacc[nt][e] * p.scale_log2 : -INFINITY;
-                mx[i] = fmaxf(mx[i], sacc[nt][e]);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    sacc[nt][e] *= p.scale_log2;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], sacc[nt][e]);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int j = key_base + nt * 8 + qc * 2 + (e & 1);
+                    const bool visible = j <= row_pos[i] && j >= row_lo[i];
+                    sacc[nt][e] = visible ? sacc[nt][e] * p.scale_log2 : -INFINITY;
+                    mx[i] = fmaxf(mx[i], sacc[nt][e]);
+                }
+        }
         float alpha[2], m_use[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -232,7 +251,7 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
             const float m_new = fmaxf(m_run[i], mx[i]);
             m_use[i] = m_new == -INFINITY ? 0.f : m_new;
-            alpha[i] = exp2f(m_run[i] - m_use[i]);
+            alpha[i] = fast_exp2(m_run[i] - m_use[i]);
             m_run[i] = m_new;
             l_run[i] *= alpha[i];
         }
@@ -240,7 +259,7 @@ __global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams
         for (int nt = 0; nt < NT_S; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float pv = exp2f(sacc[nt][e] - m_use[e >> 1]);
+                const float pv = fast_exp2(sacc[nt][e] - m_use[e >> 1]);
                 sacc[nt][e] = pv;
                 l_run[e >> 1] += pv;
             }
