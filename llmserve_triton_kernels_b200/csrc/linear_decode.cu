@@ -32,7 +32,7 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-constexpr int MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_RESIDUAL = 2;
+constexpr int MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_RESIDUAL = 2, MODE_QKV = 3;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                          unsigned b1) {
@@ -56,6 +56,13 @@ struct LinearParams {
     float* ss_out;          // MODE_RESIDUAL: [tiles of 16 features, M]
     int* error_flag;        // set to 1 if a wait for a copy gave up (host-visible memory), or null
     int group;              // warps that share a tile: 1, 2, 4 or 8
+    // MODE_QKV: w rows are [H query heads | KV key heads | KV value heads] x D; out is [M, H * D]
+    const int* positions;   // [M]
+    const float* rotary;    // [positions, D] = cos | sin halves, or null (no rotation)
+    int rotary_rows;
+    const int* slot_map;    // [M] page * page_size + offset of each token
+    __nv_bfloat16* pool;    // [pages, 2, KV, page_size, D]
+    int H, KV, D, page_size;
     const void* prefetch;   // weights that a later product will stream: pulled into L2 meanwhile (or null)
     unsigned long long prefetch_bytes;
 };
@@ -116,6 +123,10 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
         if (MODE == MODE_SWIGLU) {  // the map's box is 8 rows: gate rows, then up rows
             tma::load_2d(dst, &wmap, a_kb * BOXK, tile * 8, &full[warp][sl]);
             tma::load_2d(dst + 8 * BOXK, &wmap, a_kb * BOXK, p.up_offset + tile * 8, &full[warp][sl]);
+        } else if (MODE == MODE_QKV) {  // 8 lanes of a head's first half, then their partners in the second half
+            const int per_head = p.D >> 4, head = tile / per_head, y = head * p.D + (tile - head * per_head) * 8;
+            tma::load_2d(dst, &wmap, a_kb * BOXK, y, &full[warp][sl]);
+            tma::load_2d(dst + 8 * BOXK, &wmap, a_kb * BOXK, y + (p.D >> 1), &full[warp][sl]);
         } else {
             tma::load_2d(dst, &wmap, a_kb * BOXK, tile * 16, &full[warp][sl]);
         }
@@ -226,7 +237,38 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
         }
         // the tile is complete
         const int tile = first + ti * stride, n0 = tile * FEATURES;
-        if constexpr (MODE == MODE_SWIGLU) {
+        if constexpr (MODE == MODE_QKV) {
+            // this thread: lanes j (e = 0, 1) and j + D/2 (e = 2, 3) of one head for tokens 8 t + 2 qc and + 1:
+            // a rotation pair.  Query heads go to `out` rotated, key heads rotated into their page, value heads as
+            // they are into theirs.
+            const int D = p.D, half = D >> 1, per_head = D >> 4;
+            const int head = tile / per_head, j = (tile - head * per_head) * 8 + qr;
+#pragma unroll
+            for (int t = 0; t < MT; ++t)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int m = 8 * t + 2 * qc + i;
+                    if (m >= M) continue;
+                    float a = acc[t][i] * row_scale[m], b = acc[t][2 + i] * row_scale[m];
+                    if (head < p.H + p.KV && p.rotary) {
+                        const int pos = min(max(p.positions[m], 0), p.rotary_rows - 1);
+                        const float c = p.rotary[(size_t)pos * D + j], sn = p.rotary[(size_t)pos * D + half + j];
+                        const float ra = a * c - b * sn, rb = b * c + a * sn;
+                        a = ra;
+                        b = rb;
+                    }
+                    __nv_bfloat16* dst;
+                    if (head < p.H) {
+                        dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + head * D + j;
+                    } else {
+                        const int slot = p.slot_map[m], page = slot / p.page_size, off = slot - page * p.page_size;
+                        const int is_v = head >= p.H + p.KV, kvh = head - p.H - (is_v ? p.KV : 0);
+                        dst = p.pool + (((size_t)(page * 2 + is_v) * p.KV + kvh) * p.page_size + off) * D + j;
+                    }
+                    dst[0] = __float2bfloat16_rn(a);
+                    dst[half] = __float2bfloat16_rn(b);
+                }
+        } else if constexpr (MODE == MODE_SWIGLU) {
             // this thread: gate (e = 0, 1) and up (e = 2, 3) sums of feature qr for tokens 8 t + 2 qc and + 1
             const int n = n0 + qr;
 #pragma unroll
@@ -326,7 +368,7 @@ int launch(const LinearParams& p, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    const CUtensorMap* map = weight_map(p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, FEATURES);
+    const CUtensorMap* map = weight_map(p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, MODE == MODE_QKV ? 8 : FEATURES);
     if (!map) return LLM_ERR_UNSUPPORTED;
     const int tiles = (p.N + FEATURES - 1) / FEATURES;
     const int grid = tiles < sm_count() ? tiles : sm_count();
@@ -336,12 +378,19 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, *map);
 }
 
+// MODE_QKV: the product for all heads, rotary encoding of query and key heads, and the write of keys and
+// values into their pages, in one launch (see llm_linear_decode for the other arguments).
 template <int MODE, typename TO>
 int dispatch(const LinearParams& p, cudaStream_t stream) {
     return p.M <= 8 ? launch<1, MODE, TO>(p, stream) : launch<2, MODE, TO>(p, stream);
 }
 
 }  // namespace
+
+LLM_EXPORT int llm_linear_decode_qkv(const void* x, const void* w, void* q_out, int M, int K, int ldx, const float* in_ss,
+                                     int in_parts, float in_eps, const int* positions, const float* rotary, int rotary_rows,
+                                     const int* slot_map, void* pool, int H, int KV, int D, int page_size, int* error_flag,
+                                     cudaStream_t stream);
 
 // The most rows this kernel takes; more go to another matrix product.
 LLM_EXPORT int llm_linear_decode_max_rows() { return 16; }
@@ -365,7 +414,7 @@ LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int ou
                                  const void* prefetch, unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return LLM_ERR_UNSUPPORTED;
-    LinearParams p;
+    LinearParams p = {};
     p.x = (const __nv_bfloat16*)x;
     p.w = (const __nv_bfloat16*)w;
     p.out = out;
@@ -397,4 +446,42 @@ LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int ou
     if (out_dtype == LLM_BF16) return dispatch<MODE_PLAIN, __nv_bfloat16>(p, stream);
     if (out_dtype == LLM_F32) return dispatch<MODE_PLAIN, float>(p, stream);
     return LLM_ERR_BAD_ARGUMENT;
+}
+
+// bfloat16 x [M, K] times the stacked projection w [(H + 2 KV) D, K]: query heads, rotated by each token's
+// row of `rotary` ([positions, D] = cos | sin halves; null: no rotation), go to q_out [M, H D]; key heads,
+// rotated, and value heads go into `pool` [pages, 2, KV, page_size, D] at slot_map[m].  KV = 0: w holds
+// query heads only and nothing is written to the pool.  Needs M <= 16, K and D multiples of 8 and 16.
+LLM_EXPORT int llm_linear_decode_qkv(const void* x, const void* w, void* q_out, int M, int K, int ldx, const float* in_ss,
+                                     int in_parts, float in_eps, const int* positions, const float* rotary, int rotary_rows,
+                                     const int* slot_map, void* pool, int H, int KV, int D, int page_size, int* error_flag,
+                                     cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (M > 16 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || D < 16 || (D & 15) || H < 1 || KV < 0)
+        return LLM_ERR_UNSUPPORTED;
+    if (KV > 0 && (!slot_map || !pool || page_size < 1)) return LLM_ERR_BAD_ARGUMENT;
+    if (rotary && (!positions || rotary_rows < 1)) return LLM_ERR_BAD_ARGUMENT;
+    LinearParams p = {};
+    p.x = (const __nv_bfloat16*)x;
+    p.w = (const __nv_bfloat16*)w;
+    p.out = q_out;
+    p.M = M;
+    p.N = (H + 2 * KV) * D;
+    p.K = K;
+    p.ldx = ldx;
+    p.ldo = H * D;
+    p.in_ss = in_ss;
+    p.in_parts = in_parts;
+    p.in_eps = in_eps;
+    p.error_flag = error_flag;
+    p.positions = positions;
+    p.rotary = rotary;
+    p.rotary_rows = rotary_rows;
+    p.slot_map = slot_map;
+    p.pool = (__nv_bfloat16*)pool;
+    p.H = H;
+    p.KV = KV;
+    p.D = D;
+    p.page_size = page_size;
+    return dispatch<MODE_QKV, __nv_bfloat16>(p, stream);
 }

@@ -27,6 +27,7 @@ _SIGNATURES = {
     "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_ulonglong, _vp],
+    "llm_linear_decode_qkv": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_tcgen05": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_attention_generic": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
@@ -326,6 +327,48 @@ def _tcgen05_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):
         return None
     _check(code, "linear (tcgen05)")
     return out
+
+
+def linear_qkv_rope(
+    x,
+    w_in: torch.Tensor,
+    positions: torch.Tensor,
+    table: torch.Tensor | None,
+    slot_map: torch.Tensor | None,
+    pool: torch.Tensor | None,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    write_kv: bool = True,
+) -> torch.Tensor | None:
+    """For few bfloat16 rows, one kernel instead of three: the stacked query/key/value projection,
+    the rotary encoding of query and key heads, and the write of keys and values into their
+    pages.  Returns the rotated queries ``[M, num_heads * head_dim]``, or None when the shape is
+    not taken (the caller then runs the product, the rotation and the write one by one)."""
+    scaled = isinstance(x, NormedInput)
+    xt = x.xw if scaled else x
+    m, k = xt.shape
+    if not (xt.dtype == torch.bfloat16 and m <= _DECODE_LINEAR_MAX_ROWS and xt.stride(1) == 1 and w_in.is_contiguous()):
+        return None
+    if head_dim % 16 or (table is not None and (table.dtype != torch.float32 or table.shape[1] != head_dim)):
+        return None
+    kv = num_kv_heads if write_kv else 0
+    _need(w_in.shape[0] == (num_heads + 2 * kv) * head_dim, "the stacked projection does not match the heads")
+    if kv:
+        _i32(slot_map, "slot_map")
+        _need(pool.dtype == torch.bfloat16 and pool.is_contiguous() and tuple(pool.shape[1:3]) == (2, kv) and pool.shape[4] == head_dim, "the pool plane does not match the heads")
+    q = torch.empty((m, num_heads * head_dim), dtype=torch.bfloat16, device=xt.device)
+    code = _launch(
+        "llm_linear_decode_qkv", _ptr(xt), _ptr(w_in), _ptr(q), m, k, xt.stride(0), _ptr(x.ss) if scaled else None,
+        x.ss.shape[0] if scaled else 0, x.eps if scaled else 0.0, _ptr(positions), _ptr(table),
+        table.shape[0] if table is not None else 0, _ptr(slot_map) if kv else None, _ptr(pool) if kv else None, num_heads, kv,
+        head_dim, pool.shape[3] if kv else 1, _error_flag_ptr(), _stream(),
+    )
+    if code == 10002:
+        add_launches(-1)
+        return None
+    _check(code, "linear_qkv_rope")
+    return q
 
 
 def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:

@@ -75,17 +75,15 @@ class PagedAttention(Mixer):
 
     def forward(self, x, ctx, cache, sink=None):
         H, KV, D = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = ops.linear(x, self.w_in)
         table = getattr(self.position, "rotary_table", None)
-        if self.position is not None and table is None:
-            # a position encoding without a table: let it rewrite q and k, then store unrotated
-            n = qkv.shape[0]
-            q = qkv[:, : H * D].unflatten(1, (H, D))
-            k = qkv[:, H * D : (H + KV) * D].unflatten(1, (KV, D)) if self.own_kv else qkv.new_empty((n, 0, D))
-            self.position.apply(q, k, ctx.positions)
-        ops.rope_kv_write(
-            qkv, ctx.positions, table, cache.slot_map, cache.pool, H, KV, D, write_kv=self.own_kv
-        )
+        qkv = None
+        if self.position is None or table is not None:
+            # few rows: projection, rotation and the cache write in one kernel
+            qkv = ops.linear_qkv_rope(
+                x, self.w_in, ctx.positions, table, cache.slot_map, cache.pool, H, KV, D, write_kv=self.own_kv
+            )
+        if qkv is None:
+            qkv = self._project_rotate_store(x, ctx, cache, table)
         out = ops.paged_attention(
             qkv,
             cache.pool,
@@ -102,6 +100,20 @@ class PagedAttention(Mixer):
             if handed_on is not None:
                 return handed_on
         return ops.linear(out, self.w_out)
+
+    def _project_rotate_store(self, x, ctx, cache, table):
+        H, KV, D = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = ops.linear(x, self.w_in)
+        if self.position is not None and table is None:
+            # a position encoding without a table: let it rewrite q and k, then store unrotated
+            n = qkv.shape[0]
+            q = qkv[:, : H * D].unflatten(1, (H, D))
+            k = qkv[:, H * D : (H + KV) * D].unflatten(1, (KV, D)) if self.own_kv else qkv.new_empty((n, 0, D))
+            self.position.apply(q, k, ctx.positions)
+        ops.rope_kv_write(
+            qkv, ctx.positions, table, cache.slot_map, cache.pool, H, KV, D, write_kv=self.own_kv
+        )
+        return qkv
 
 
 register_part("mixer", "attention", PagedAttention)

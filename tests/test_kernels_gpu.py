@@ -138,6 +138,32 @@ def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
         torch.testing.assert_close(got_act.double(), want_act, atol=bound, rtol=3e-2)
 
 
+@pytest.mark.parametrize("m,H,KV,D,hidden,page_size,rotate", [(1, 32, 4, 64, 2048, 16, True), (8, 4, 2, 16, 64, 8, True),
+                                                            (16, 3, 1, 32, 96, 4, True), (5, 6, 3, 128, 72, 16, False),
+                                                            (2, 5, 0, 48, 40, 1, True)])
+def test_linear_qkv_rope_fused_for_few_rows(m, H, KV, D, hidden, page_size, rotate):
+    """Projection, rotation and cache write in one kernel against the three done plainly."""
+    o = ops()
+    x = rnd(m, hidden, dtype=torch.bfloat16, seed=51)
+    w = rnd((H + 2 * KV) * D, hidden, dtype=torch.bfloat16, seed=52, std=0.1)
+    cos, sin = plain_llama.rope_cos_sin(torch.arange(200), D, 1234.0)
+    table = torch.cat((cos[:, : D // 2], sin[:, : D // 2]), dim=-1).contiguous().to(DEV) if rotate else None
+    positions = torch.randint(0, 200, (m,), generator=torch.Generator().manual_seed(3)).to(torch.int32).to(DEV)
+    pages = 12
+    slot_map = torch.randperm(pages * page_size, generator=torch.Generator().manual_seed(4))[:m].to(torch.int32).to(DEV)
+    pool_a = torch.zeros(pages, 2, max(KV, 1), page_size, D, dtype=torch.bfloat16, device=DEV) if KV else None
+    pool_b = pool_a.clone() if KV else None
+    got_q = o.linear_qkv_rope(x, w, positions, table, slot_map if KV else None, pool_a, H, KV, D, write_kv=KV > 0)
+    assert got_q is not None
+    qkv = plain_ops.linear(x, w, out_dtype=torch.float32)  # the plain chain keeps 32 bits until the stores
+    plain_ops.rope_kv_write(qkv, positions, table, slot_map if KV else None, pool_b, H, KV, D, write_kv=KV > 0)
+    scale = float(qkv.abs().max())
+    torch.testing.assert_close(got_q.float(), qkv[:, : H * D], atol=1e-2 * scale, rtol=1.6e-2)
+    if KV:
+        torch.testing.assert_close(pool_a.float(), pool_b.float(), atol=1e-2 * scale, rtol=1.6e-2)
+        assert float(pool_a.float().abs().sum()) > 0
+
+
 def make_cache(requests, KV, D, page_size, dtype, seed=0, shuffle=True):
     """A pool with the keys and values of ``requests`` (list of context lengths) on shuffled pages."""
     pages_of = [-(-n // page_size) for n in requests]
