@@ -76,7 +76,7 @@ struct AttnParams {
 };
 
 // Stages of the key/value ring: four where shared memory allows, three for the largest tiles.
-__host__ __device__ constexpr int stages_of(int D, int key_warps) { return key_warps > 1 ? (D <= 64 ? 4 : 3) : (D <= 64 ? 4 : 3); }
+__host__ __device__ constexpr int stages_of(int D, int key_warps) { return D <= 64 ? 4 : 3; }
 
 // D: head size.  ROW_WARPS x KEY_WARPS = 4 warps.  BN: keys per warp and tile.
 template <int D, int ROW_WARPS, int KEY_WARPS, int BN>

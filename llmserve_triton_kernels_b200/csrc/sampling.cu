@@ -65,7 +65,26 @@ __device__ MaxIdx block_argmax(MaxIdx mine, MaxIdx* scratch) {
 
 __device__ MaxIdx row_argmax(const float* row, int vocab, MaxIdx* scratch) {
     MaxIdx mine{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mine = better(mine, MaxIdx{row[i], i});
+    if ((vocab & 3) == 0 && ((uintptr_t)row & 15) == 0) {
+        // four loads of 16 bytes in flight per thread: the scan is bound by load latency, not by comparisons
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int n4 = vocab >> 2, step = blockDim.x;
+        for (int i = threadIdx.x; i < n4; i += 4 * step) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = i + u * step < n4 ? row4[i + u * step] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int base = (i + u * step) * 4;
+                mine = better(mine, MaxIdx{v[u].x, base});
+                mine = better(mine, MaxIdx{v[u].y, base + 1});
+                mine = better(mine, MaxIdx{v[u].z, base + 2});
+                mine = better(mine, MaxIdx{v[u].w, base + 3});
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) mine = better(mine, MaxIdx{row[i], i});
+    }
     return block_argmax(mine, scratch);
 }
 
