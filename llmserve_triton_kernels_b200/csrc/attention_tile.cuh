@@ -1,0 +1,403 @@
+// The tensor-core attention over the paged cache as a device function: one CTA of 4 warps computes
+// one (request, key/value head, row tile, split of the keys).  Shared by the attention kernel
+// (attention_mma.cu) and the kernel that runs a whole decode step (decode_fused.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace attn {
+
+
+constexpr int THREADS = 128;
+constexpr int SMALL_ROWS = 16;  // requests with at most this many rows go to the KEYS shape
+
+// The 128 threads that compute a tile meet here.  A named barrier, not __syncthreads: inside the fused decode
+// kernel the tile is computed by four of the CTA's eight warps.
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 9, 128;\n" ::: "memory"); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {  // 2^x by the special-function unit: exp2(-inf) = 0, relative error about 2^-22
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct AttnParams {
+    const __nv_bfloat16* q;
+    int q_stride;
+    __nv_bfloat16* out;
+    int out_stride;
+    const __nv_bfloat16* pool;
+    const int* page_table;
+    int table_width;
+    const int* cu_tokens;
+    const int* ctx_lens;
+    int H, KV, G, page_size, window;
+    int tiles_per_request;  // gridDim.z = requests * tiles_per_request
+    float scale_log2;       // softmax scale * log2(e)
+    int splits;             // gridDim.x
+    float* part_o;          // [tokens, H, splits, D], relative to the split's max
+    float* part_ml;         // [tokens, H, splits, 2]: (max in the base-2 domain, sum)
+    int* counters;          // [requests * KV] zeros: how many splits of a (request, kv head) have finished
+};
+
+// Stages of the key/value ring: four where shared memory allows, three for the largest tiles.
+__host__ __device__ constexpr int stages_of(int D, int key_warps) { return D <= 64 ? 4 : 3; }
+
+// D: head size.  ROW_WARPS x KEY_WARPS = 4 warps.  BN: keys per warp and tile.
+template <int D, int ROW_WARPS, int KEY_WARPS, int BN, int STAGES = stages_of(D, KEY_WARPS)>
+__device__ __forceinline__ void attention_tile(const AttnParams& p, int split, int kvh, int r, int tile, unsigned char* smem_raw,
+                                               bool use_pdl) {
+    constexpr int BM = 16 * ROW_WARPS;   // rows of the CTA
+    constexpr int BNC = BN * KEY_WARPS;  // keys of one CTA tile
+    constexpr int CHUNKS = D / 8;        // 16-byte pieces of a key row
+    constexpr int SWZ = CHUNKS >= 8 ? 7 : CHUNKS - 1;
+    constexpr int KSTEPS = D / 16;
+    constexpr int NT_S = BN / 8;  // 8-key tiles of a warp's scores
+    constexpr int NT_O = D / 8;   // 8-wide tiles of the output
+    constexpr bool SMALL = KEY_WARPS > 1;
+    // STAGES tiles in flight: a tile's latency is a page lookup plus a trip to HBM
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][BNC][D]
+    __nv_bfloat16* v_s = k_s + STAGES * BNC * D;                      // [STAGES][BNC][D]
+
+    const int q_begin = p.cu_tokens[r], q_len = p.cu_tokens[r + 1] - q_begin;
+    const int G = p.G, rows_total = q_len * G;
+    if ((rows_total <= SMALL_ROWS) != SMALL) return;
+    const int row0 = tile * BM;
+    if (row0 >= rows_total) return;
+    const int ctx = p.ctx_lens[r], pos0 = ctx - q_len;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row_warp = warp % ROW_WARPS, key_warp = warp / ROW_WARPS;
+    const int qr = lane >> 2, qc = lane & 3;
+
+    // the two rows this thread holds pieces of
+    int row_tok[2], row_pos[2], row_lo[2], row_head[2];
+    bool row_ok[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int rho = row0 + row_warp * 16 + qr + 8 * i;
+        row_ok[i] = rho < rows_total;
+        const int tok = row_ok[i] ? rho / G : 0;
+        row_tok[i] = q_begin + tok;
+        row_head[i] = kvh * G + (row_ok[i] ? rho - tok * G : 0);
+        row_pos[i] = row_ok[i] ? pos0 + tok : -1;
+        row_lo[i] = p.window > 0 ? max(0, row_pos[i] - p.window + 1) : 0;
+    }
+    // keys this CTA needs: from the window's start of its first token to its last token's position
+    const int tok_first = row0 / G, tok_last = (min(rows_total, row0 + BM) - 1) / G;
+    const int key_hi = pos0 + tok_last;
+    const int key_lo = p.window > 0 ? max(0, pos0 + tok_first - p.window + 1) : 0;
+    // a key tile needs no mask if every row of the CTA sees all of it (rows past the end are never written)
+    const int tile_pos_min = pos0 + tok_first;
+    const int tile_lo_max = p.window > 0 ? max(0, pos0 + tok_last - p.window + 1) : 0;
+    const int tile_first = key_lo / BNC, tile_last = key_hi / BNC;
+    // a split takes at least two tiles, so short contexts use few splits however many the grid has; splits
+    // beyond the last active one do nothing
+    const int n_tiles = tile_last - tile_first + 1;
+    const int per_split = max(SMALL ? 2 : 1, (n_tiles + p.splits - 1) / p.splits);
+    const int active_splits = (n_tiles + per_split - 1) / per_split;
+    const int t_begin = tile_first + split * per_split;
+    const int t_end = min(tile_last + 1, t_begin + per_split);
+    if (SMALL && split >= active_splits) return;
+
+    // up to here only the step's descriptor arrays were read, which no kernel writes; the queries and the
+    // cache come from the kernels before this one
+    if (use_pdl) {
+        pdl_trigger();
+        pdl_wait();
+    }
+
+    // query fragments, straight from global memory
+    unsigned qa[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int which = i & 1;
+            const __nv_bfloat16* src = p.q + (size_t)row_tok[which] * p.q_stride + (size_t)row_head[which] * D +
+                                       ks * 16 + (i >> 1) * 8 + qc * 2;
+            qa[ks][i] = row_ok[which] ? *reinterpret_cast<const unsigned*>(src) : 0u;
+        }
+
+    const int* table = p.page_table + (size_t)r * p.table_width;
+    const size_t head_stride = (size_t)p.page_size * D;
+
+    // one key row (or a fixed part of it) per thread: one page lookup and a few 16-byte copies per tile
+    constexpr int TPK = THREADS / BNC;        // threads per key
+    constexpr int CPT = CHUNKS / TPK;         // 16-byte pieces per thread
+    static_assert(THREADS % BNC == 0 && CHUNKS % TPK == 0, "a key row must split evenly over its threads");
+    const int load_key = tid / TPK, load_c0 = (tid % TPK) * CPT;
+    auto load_tile = [&](int t, int stage) {
+        const int j = t * BNC + load_key;
+        const bool valid = j >= key_lo && j <= key_hi;
+        size_t off = 0;
+        if (valid) {
+            const int lp = j / p.page_size;
+            off = ((size_t)(table[lp] * 2) * p.KV + kvh) * head_stride + (size_t)(j - lp * p.page_size) * D;
+        }
+        const int dst_row = (stage * BNC + load_key) * D;
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int c = load_c0 + i;
+            const int dst = dst_row + ((c ^ (load_key & SWZ)) * 8);
+            cp_async16(k_s + dst, p.pool + off + c * 8, valid);
+            cp_async16(v_s + dst, p.pool + off + (size_t)p.KV * head_stride + c * 8, valid);
+        }
+    };
+
+    float oacc[NT_O][4];
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    // one commit group per tile, empty past the end, so that the wait below counts tiles
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        if (t_begin + i < t_end) load_tile(t_begin + i, i);
+        cp_async_commit();
+    }
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) % STAGES;
+        cp_async_wait<STAGES - 2>();  // tile t has landed (this thread's copies) ...
+        cta_sync();              // ... everyone's; and the stage refilled next is no longer read
+        if (t + STAGES - 1 < t_end) load_tile(t + STAGES - 1, (t - t_begin + STAGES - 1) % STAGES);
+        cp_async_commit();
+        const __nv_bfloat16* ks_tile = k_s + (stage * BNC + key_warp * BN) * D;
+        const __nv_bfloat16* vs_tile = v_s + (stage * BNC + key_warp * BN) * D;
+        const int key_base = t * BNC + key_warp * BN;
+
+        // scores: S = Q K^T
+        float sacc[NT_S][4];
+#pragma unroll
+        for (int i = 0; i < NT_S; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[i][e] = 0.f;
+        const int mi = lane >> 3, ri = lane & 7;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < NT_S / 2; ++np) {
+                const int key = np * 16 + (mi >> 1) * 8 + ri;  // row of the tile; key_warp*BN is a multiple of 8
+                const int chunk = ks * 2 + (mi & 1);
+                unsigned b[4];
+                ldmatrix_x4(b, ks_tile + key * D + ((chunk ^ (key & SWZ)) * 8));
+                mma_bf16(sacc[2 * np], qa[ks], b[0], b[1]);
+                mma_bf16(sacc[2 * np + 1], qa[ks], b[2], b[3]);
+            }
+        }
+        // mask (only in tiles that some row does not see whole), running max and sum
+        float mx[2] = {-INFINITY, -INFINITY};
+        const bool whole = key_base + BN - 1 <= tile_pos_min && key_base >= tile_lo_max;
+        if (whole) {
+#pragma unroll
+            for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    sacc[nt][e] *= p.scale_log2;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], sacc[nt][e]);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int j = key_base + nt * 8 + qc * 2 + (e & 1);
+                    const bool visible = j <= row_pos[i] && j >= row_lo[i];
+                    sacc[nt][e] = visible ? sacc[nt][e] * p.scale_log2 : -INFINITY;
+                    mx[i] = fmaxf(mx[i], sacc[nt][e]);
+                }
+        }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            m_use[i] = m_new == -INFINITY ? 0.f : m_new;
+            alpha[i] = fast_exp2(m_run[i] - m_use[i]);
+            m_run[i] = m_new;
+            l_run[i] *= alpha[i];
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = fast_exp2(sacc[nt][e] - m_use[e >> 1]);
+                sacc[nt][e] = pv;
+                l_run[e >> 1] += pv;
+            }
+#pragma unroll
+        for (int nt = 0; nt < NT_O; ++nt) {
+            oacc[nt][0] *= alpha[0];
+            oacc[nt][1] *= alpha[0];
+            oacc[nt][2] *= alpha[1];
+            oacc[nt][3] *= alpha[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+            unsigned pa[4];
+            pa[0] = pack_bf16(sacc[2 * kk][0], sacc[2 * kk][1]);
+            pa[1] = pack_bf16(sacc[2 * kk][2], sacc[2 * kk][3]);
+            pa[2] = pack_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+            pa[3] = pack_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < NT_O / 2; ++dp) {
+                const int key = kk * 16 + (mi & 1) * 8 + ri;
+                const int chunk = dp * 2 + (mi >> 1);
+                unsigned b[4];
+                ldmatrix_x4_trans(b, vs_tile + key * D + ((chunk ^ (key & SWZ)) * 8));
+                mma_bf16(oacc[2 * dp], pa, b[0], b[1]);
+                mma_bf16(oacc[2 * dp + 1], pa, b[2], b[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    cta_sync();  // the ring is free (the small shape merges its warps through it)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+
+    if constexpr (!SMALL) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!row_ok[i]) continue;
+            if (p.splits == 1) {
+                const float inv = 1.f / l_run[i];
+                __nv_bfloat16* dst = p.out + (size_t)row_tok[i] * p.out_stride + (size_t)row_head[i] * D + qc * 2;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt)
+                    *reinterpret_cast<unsigned*>(dst + nt * 8) = pack_bf16(oacc[nt][2 * i] * inv, oacc[nt][2 * i + 1] * inv);
+            } else {
+                const size_t slot = ((size_t)row_tok[i] * p.H + row_head[i]) * p.splits + split;
+                float* dst = p.part_o + slot * D + qc * 2;
+#pragma unroll
+                for (int nt = 0; nt < NT_O; ++nt) {
+                    dst[nt * 8] = oacc[nt][2 * i];
+                    dst[nt * 8 + 1] = oacc[nt][2 * i + 1];
+                }
+                if (qc == 0) {
+                    p.part_ml[slot * 2] = m_run[i];
+                    p.part_ml[slot * 2 + 1] = l_run[i];
+                }
+            }
+        }
+    } else {
+        // merge the four warps' shares of the keys through shared memory (the key tiles are done with)
+        float* o_sm = reinterpret_cast<float*>(smem_raw);    // [KEY_WARPS][16][D]
+        float* ml_sm = o_sm + KEY_WARPS * 16 * D;            // [KEY_WARPS][16][2]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = qr + 8 * i;
+            float* dst = o_sm + (key_warp * 16 + row) * D + qc * 2;
+#pragma unroll
+            for (int nt = 0; nt < NT_O; ++nt) {
+                dst[nt * 8] = oacc[nt][2 * i];
+                dst[nt * 8 + 1] = oacc[nt][2 * i + 1];
+            }
+            if (qc == 0) {
+                ml_sm[(key_warp * 16 + row) * 2] = m_run[i];
+                ml_sm[(key_warp * 16 + row) * 2 + 1] = l_run[i];
+            }
+        }
+        cta_sync();
+        for (int idx = tid; idx < 16 * D; idx += THREADS) {
+            const int row = idx / D, d = idx - row * D;
+            if (row >= rows_total) continue;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < KEY_WARPS; ++w) m = fmaxf(m, ml_sm[(w * 16 + row) * 2]);
+            const float m_use = m == -INFINITY ? 0.f : m;
+            float o = 0.f, l = 0.f;
+#pragma unroll
+            for (int w = 0; w < KEY_WARPS; ++w) {
+                const float f = exp2f(ml_sm[(w * 16 + row) * 2] - m_use);
+                o += o_sm[(w * 16 + row) * D + d] * f;
+                l += ml_sm[(w * 16 + row) * 2 + 1] * f;
+            }
+            const int tok = row / G, head = kvh * G + (row - tok * G);
+            if (active_splits == 1) {
+                p.out[(size_t)(q_begin + tok) * p.out_stride + (size_t)head * D + d] = __float2bfloat16_rn(o / l);
+            } else {
+                const size_t slot = ((size_t)(q_begin + tok) * p.H + head) * p.splits + split;
+                p.part_o[slot * D + d] = o;
+                if (d == 0) {
+                    p.part_ml[slot * 2] = m;
+                    p.part_ml[slot * 2 + 1] = l;
+                }
+            }
+        }
+        if (active_splits > 1) {
+            // the split that finishes last merges all of them: no second launch
+            __shared__ int ticket;
+            __threadfence();
+            cta_sync();
+            if (tid == 0) ticket = atomicAdd(&p.counters[r * p.KV + kvh], 1);
+            cta_sync();
+            if (ticket != active_splits - 1) return;
+            __threadfence();
+            // factors of every (row, split) first, side by side, then the weighted sums
+            float* f_sm = reinterpret_cast<float*>(smem_raw);  // [rows][splits] factor, then [rows] 1 / sum
+            float* inv_sm = f_sm + SMALL_ROWS * 32;
+            for (int row = tid; row < rows_total; row += THREADS) {
+                const int tok = row / G, head = kvh * G + (row - tok * G);
+                const size_t slot = ((size_t)(q_begin + tok) * p.H + head) * p.splits;
+                float m = -INFINITY;
+                for (int s2 = 0; s2 < active_splits; ++s2) m = fmaxf(m, __ldcg(&p.part_ml[(slot + s2) * 2]));
+                const float m_use = m == -INFINITY ? 0.f : m;
+                float l = 0.f;
+                for (int s2 = 0; s2 < active_splits; ++s2) {
+                    const float f = exp2f(__ldcg(&p.part_ml[(slot + s2) * 2]) - m_use);
+                    f_sm[row * 32 + s2] = f;
+                    l += __ldcg(&p.part_ml[(slot + s2) * 2 + 1]) * f;
+                }
+                inv_sm[row] = 1.f / l;
+            }
+            cta_sync();
+            for (int idx = tid; idx < rows_total * D; idx += THREADS) {
+                const int row = idx / D, d = idx - row * D;
+                const int tok = row / G, head = kvh * G + (row - tok * G);
+                const size_t slot = ((size_t)(q_begin + tok) * p.H + head) * p.splits;
+                float o = 0.f;
+#pragma unroll 4
+                for (int s2 = 0; s2 < active_splits; ++s2) o += __ldcg(&p.part_o[(slot + s2) * D + d]) * f_sm[row * 32 + s2];
+                p.out[(size_t)(q_begin + tok) * p.out_stride + (size_t)head * D + d] = __float2bfloat16_rn(o * inv_sm[row]);
+            }
+            if (tid == 0) p.counters[r * p.KV + kvh] = 0;  // ready for the next launch
+        }
+    }
+}
+
+}  // namespace attn

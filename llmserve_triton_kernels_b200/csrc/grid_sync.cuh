@@ -7,7 +7,7 @@
 
 namespace grid_sync {
 
-constexpr int SPIN_LIMIT = 1 << 24;  // polls of the counter before giving up (seconds, not microseconds)
+constexpr int SPIN_LIMIT = 1 << 22;  // polls of the counter before giving up (on the order of a second)
 
 // `counter` starts at zero for the launch and only grows; `arrivals_so_far` is gridDim.x times the number of
 // barriers this CTA has passed before.  Returns false if the wait gave up.

@@ -43,6 +43,9 @@ class StepContext:
     host_state_slots: list[int]
     max_query_len: int
     max_context_len: int
+    # True for the fixed buffers of a captured decode step: one token per request, every row's logits wanted,
+    # the same addresses at every replay (a model may then build a plan for the step once and keep it)
+    static_decode: bool = False
 
 
 def pack_step(entries: list[StepEntry], lengths: list[int], state_slots: np.ndarray, group_arrays, device):

@@ -51,7 +51,7 @@ class DecodeGraph:
             num_tokens=R, num_requests=R, num_logits=R,
             token_ids=d(0), positions=d(1), token_request=d(2), cu_tokens=d(3), context_lens=d(4), logit_rows=d(5),
             state_slots=d(6), host_cu_tokens=list(range(R + 1)), host_context_lens=None, host_state_slots=None,
-            max_query_len=1, max_context_len=model.plan.max_positions,
+            max_query_len=1, max_context_len=model.plan.max_positions, static_decode=True,
         )
         group_tensors = []
         for g, w in enumerate(self.widths):

@@ -104,6 +104,39 @@ class Model:
             getattr(b, "graph_safe", False) for b in self.blocks
         ) and getattr(self.final_norm, "graph_safe", False)
 
+    def _fused_decode(self, ctx, caches):
+        """A captured decode step of few tokens through the one-kernel path, when every layer of the
+        order is of the kind that kernel runs and all agree in their sizes; else None."""
+        plan = getattr(ctx, "_fused_plan", None)
+        if plan is None:
+            plan = self._make_fused_plan(ctx, caches) or False
+            ctx._fused_plan = plan
+        return ops.fused_decode_run(plan) if plan else None
+
+    def _make_fused_plan(self, ctx, caches):
+        order = self.plan.schedule
+        if any(run.cache_of is not None for run in order) or getattr(self.final_norm, "fused_params", None) is None:
+            return None
+        specs = []
+        for i, run in enumerate(order):
+            spec = getattr(self.blocks[run.layer], "fused_decode_spec", lambda c: None)(caches[i])
+            if spec is None:
+                return None
+            specs.append(spec)
+        first = specs[0]
+        if any(s["dims"] != first["dims"] or s["rotary_table"] is not first["rotary_table"] or s["page_size"] != first["page_size"] for s in specs):
+            return None
+        layers = []
+        for i, s in enumerate(specs):
+            nxt = specs[i + 1]["mixer_norm"] if i + 1 < len(specs) else self.final_norm.fused_params()
+            layers.append({**s, "next_norm": nxt})
+        hidden, heads, kv_heads, head_dim, inter = first["dims"]
+        return ops.fused_decode_plan(
+            ctx=ctx, hidden=hidden, num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, inter=inter,
+            vocab=self.plan.vocab_size, page_size=first["page_size"], embedding=self.embedding, first_norm=first["mixer_norm"],
+            rotary_table=first["rotary_table"], layers=layers, head=self.head,
+        )
+
     # ------------------------------------------------------------------ caches
     def cache_specs(self) -> list[PagedKVSpec | StateSpec | None]:
         """For each entry of the order: what its mixer keeps, or None if it keeps nothing of its
@@ -117,6 +150,10 @@ class Model:
     def forward(self, ctx, caches) -> torch.Tensor:
         """Run the tokens of ``ctx`` through every entry of the order; ``caches[i]`` is the view
         of entry i's cache.  Returns 32-bit logits ``[len(ctx.logit_rows), vocab]``."""
+        if getattr(ctx, "static_decode", False) and self.dtype == torch.bfloat16:
+            logits = self._fused_decode(ctx, caches)
+            if logits is not None:
+                return logits
         resid = ops.embed(ctx.token_ids, self.embedding)
         pending = None
         order = self.plan.schedule

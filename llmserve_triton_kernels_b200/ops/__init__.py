@@ -28,6 +28,9 @@ _SIGNATURES = {
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_ulonglong, _vp],
     "llm_linear_decode_qkv": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
+    "llm_fused_layer_fill": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _f, _vp, _vp, _i, _vp, _i, _f],
+    "llm_decode_fused": [_i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                         _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_gemm_tcgen05": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_attention_generic": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
@@ -57,6 +60,7 @@ def library():
                 fn = getattr(lib, name)
                 fn.argtypes = args
                 fn.restype = ctypes.c_int
+            lib.llm_fused_layer_bytes.restype = ctypes.c_int
             lib.llm_error_string.argtypes = [ctypes.c_int]
             lib.llm_error_string.restype = ctypes.c_char_p
             _lib = lib
@@ -369,6 +373,90 @@ def linear_qkv_rope(
         return None
     _check(code, "linear_qkv_rope")
     return q
+
+
+# The whole decode step in one cooperative kernel (csrc/decode_fused.cu).  Correct and tested, but measured slower
+# than the step kernel by kernel with programmatic dependent launch (1.50 ms against 1.22 ms per step of 8 requests
+# on a 1.1B model): each of its 111 phases pays a grid barrier and a chain of dependent trips to L2.  Off by default.
+_FUSED_DECODE_ENABLED = False
+_FUSED_DECODE_MAX_TOKENS = 8
+_FUSED_DECODE_HEAD_DIMS = (64, 128)
+
+
+class FusedDecodePlan:
+    """Everything the one-kernel decode step needs, made once per captured decode shape: the
+    layers' records (tensor maps of the four matrices, norm weights, cache plane, page table and
+    slot map of the step's static buffers) on the device, and the scratch tensors."""
+
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def fused_decode_plan(*, ctx, hidden, num_heads, num_kv_heads, head_dim, inter, vocab, page_size, embedding, first_norm,
+                      rotary_table, layers: list[dict], head) -> "FusedDecodePlan | None":
+    """A plan for :func:`fused_decode_run`, or None when the kernel does not take these sizes.
+    ``layers``: per layer ``w_in, w_out, w_gate_up, w_down`` (bfloat16), ``ff_norm`` and
+    ``next_norm`` as ``(weight, eps)``, ``pool``, ``page_table``, ``slot_map``, ``window``, ``scale``."""
+    m = ctx.num_tokens
+    if not _FUSED_DECODE_ENABLED:
+        return None
+    if m > _FUSED_DECODE_MAX_TOKENS or head_dim not in _FUSED_DECODE_HEAD_DIMS or embedding.dtype != torch.bfloat16:
+        return None
+    if hidden % 8 or inter % 8 or num_heads % num_kv_heads or num_heads // num_kv_heads > 16:
+        return None
+    lib = library()
+    dev = embedding.device
+    record = lib.llm_fused_layer_bytes()
+    host = torch.zeros(len(layers) * record + 64, dtype=torch.uint8).pin_memory()
+    base = (-host.data_ptr()) % 64
+    for i, L in enumerate(layers):
+        pt = L["page_table"]
+        code = lib.llm_fused_layer_fill(
+            host.data_ptr() + base + i * record, _ptr(L["w_in"]), _ptr(L["w_out"]), _ptr(L["w_gate_up"]), _ptr(L["w_down"]),
+            hidden, num_heads, num_kv_heads, head_dim, inter, _ptr(L["ff_norm"][0]), float(L["ff_norm"][1]),
+            _ptr(L["next_norm"][0]), float(L["next_norm"][1]), _ptr(L["pool"]), _ptr(pt), pt.shape[1], _ptr(L["slot_map"]),
+            int(L["window"] or 0), float(L["scale"]),
+        )
+        if code != 0:
+            return None
+    device_records = torch.empty(len(layers) * record + 64, dtype=torch.uint8, device=dev)
+    dbase = (-device_records.data_ptr()) % 64
+    device_records[dbase : dbase + len(layers) * record].copy_(host[base : base + len(layers) * record])
+    longest = ctx.max_context_len
+    splits = max(1, min(-(-longest // _SMALL_TILE_KEYS), -(-_SM_COUNT // (m * num_kv_heads)), 32))
+    f32 = dict(dtype=torch.float32, device=dev)
+    bf16 = dict(dtype=torch.bfloat16, device=dev)
+    plan = FusedDecodePlan(
+        ctx=ctx, m=m, hidden=hidden, H=num_heads, KV=num_kv_heads, D=head_dim, inter=inter, vocab=vocab, page_size=page_size,
+        n_layers=len(layers), embedding=embedding, first_norm=first_norm, rotary_table=rotary_table, head=head,
+        records=device_records, records_ptr=device_records.data_ptr() + dbase, keep=layers, splits=splits,
+        resid=torch.empty((m, hidden), **f32), xw=torch.empty((m, hidden), **bf16),
+        ss=torch.empty((-(-hidden // 16), m), **f32), q=torch.empty((m, num_heads * head_dim), **bf16),
+        attn=torch.empty((m, num_heads * head_dim), **bf16), act=torch.empty((m, inter), **bf16),
+        part_o=torch.empty((m * num_heads * splits * head_dim,), **f32), part_ml=torch.empty((m * num_heads * splits * 2,), **f32),
+        counters=torch.zeros((m * num_kv_heads,), dtype=torch.int32, device=dev),
+        barrier=torch.zeros((1,), dtype=torch.int32, device=dev), logits=torch.empty((m, vocab), **f32),
+    )
+    torch.cuda.synchronize(dev)  # the records are on the device before the pinned buffer goes away
+    return plan
+
+
+def fused_decode_run(plan: "FusedDecodePlan") -> torch.Tensor | None:
+    """One decode step in one kernel; returns the plan's logits tensor ``[tokens, vocab]``
+    (overwritten by the next run), or None if the kernel refused."""
+    p, ctx = plan, plan.ctx
+    code = _launch(
+        "llm_decode_fused", p.m, p.hidden, p.H, p.KV, p.D, p.inter, p.vocab, p.page_size, p.n_layers, _ptr(ctx.token_ids),
+        _ptr(p.embedding), _ptr(p.first_norm[0]), float(p.first_norm[1]), _ptr(ctx.positions), _ptr(p.rotary_table),
+        p.rotary_table.shape[0], _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), _ptr(p.resid), _ptr(p.xw), _ptr(p.ss), _ptr(p.q),
+        _ptr(p.attn), _ptr(p.act), p.splits, _ptr(p.part_o), _ptr(p.part_ml), _ptr(p.counters), p.records_ptr, _ptr(p.head),
+        _ptr(p.logits), _ptr(p.barrier), _error_flag_ptr(), _stream(),
+    )
+    if code == 10002:
+        add_launches(-1)
+        return None
+    _check(code, "fused decode step")
+    return p.logits
 
 
 def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:

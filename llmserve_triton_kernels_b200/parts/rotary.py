@@ -15,6 +15,9 @@ from .. import ops
 from .base import PositionEncoding, register_part
 
 
+_TABLES: dict = {}
+
+
 class RotaryEmbedding(PositionEncoding):
     graph_safe = True
 
@@ -27,10 +30,14 @@ class RotaryEmbedding(PositionEncoding):
         self.rotary_table: torch.Tensor | None = None  # [max_positions, head_dim]: cos | sin halves
 
     def bind(self, tensors, dtype, device) -> None:
-        exponent = torch.arange(0, self.head_dim, 2, dtype=torch.float32) / self.head_dim
-        inv_freq = 1.0 / (self.theta**exponent)
-        angles = torch.arange(self.max_positions, dtype=torch.float32)[:, None] * inv_freq
-        self.rotary_table = torch.cat((angles.cos(), angles.sin()), dim=-1).contiguous().to(device)
+        key = (self.head_dim, self.theta, self.max_positions, str(torch.device(device)))
+        table = _TABLES.get(key)
+        if table is None:  # layers with the same constants share one table
+            exponent = torch.arange(0, self.head_dim, 2, dtype=torch.float32) / self.head_dim
+            inv_freq = 1.0 / (self.theta**exponent)
+            angles = torch.arange(self.max_positions, dtype=torch.float32)[:, None] * inv_freq
+            table = _TABLES[key] = torch.cat((angles.cos(), angles.sin()), dim=-1).contiguous().to(device)
+        self.rotary_table = table
 
     def apply(self, q, k, positions) -> None:
         ops.rope_inplace(q, positions, self.rotary_table)

@@ -76,7 +76,7 @@ def test_replay_host_logic_with_plain_operations(name, model_folder, tmp_path, p
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_replay_on_gpu(name, dtype, model_folder, tmp_path):
     cfg, seed, _, _ = tiny_configs.TINY[name]
     storage = torch.float32 if dtype == "float32" else torch.bfloat16

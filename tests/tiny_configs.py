@@ -39,9 +39,23 @@ TINY_B = {
 }
 TINY_B_SEED, TINY_B_PROMPT_SEED, TINY_B_PROMPT_LENS = 2, 3, (1, 7, 23, 40)
 
+# Head sizes 64 and 128: the sizes the one-kernel decode step takes (the two above go kernel by kernel)
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 320, "hidden_size": 128, "intermediate_size": 200,
+    "num_hidden_layers": 2, "num_attention_heads": 2, "num_key_value_heads": 1, "max_position_embeddings": 192,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 288, "hidden_size": 384, "intermediate_size": 264,
+    "num_hidden_layers": 3, "num_attention_heads": 3, "num_key_value_heads": 3, "max_position_embeddings": 160,
+    "rope_theta": 50000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+
 TINY = {
     "a": (TINY_A, TINY_A_SEED, TINY_A_PROMPT_SEED, TINY_A_PROMPT_LENS),
     "b": (TINY_B, TINY_B_SEED, TINY_B_PROMPT_SEED, TINY_B_PROMPT_LENS),
+    "c": (TINY_C, 4, 5, (3, 9, 21)),
+    "d": (TINY_D, 6, 7, (2, 14, 30)),
 }
 
 
