@@ -33,7 +33,7 @@ using namespace lin;
 
 // One product: MT 8-token tiles (M <= 8 MT), one CTA per SM (see linear_stream.cuh for how it streams).
 template <int MT, int MODE, typename TO>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [WARPS][SLOTS][SLOT_ELEMS]
