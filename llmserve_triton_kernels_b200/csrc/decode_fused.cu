@@ -59,6 +59,8 @@ struct FusedParams {
     float* logits;         // [M, vocab]
     unsigned* barrier;
     int* error_flag;
+    unsigned long long* timeline;  // [CTAs, timeline_len, 2] (global timer, SM clock) at each barrier's two sides, or null
+    int timeline_len;
 };
 
 struct Smem {
@@ -109,12 +111,23 @@ __global__ void __launch_bounds__(THREADS) decode_fused_kernel(const FusedParams
     unsigned base = 0, arrivals = 0;
     const int M = p.M, hidden = p.hidden;
     bool ok = true;
+    int stamps = 0;
+    auto stamp = [&]() {
+        if (p.timeline && tid == 0 && stamps < p.timeline_len) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+            p.timeline[((size_t)blockIdx.x * p.timeline_len + stamps) * 2] = t;
+            p.timeline[((size_t)blockIdx.x * p.timeline_len + stamps++) * 2 + 1] = (unsigned long long)clock64();
+        }
+    };
 #define FUSED_BARRIER()                                                \
     do {                                                               \
+        stamp();                                                       \
         if (!ok || !grid_sync::barrier(p.barrier, arrivals)) {         \
             if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 1); \
             return;                                                    \
         }                                                              \
+        stamp();                                                       \
     } while (0)
 
     // ---- embedding, and the stream in factored normalised form for the first norm (one part per row) ----
@@ -232,9 +245,13 @@ __global__ void __launch_bounds__(THREADS) decode_fused_kernel(const FusedParams
 
     // ---- output matrix ----
     ok = phase_run<MODE_PLAIN, float>(st, head, &head_map, sm, base);
+    stamp();
     if (!ok && tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
 #undef FUSED_BARRIER
 }
+
+unsigned long long* g_timeline = nullptr;  // see llm_decode_fused_timeline
+int g_timeline_len = 0;
 
 int sm_count() {
     static int count = 0;
@@ -295,6 +312,16 @@ LLM_EXPORT int llm_fused_layer_fill(void* dst, const void* w_in, const void* w_o
     return 0;
 }
 
+// For profiling: later launches of llm_decode_fused record, per CTA, the device's global timer when the CTA arrives
+// at and when it leaves each grid-wide barrier (and once at its end), with the SM's cycle counter beside it, into
+// buffer [CTAs, len, 2] (device memory, the
+// caller zeroes it); null switches it off.  A graph keeps the setting it was captured with.
+LLM_EXPORT int llm_decode_fused_timeline(unsigned long long* buffer, int len) {
+    g_timeline = len > 0 ? buffer : nullptr;
+    g_timeline_len = buffer ? len : 0;
+    return 0;
+}
+
 // One decode step of M <= 8 tokens (one per request) through n_layers layers and the output matrix.
 // layers: device copy of the records filled above.  resid, xw, ss, q, attn, act, part_o, part_ml, counters
 // (zeroed), barrier: device scratch of the sizes named in FusedParams.  Returns LLM_ERR_UNSUPPORTED for sizes
@@ -344,6 +371,8 @@ LLM_EXPORT int llm_decode_fused(int M, int hidden, int H, int KV, int D, int int
     p.logits = logits;
     p.barrier = barrier;
     p.error_flag = error_flag;
+    p.timeline = g_timeline;
+    p.timeline_len = g_timeline_len;
     cudaError_t e = cudaMemsetAsync(barrier, 0, sizeof(unsigned), stream);
     if (e != cudaSuccess) return (int)e;
     void* kernel = D == 64 ? (void*)decode_fused_kernel<64> : (void*)decode_fused_kernel<128>;
