@@ -71,21 +71,31 @@ struct Smem {
     unsigned long long (*full)[SLOTS];
 };
 
-// A product in two halves: its first boxes of weights are asked for as soon as the product before it has let
-// go of the ring (before the grid barrier: weights depend on nothing), the rest runs once its input is there.
+// A product in three steps.  phase_plan: its split of the work and what the end of its first tile needs besides the
+// product (nothing that depends on the product's input).  Its boxes of weights are asked for as the product before
+// it frees the ring's slots (weights depend on nothing), and by phase_arm once that product is done.  phase_run: the
+// rest, once the input is there (after the grid barrier).
 template <int MODE>
-__device__ __forceinline__ void phase_begin(StreamState& st, const LinearParams& lp, const CUtensorMap* map, const Smem& sm, unsigned base) {
-    const int warp = threadIdx.x >> 5;
-    stream_begin<MODE>(st, lp, map, sm.ring + (size_t)warp * SLOTS * SLOT_ELEMS, sm.full[warp], base);
+__device__ __forceinline__ void phase_plan(StreamState& st, const LinearParams& lp, unsigned base) {
+    stream_plan<MODE, 1>(st, lp, base);
 }
 
-template <int MODE, typename TO>
-__device__ __forceinline__ bool phase_run(StreamState& st, const LinearParams& lp, const CUtensorMap* map, const Smem& sm, unsigned& base) {
+__device__ __forceinline__ void phase_arm(StreamState& st, const CUtensorMap* map, const Smem& sm) {
+    const int warp = threadIdx.x >> 5;
+    stream_arm(st, map, sm.ring + (size_t)warp * SLOTS * SLOT_ELEMS, sm.full[warp], 0);
+}
+
+template <int MODE, typename TO, typename Stamp>
+__device__ __forceinline__ bool phase_run(StreamState& st, const LinearParams& lp, const CUtensorMap* map, const Smem& sm, unsigned& base,
+                                          Stamp& stamp, StreamState* next, const CUtensorMap* next_map) {
     const int warp = threadIdx.x >> 5;
     stream_stage_x<1>(lp, sm.x_s, sm.row_scale);
     __syncthreads();
-    const bool ok = stream_run<1, MODE, TO>(st, lp, map, sm.ring + (size_t)warp * SLOTS * SLOT_ELEMS, sm.full[warp], sm.red, sm.x_s, sm.row_scale);
+    stamp();
+    const bool ok = stream_run<1, MODE, TO>(st, lp, map, sm.ring + (size_t)warp * SLOTS * SLOT_ELEMS, sm.full[warp], sm.red, sm.x_s,
+                                            sm.row_scale, next, next_map);
     base += (unsigned)st.units;
+    if (next) phase_arm(*next, next_map, sm);  // the ring is this product's no more
     return ok;
 }
 
@@ -153,7 +163,7 @@ __global__ void __launch_bounds__(THREADS) decode_fused_kernel(const FusedParams
     unsigned char* attn_smem = ATTN_BESIDE ? reinterpret_cast<unsigned char*>(sm.red) : smem_raw;
 
     LinearParams qkv = {}, out = {}, gate_up = {}, down = {}, head = {};
-    StreamState st;
+    StreamState st_a, st_b;  // the product that runs and the one that follows it, by turns
     auto set_qkv = [&](int l, int in_parts, float in_eps) {
         const FusedLayer& L = p.layers[l];
         qkv.M = M; qkv.error_flag = p.error_flag;
@@ -164,17 +174,19 @@ __global__ void __launch_bounds__(THREADS) decode_fused_kernel(const FusedParams
         qkv.slot_map = L.slot_map; qkv.pool = L.pool; qkv.H = p.H; qkv.KV = p.KV; qkv.D = p.D; qkv.page_size = p.page_size;
     };
     set_qkv(0, 1, p.first_eps);
-    phase_begin<MODE_QKV>(st, qkv, &p.layers[0].w_in, sm, base);
+    phase_plan<MODE_QKV>(st_a, qkv, base);
+    phase_arm(st_a, &p.layers[0].w_in, sm);
     FUSED_BARRIER();
 
     for (int l = 0; l < p.n_layers; ++l) {
         const FusedLayer& L = p.layers[l];
-        // ---- stacked projection, rotary encoding, cache write ----
-        ok = phase_run<MODE_QKV, __nv_bfloat16>(st, qkv, &L.w_in, sm, base);
+        const bool last = l + 1 == p.n_layers;
+        // ---- stacked projection, rotary encoding, cache write (st_a); the output projection follows (st_b) ----
         out.M = M; out.error_flag = p.error_flag;
         out.x = p.attn; out.ldx = p.H * p.D; out.K = p.H * p.D; out.N = hidden; out.group = L.group_out;
-        out.resid = p.resid; out.norm_w = L.ff_norm_w; out.xw_out = p.xw; out.ss_out = p.ss;
-        if (ATTN_BESIDE) phase_begin<MODE_RESIDUAL>(st, out, &L.w_out, sm, base);
+        out.resid = p.resid; out.norm_w = L.ff_norm_w; out.xw_out = p.xw; out.ss_out = p.ss; out.resid_early = 1;
+        phase_plan<MODE_RESIDUAL>(st_b, out, base + (unsigned)st_a.units);
+        ok = phase_run<MODE_QKV, __nv_bfloat16>(st_a, qkv, &L.w_in, sm, base, stamp, ATTN_BESIDE ? &st_b : nullptr, &L.w_out);
         FUSED_BARRIER();
 
         // ---- attention: items are (request, key/value head, split of the keys) ----
@@ -208,43 +220,46 @@ __global__ void __launch_bounds__(THREADS) decode_fused_kernel(const FusedParams
                 __syncthreads();  // shared memory is free again
             }
         }
-        if (!ATTN_BESIDE) phase_begin<MODE_RESIDUAL>(st, out, &L.w_out, sm, base);
+        if (!ATTN_BESIDE) phase_arm(st_b, &L.w_out, sm);
         FUSED_BARRIER();
 
-        // ---- output projection into the residual stream, handed on for the feed-forward's norm ----
-        ok = phase_run<MODE_RESIDUAL, __nv_bfloat16>(st, out, &L.w_out, sm, base);
+        // ---- output projection into the residual stream (st_b); gate and up follow (st_a) ----
         gate_up.M = M; gate_up.error_flag = p.error_flag;
         gate_up.x = p.xw; gate_up.ldx = hidden; gate_up.K = hidden; gate_up.N = p.inter;
         gate_up.in_ss = p.ss; gate_up.in_parts = hidden_parts; gate_up.in_eps = L.ff_eps;
         gate_up.out = p.act; gate_up.ldo = p.inter; gate_up.up_offset = p.inter; gate_up.group = L.group_gate_up;
-        phase_begin<MODE_SWIGLU>(st, gate_up, &L.w_gate_up, sm, base);
+        phase_plan<MODE_SWIGLU>(st_a, gate_up, base + (unsigned)st_b.units);
+        ok = phase_run<MODE_RESIDUAL, __nv_bfloat16>(st_b, out, &L.w_out, sm, base, stamp, &st_a, &L.w_gate_up);
         FUSED_BARRIER();
 
-        // ---- gate and up with the activation ----
-        ok = phase_run<MODE_SWIGLU, __nv_bfloat16>(st, gate_up, &L.w_gate_up, sm, base);
+        // ---- gate and up with the activation (st_a); down follows (st_b) ----
         down.M = M; down.error_flag = p.error_flag;
         down.x = p.act; down.ldx = p.inter; down.K = p.inter; down.N = hidden; down.group = L.group_down;
-        down.resid = p.resid; down.norm_w = L.next_norm_w; down.xw_out = p.xw; down.ss_out = p.ss;
-        phase_begin<MODE_RESIDUAL>(st, down, &L.w_down, sm, base);
+        down.resid = p.resid; down.norm_w = L.next_norm_w; down.xw_out = p.xw; down.ss_out = p.ss; down.resid_early = 1;
+        phase_plan<MODE_RESIDUAL>(st_b, down, base + (unsigned)st_a.units);
+        ok = phase_run<MODE_SWIGLU, __nv_bfloat16>(st_a, gate_up, &L.w_gate_up, sm, base, stamp, &st_b, &L.w_down);
         FUSED_BARRIER();
 
-        // ---- down into the residual stream, handed on for the next norm ----
-        ok = phase_run<MODE_RESIDUAL, __nv_bfloat16>(st, down, &L.w_down, sm, base);
-        if (l + 1 < p.n_layers) {
+        // ---- down into the residual stream (st_b); the next layer's stacked projection or the output matrix follows ----
+        const CUtensorMap* after;
+        if (!last) {
             set_qkv(l + 1, hidden_parts, L.next_eps);
-            phase_begin<MODE_QKV>(st, qkv, &p.layers[l + 1].w_in, sm, base);
+            phase_plan<MODE_QKV>(st_a, qkv, base + (unsigned)st_b.units);
+            after = &p.layers[l + 1].w_in;
         } else {
             head.M = M; head.error_flag = p.error_flag;
             head.x = p.xw; head.ldx = hidden; head.K = hidden; head.N = p.vocab;
             head.in_ss = p.ss; head.in_parts = hidden_parts; head.in_eps = L.next_eps;
             head.out = p.logits; head.ldo = p.vocab; head.group = p.group_head;
-            phase_begin<MODE_PLAIN>(st, head, &head_map, sm, base);
+            phase_plan<MODE_PLAIN>(st_a, head, base + (unsigned)st_b.units);
+            after = &head_map;
         }
+        ok = phase_run<MODE_RESIDUAL, __nv_bfloat16>(st_b, down, &L.w_down, sm, base, stamp, &st_a, after);
         FUSED_BARRIER();
     }
 
     // ---- output matrix ----
-    ok = phase_run<MODE_PLAIN, float>(st, head, &head_map, sm, base);
+    ok = phase_run<MODE_PLAIN, float>(st_a, head, &head_map, sm, base, stamp, nullptr, nullptr);
     stamp();
     if (!ok && tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
 #undef FUSED_BARRIER
@@ -263,11 +278,7 @@ int sm_count() {
     return count;
 }
 
-int group_for(int tiles, int grid) {
-    int g = 1;
-    while (g < WARPS && (long long)tiles * g * 2 <= (long long)grid * WARPS) g *= 2;
-    return g;
-}
+int kblocks_of(int K) { return (K + BOXK - 1) / BOXK; }
 
 size_t smem_bytes(int k_max, int D) {
     const size_t linear = (size_t)WARPS * SLOTS * SLOT_ELEMS * 2 + (size_t)2 * WARPS * 4 * 32 * sizeof(float) + (size_t)8 * (k_max + X_PAD) * 2;
@@ -304,10 +315,10 @@ LLM_EXPORT int llm_fused_layer_fill(void* dst, const void* w_in, const void* w_o
     L.slot_map = slot_map;
     L.window = window;
     L.scale_log2 = scale * 1.4426950408889634f;
-    L.group_in = group_for(qkv_rows / 16, grid);
-    L.group_out = group_for((hidden + 15) / 16, grid);
-    L.group_gate_up = group_for((inter + 7) / 8, grid);
-    L.group_down = group_for((hidden + 15) / 16, grid);
+    L.group_in = choose_group(qkv_rows / 16, kblocks_of(hidden), grid);
+    L.group_out = choose_group((hidden + 15) / 16, kblocks_of(H * D), grid);
+    L.group_gate_up = choose_group((inter + 7) / 8, kblocks_of(hidden), grid);
+    L.group_down = choose_group((hidden + 15) / 16, kblocks_of(inter), grid);
     memcpy(dst, &L, sizeof L);
     return 0;
 }
@@ -367,7 +378,7 @@ LLM_EXPORT int llm_decode_fused(int M, int hidden, int H, int KV, int D, int int
     p.part_ml = part_ml;
     p.counters = counters;
     p.layers = (const FusedLayer*)layers;
-    p.group_head = group_for((vocab + 15) / 16, sm_count());
+    p.group_head = choose_group((vocab + 15) / 16, kblocks_of(hidden), sm_count());
     p.logits = logits;
     p.barrier = barrier;
     p.error_flag = error_flag;

@@ -53,7 +53,7 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
     StreamState st;
     // the weights do not depend on what ran before: their first boxes are asked for at once, while the
     // kernel before this one may still be running; everything else waits for it
-    stream_begin<MODE>(st, p, &wmap, my_ring, full[warp], 0u);
+    stream_begin<MODE, MT>(st, p, &wmap, my_ring, full[warp], 0u);
     // and the weights of a later product start their way into L2, a slice per CTA, 4 KB per instruction
     if (p.prefetch && warp == WARPS - 1) {
         const unsigned long long per_cta = ((p.prefetch_bytes / gridDim.x) + 4095) & ~4095ull;
@@ -125,8 +125,7 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     const int tiles = (p.N + FEATURES - 1) / FEATURES;
     const int grid = tiles < sm_count() ? tiles : sm_count();
     LinearParams q = p;
-    q.group = 1;  // the most warps per tile (a power of two) that still leaves every warp of the grid a tile
-    while (q.group < WARPS && (long long)tiles * q.group * 2 <= (long long)grid * WARPS) q.group *= 2;
+    q.group = choose_group(tiles, (p.K + BOXK - 1) / BOXK, grid);
     return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, *map);
 }
 

@@ -47,36 +47,67 @@ struct LinearParams {
     const int* slot_map;    // [M] page * page_size + offset of each token
     __nv_bfloat16* pool;    // [pages, 2, KV, page_size, D]
     int H, KV, D, page_size;
+    int resid_early;        // MODE_RESIDUAL: resid may be read before the product's input is ready (it was written
+                            // before the previous grid-wide barrier); a kernel of its own must leave this 0
     const void* prefetch;   // weights that a later product will stream: pulled into L2 meanwhile (or null)
     unsigned long long prefetch_bytes;
 };
 
-constexpr int SLOTS = 4;   // boxes per warp: three in flight while one is being used
+constexpr int SLOTS = 4;   // boxes per warp, all in flight but for the moment in which one is read into registers
 constexpr int BOXK = 128;  // k per box: a slot is 16 rows x 128 k = 4 KB
 constexpr int SLOT_ELEMS = 16 * BOXK;
 constexpr int PIECES = BOXK / 32;
 constexpr int X_PAD = 32;  // elements between the rows of x in shared memory: 8 tokens x 64 bytes hit 8 bank groups
 
 
+constexpr int MT_MAX = 2;  // 8-token tiles a product may carry
+
+// How many warps share a tile (1, 2, 4 or 8, splitting its k-blocks): the choice that leaves the busiest warp the
+// fewest boxes to stream.  The warps of a CTA form WARPS / g teams, team j of CTA b takes tiles b + j grid,
+// b + (j + WARPS / g) grid, ...; a shared tile costs its team a meeting in shared memory, counted as half a box.
+inline int choose_group(int tiles, int kblocks, int grid) {
+    int best = 1;
+    float best_cost = 1e30f;
+    for (int g = 1; g <= WARPS; g *= 2) {
+        const int teams = grid * (WARPS / g);
+        const int tiles_each = (tiles + teams - 1) / teams, boxes_each = (kblocks + g - 1) / g;
+        const float cost = (float)tiles_each * ((float)boxes_each + (g > 1 ? 0.5f : 0.f));
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = g;
+        }
+    }
+    return best;
+}
+
 struct StreamState {
     int group, member, tiles, kblocks, first, stride, my_tiles, units;
     int a_ti, a_kb, armed;
+    int mode, up_offset, D;  // what arm_next needs of the product: which rows a box takes
     unsigned base;  // boxes this warp's ring carried before this product
+    // What the end of this warp's FIRST tile needs besides the product, fetched together with the first weights
+    // (none of it depends on the product's input), so that the end is not a chain of trips to memory:
+    bool early;                                  // the values below are there
+    float e_cos[MT_MAX][2], e_sin[MT_MAX][2];    // MODE_QKV: the rotation of this thread's pair, per token
+    int e_slot[MT_MAX][2];                       // MODE_QKV: the tokens' cache slots
+    float e_resid[MT_MAX][4];                    // MODE_RESIDUAL: the stream's values (only with resid_early)
+    float e_norm[2];                             // MODE_RESIDUAL: the next norm's weights of this thread's features
 };
 
-template <int MODE>
-__device__ __forceinline__ void arm_next(StreamState& st, const LinearParams& p, const CUtensorMap* wmap, __nv_bfloat16* my_ring,
-                                         unsigned long long* my_full) {  // lane 0 only
+// Asks for the next box of the product whose state is `st` (lane 0 only).  The slot and its mbarrier phase follow
+// from the number of boxes the ring has carried, so a product's boxes may be asked for while the product before
+// it is still being computed.
+__device__ __forceinline__ void arm_next(StreamState& st, const CUtensorMap* wmap, __nv_bfloat16* my_ring, unsigned long long* my_full) {
     const int tile = st.first + st.a_ti * st.stride, sl = (st.base + st.armed) % SLOTS;
     __nv_bfloat16* dst = my_ring + (size_t)sl * SLOT_ELEMS;
     tma::mbar_expect_tx(&my_full[sl], (unsigned)(SLOT_ELEMS * 2));
-    if (MODE == MODE_SWIGLU) {  // the map's box is 8 rows: gate rows, then up rows
+    if (st.mode == MODE_SWIGLU) {  // the map's box is 8 rows: gate rows, then up rows
         tma::load_2d(dst, wmap, st.a_kb * BOXK, tile * 8, &my_full[sl]);
-        tma::load_2d(dst + 8 * BOXK, wmap, st.a_kb * BOXK, p.up_offset + tile * 8, &my_full[sl]);
-    } else if (MODE == MODE_QKV) {  // 8 lanes of a head's first half, then their partners in the second half
-        const int per_head = p.D >> 4, head = tile / per_head, y = head * p.D + (tile - head * per_head) * 8;
+        tma::load_2d(dst + 8 * BOXK, wmap, st.a_kb * BOXK, st.up_offset + tile * 8, &my_full[sl]);
+    } else if (st.mode == MODE_QKV) {  // 8 lanes of a head's first half, then their partners in the second half
+        const int per_head = st.D >> 4, head = tile / per_head, y = head * st.D + (tile - head * per_head) * 8;
         tma::load_2d(dst, wmap, st.a_kb * BOXK, y, &my_full[sl]);
-        tma::load_2d(dst + 8 * BOXK, wmap, st.a_kb * BOXK, y + (p.D >> 1), &my_full[sl]);
+        tma::load_2d(dst + 8 * BOXK, wmap, st.a_kb * BOXK, y + (st.D >> 1), &my_full[sl]);
     } else {
         tma::load_2d(dst, wmap, st.a_kb * BOXK, tile * 16, &my_full[sl]);
     }
@@ -88,11 +119,11 @@ __device__ __forceinline__ void arm_next(StreamState& st, const LinearParams& p,
     }
 }
 
-// Splits the work and asks for the first boxes.  Touches nothing but the weights: it may run before the
-// data of the product is ready.
-template <int MODE>
-__device__ __forceinline__ void stream_begin(StreamState& st, const LinearParams& p, const CUtensorMap* wmap,
-                                             __nv_bfloat16* my_ring, unsigned long long* my_full, unsigned base) {
+// Splits the work and fetches what the end of the first tile needs.  Touches nothing that depends on the product's
+// input: it may run before that is ready.  Asks for no box yet (stream_arm does).
+template <int MODE, int MT = 1>
+__device__ __forceinline__ void stream_plan(StreamState& st, const LinearParams& p, unsigned base) {
+    static_assert(MT <= MT_MAX, "too many token tiles");
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     st.group = p.group;
@@ -108,42 +139,117 @@ __device__ __forceinline__ void stream_begin(StreamState& st, const LinearParams
     st.a_kb = st.member;
     st.armed = 0;
     st.base = base;
-    if (lane == 0)
-        while (st.armed < SLOTS - 1 && st.armed < st.units) arm_next<MODE>(st, p, wmap, my_ring, my_full);
+    st.mode = MODE;
+    st.up_offset = p.up_offset;
+    st.D = p.D;
+    st.early = false;
+    if (st.member == 0 && st.my_tiles > 0) {
+        const int qr = lane >> 2, qc = lane & 3, tile = st.first;
+        if constexpr (MODE == MODE_QKV) {
+            const int D = p.D, half = D >> 1, per_head = D >> 4;
+            const int head = tile / per_head, j = (tile - head * per_head) * 8 + qr;
+            const bool rotate = head < p.H + p.KV && p.rotary;
+#pragma unroll
+            for (int t = 0; t < MT; ++t)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int m = 8 * t + 2 * qc + i;
+                    st.e_cos[t][i] = 1.f;
+                    st.e_sin[t][i] = 0.f;
+                    st.e_slot[t][i] = 0;
+                    if (m >= p.M) continue;
+                    if (rotate) {
+                        const int pos = min(max(p.positions[m], 0), p.rotary_rows - 1);
+                        st.e_cos[t][i] = p.rotary[(size_t)pos * D + j];
+                        st.e_sin[t][i] = p.rotary[(size_t)pos * D + half + j];
+                    }
+                    if (head >= p.H) st.e_slot[t][i] = p.slot_map[m];
+                }
+            st.early = true;
+        } else if constexpr (MODE == MODE_RESIDUAL) {
+            const int n0 = tile * 16;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) st.e_norm[h] = n0 + qr + 8 * h < p.N ? p.norm_w[n0 + qr + 8 * h] : 0.f;
+#pragma unroll
+            for (int t = 0; t < MT; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int n = n0 + qr + 8 * (e >> 1), m = 8 * t + 2 * qc + (e & 1);
+                    st.e_resid[t][e] = p.resid_early && m < p.M && n < p.N ? p.resid[(size_t)m * p.N + n] : 0.f;
+                }
+            st.early = true;
+        }
+    }
+}
+
+// Fills the free slots of the ring with the product's next boxes; `consumed`: how many of its boxes have been used.
+__device__ __forceinline__ void stream_arm(StreamState& st, const CUtensorMap* wmap, __nv_bfloat16* my_ring, unsigned long long* my_full,
+                                           int consumed) {
+    if ((threadIdx.x & 31) == 0)
+        while (st.armed < st.units && st.armed < consumed + SLOTS) arm_next(st, wmap, my_ring, my_full);
+}
+
+template <int MODE, int MT = 1>
+__device__ __forceinline__ void stream_begin(StreamState& st, const LinearParams& p, const CUtensorMap* wmap,
+                                             __nv_bfloat16* my_ring, unsigned long long* my_full, unsigned base) {
+    stream_plan<MODE, MT>(st, p, base);
+    stream_arm(st, wmap, my_ring, my_full, 0);
 }
 
 // x into shared memory (rows beyond M as zeros) and the input rows' RMS scales; the caller synchronises the CTA.
+// Every load is asked for before the first is used: one trip to memory, not one per loop.
 template <int MT>
 __device__ __forceinline__ void stream_stage_x(const LinearParams& p, __nv_bfloat16* x_s, float* row_scale) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int M = p.M, K = p.K, x_pitch = K + X_PAD;
-    // x into shared memory (rows beyond M as zeros), and the input rows' RMS scale from the partial sums of
-    // squares: warp w sums rows w, w + 8, ...; its lanes take the parts in strides of 32 (a fixed order)
-    {
-        const int per_row = K >> 3;
-        for (int idx = tid; idx < 8 * MT * per_row; idx += THREADS) {
-            const int m = idx / per_row, c = idx - m * per_row;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (m < M) v = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + c * 8);
-            *reinterpret_cast<uint4*>(x_s + (size_t)m * x_pitch + c * 8) = v;
+    // the partial sums of squares of this warp's rows (row m = warp + 8 t; lanes take the parts in strides of 32)
+    constexpr int SS_AHEAD = 4;
+    float ss[MT][SS_AHEAD];
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int j = 0; j < SS_AHEAD; ++j) {
+            const int m = warp + WARPS * t, i = lane + 32 * j;
+            ss[t][j] = p.in_ss && m < M && i < p.in_parts ? p.in_ss[(size_t)i * M + m] : 0.f;
         }
+    {
+        // asynchronous 16-byte copies straight into shared memory: all of them in flight at once
+        const int per_row = K >> 3, total = 8 * MT * per_row;
+        for (int idx = tid; idx < total; idx += THREADS) {
+            const int m = idx / per_row, c = idx - m * per_row;
+            __nv_bfloat16* dst = x_s + (size_t)m * x_pitch + c * 8;
+            if (m < M) {
+                const unsigned d32 = (unsigned)__cvta_generic_to_shared(dst);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d32), "l"(p.x + (size_t)m * p.ldx + c * 8) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
-    for (int m = warp; m < 8 * MT; m += WARPS) {
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+        const int m = warp + WARPS * t;
         float s = 1.f;
         if (p.in_ss && m < M) {
             float sum = 0.f;
-            for (int i = lane; i < p.in_parts; i += 32) sum += p.in_ss[(size_t)i * M + m];
+#pragma unroll
+            for (int j = 0; j < SS_AHEAD; ++j) sum += ss[t][j];  // a fixed order: parts lane, lane + 32, ...
+            for (int i = lane + 32 * SS_AHEAD; i < p.in_parts; i += 32) sum += p.in_ss[(size_t)i * M + m];
             s = rsqrtf(warp_sum(sum) / (float)K + p.in_eps);
         }
         if (lane == 0) row_scale[m] = s;
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");  // this thread's copies have landed; the caller's barrier shows them to all
 }
 
 // The products of every box of this warp's tiles and the tiles' epilogues.  Returns false if a wait gave up.
+// `next` (or null): the planned product that follows on the same ring (its base is this one's base plus units); once
+// all of this product's boxes are on their way, the slots it frees take the next product's boxes.
 template <int MT, int MODE, typename TO>
 __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& p, const CUtensorMap* wmap, __nv_bfloat16* my_ring,
                                            unsigned long long* my_full, float* red, const __nv_bfloat16* x_s,
-                                           const float* row_scale) {
+                                           const float* row_scale, StreamState* next = nullptr, const CUtensorMap* next_map = nullptr) {
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qr = lane >> 2, qc = lane & 3;
@@ -164,8 +270,6 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
         for (int kb = member; kb < kblocks; kb += group, ++unit) {
-            // the slot used one unit ago is free (the __syncwarp below): ask for the box three units ahead
-            if (lane == 0 && st.armed < units) arm_next<MODE>(st, p, wmap, my_ring, my_full);
             if (!gave_up && !tma::mbar_wait(&my_full[(st.base + unit) % SLOTS], ((st.base + unit) / SLOTS) & 1)) {
                 gave_up = true;
                 if (p.error_flag) atomicExch(p.error_flag, 1);
@@ -183,6 +287,11 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 for (int t = 0; t < MT; ++t)
                     b[i][t] = have ? *reinterpret_cast<const uint4*>(xrow[t] + k0 + i * 32) : make_uint4(0, 0, 0, 0);
             }
+            __syncwarp();  // every lane holds its pieces of the slot in registers: the slot takes the next box
+            if (lane == 0) {
+                if (st.armed < units) arm_next(st, wmap, my_ring, my_full);
+                else if (next && next->armed < next->units) arm_next(*next, next_map, my_ring, my_full);
+            }
 #pragma unroll
             for (int i = 0; i < PIECES; ++i)
 #pragma unroll
@@ -190,7 +299,6 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     mma_bf16(acc[t], a[i][0].x, a[i][1].x, a[i][0].y, a[i][1].y, b[i][t].x, b[i][t].y);
                     mma_bf16(acc[t], a[i][0].z, a[i][1].z, a[i][0].w, a[i][1].w, b[i][t].z, b[i][t].w);
                 }
-            __syncwarp();  // every lane has read the slot: it may be refilled
         }
         if (group > 1) {
             // the members' partial sums meet in shared memory (two buffers by tile parity: the first member may
@@ -226,8 +334,15 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     if (m >= M) continue;
                     float a = acc[t][i] * row_scale[m], b = acc[t][2 + i] * row_scale[m];
                     if (head < p.H + p.KV && p.rotary) {
-                        const int pos = min(max(p.positions[m], 0), p.rotary_rows - 1);
-                        const float c = p.rotary[(size_t)pos * D + j], sn = p.rotary[(size_t)pos * D + half + j];
+                        float c, sn;
+                        if (ti == 0 && st.early) {
+                            c = st.e_cos[t][i];
+                            sn = st.e_sin[t][i];
+                        } else {
+                            const int pos = min(max(p.positions[m], 0), p.rotary_rows - 1);
+                            c = p.rotary[(size_t)pos * D + j];
+                            sn = p.rotary[(size_t)pos * D + half + j];
+                        }
                         const float ra = a * c - b * sn, rb = b * c + a * sn;
                         a = ra;
                         b = rb;
@@ -236,7 +351,8 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     if (head < p.H) {
                         dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + head * D + j;
                     } else {
-                        const int slot = p.slot_map[m], page = slot / p.page_size, off = slot - page * p.page_size;
+                        const int slot = ti == 0 && st.early ? st.e_slot[t][i] : p.slot_map[m];
+                        const int page = slot / p.page_size, off = slot - page * p.page_size;
                         const int is_v = head >= p.H + p.KV, kvh = head - p.H - (is_v ? p.KV : 0);
                         dst = p.pool + (((size_t)(page * 2 + is_v) * p.KV + kvh) * p.page_size + off) * D + j;
                     }
@@ -266,9 +382,11 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     const float s = acc[t][e] * row_scale[m];
                     if constexpr (MODE == MODE_RESIDUAL) {
                         if (live) {
-                            const float v = p.resid[(size_t)m * N + n] + s;
+                            const bool have = ti == 0 && st.early;
+                            const float before = have && p.resid_early ? st.e_resid[t][e] : p.resid[(size_t)m * N + n];
+                            const float v = before + s;
                             p.resid[(size_t)m * N + n] = v;
-                            p.xw_out[(size_t)m * N + n] = __float2bfloat16_rn(v * p.norm_w[n]);
+                            p.xw_out[(size_t)m * N + n] = __float2bfloat16_rn(v * (have ? st.e_norm[e >> 1] : p.norm_w[n]));
                             sq[e & 1] += v * v;
                         }
                     } else {

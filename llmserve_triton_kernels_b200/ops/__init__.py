@@ -423,7 +423,7 @@ def fused_decode_plan(*, ctx, hidden, num_heads, num_kv_heads, head_dim, inter, 
     dbase = (-device_records.data_ptr()) % 64
     device_records[dbase : dbase + len(layers) * record].copy_(host[base : base + len(layers) * record])
     longest = ctx.max_context_len
-    splits = max(1, min(-(-longest // _SMALL_TILE_KEYS), -(-_SM_COUNT // (m * num_kv_heads)), 32))
+    splits = max(1, min(-(-longest // _SMALL_TILE_KEYS), _SM_COUNT // (m * num_kv_heads), 32))  # an item per CTA at most
     f32 = dict(dtype=torch.float32, device=dev)
     bf16 = dict(dtype=torch.bfloat16, device=dev)
     plan = FusedDecodePlan(
