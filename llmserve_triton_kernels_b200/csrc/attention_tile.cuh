@@ -10,6 +10,7 @@ namespace attn {
 
 constexpr int THREADS = 128;
 constexpr int SMALL_ROWS = 16;  // requests with at most this many rows go to the KEYS shape
+constexpr int SMALL_MIN_TILES = 8;  // tiles (of 128 keys) a split of that shape takes at least
 
 // The 128 threads that compute a tile meet here.  A named barrier, not __syncthreads: inside the fused decode
 // kernel the tile is computed by four of the CTA's eight warps.
@@ -118,10 +119,11 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     const int tile_pos_min = pos0 + tok_first;
     const int tile_lo_max = p.window > 0 ? max(0, pos0 + tok_last - p.window + 1) : 0;
     const int tile_first = key_lo / BNC, tile_last = key_hi / BNC;
-    // a split takes at least two tiles, so short contexts use few splits however many the grid has; splits
+    // a split of the small shape takes at least SMALL_MIN_TILES tiles, so contexts up to that many tiles are not
+    // split however many splits the grid has (merging splits costs more than a few more tiles in a row); splits
     // beyond the last active one do nothing
     const int n_tiles = tile_last - tile_first + 1;
-    const int per_split = max(SMALL ? 2 : 1, (n_tiles + p.splits - 1) / p.splits);
+    const int per_split = max(SMALL ? SMALL_MIN_TILES : 1, (n_tiles + p.splits - 1) / p.splits);
     const int active_splits = (n_tiles + per_split - 1) / per_split;
     const int t_begin = tile_first + split * per_split;
     const int t_end = min(tile_last + 1, t_begin + per_split);
@@ -154,14 +156,17 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     constexpr int CPT = CHUNKS / TPK;         // 16-byte pieces per thread
     static_assert(THREADS % BNC == 0 && CHUNKS % TPK == 0, "a key row must split evenly over its threads");
     const int load_key = tid / TPK, load_c0 = (tid % TPK) * CPT;
-    auto load_tile = [&](int t, int stage) {
+    // the page of this thread's key row in tile t (-1: the row lies outside the piece's keys and reads as zeros);
+    // looked up one tile ahead of the copies that use it, so that a tile's latency is one trip to memory, not two
+    auto page_of = [&](int t) -> int {
         const int j = t * BNC + load_key;
-        const bool valid = j >= key_lo && j <= key_hi;
+        return t < t_end && j >= key_lo && j <= key_hi ? table[j / p.page_size] : -1;
+    };
+    auto load_tile = [&](int t, int stage, int page) {
+        const int j = t * BNC + load_key;
+        const bool valid = page >= 0;
         size_t off = 0;
-        if (valid) {
-            const int lp = j / p.page_size;
-            off = ((size_t)(table[lp] * 2) * p.KV + kvh) * head_stride + (size_t)(j - lp * p.page_size) * D;
-        }
+        if (valid) off = ((size_t)(page * 2) * p.KV + kvh) * head_stride + (size_t)(j % p.page_size) * D;
         const int dst_row = (stage * BNC + load_key) * D;
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
@@ -180,17 +185,24 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     // one commit group per tile, empty past the end, so that the wait below counts tiles
+    {
+        int first_pages[STAGES - 1];
 #pragma unroll
-    for (int i = 0; i < STAGES - 1; ++i) {
-        if (t_begin + i < t_end) load_tile(t_begin + i, i);
-        cp_async_commit();
+        for (int i = 0; i < STAGES - 1; ++i) first_pages[i] = page_of(t_begin + i);
+#pragma unroll
+        for (int i = 0; i < STAGES - 1; ++i) {
+            if (t_begin + i < t_end) load_tile(t_begin + i, i, first_pages[i]);
+            cp_async_commit();
+        }
     }
+    int page_next = page_of(t_begin + STAGES - 1);
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) % STAGES;
         cp_async_wait<STAGES - 2>();  // tile t has landed (this thread's copies) ...
         cta_sync();              // ... everyone's; and the stage refilled next is no longer read
-        if (t + STAGES - 1 < t_end) load_tile(t + STAGES - 1, (t - t_begin + STAGES - 1) % STAGES);
+        if (t + STAGES - 1 < t_end) load_tile(t + STAGES - 1, (t - t_begin + STAGES - 1) % STAGES, page_next);
         cp_async_commit();
+        page_next = page_of(t + STAGES);
         const __nv_bfloat16* ks_tile = k_s + (stage * BNC + key_warp * BN) * D;
         const __nv_bfloat16* vs_tile = v_s + (stage * BNC + key_warp * BN) * D;
         const int key_base = t * BNC + key_warp * BN;

@@ -251,6 +251,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                                            unsigned long long* my_full, float* red, const __nv_bfloat16* x_s,
                                            const float* row_scale, StreamState* next = nullptr, const CUtensorMap* next_map = nullptr) {
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
+    constexpr int CHAINS = MT == 1 ? 4 : 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qr = lane >> 2, qc = lane & 3;
     const int M = p.M, N = p.N, K = p.K, x_pitch = K + X_PAD;
@@ -264,11 +265,15 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
 
     int unit = 0;
     for (int ti = 0; ti < my_tiles; ++ti) {
-        float acc[MT][4];
+        // CHAINS independent sums per token tile, joined when the tile is complete: an MMA waits for the one before it
+        // on the same accumulator, and one chain of eight per box would leave the tensor pipe idle most of the time
+        float part[MT][CHAINS][4];
 #pragma unroll
         for (int t = 0; t < MT; ++t)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+            for (int c = 0; c < CHAINS; ++c)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) part[t][c][e] = 0.f;
         for (int kb = member; kb < kblocks; kb += group, ++unit) {
             if (!gave_up && !tma::mbar_wait(&my_full[(st.base + unit) % SLOTS], ((st.base + unit) / SLOTS) & 1)) {
                 gave_up = true;
@@ -296,10 +301,20 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
             for (int i = 0; i < PIECES; ++i)
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
-                    mma_bf16(acc[t], a[i][0].x, a[i][1].x, a[i][0].y, a[i][1].y, b[i][t].x, b[i][t].y);
-                    mma_bf16(acc[t], a[i][0].z, a[i][1].z, a[i][0].w, a[i][1].w, b[i][t].z, b[i][t].w);
+                    mma_bf16(part[t][(2 * i) % CHAINS], a[i][0].x, a[i][1].x, a[i][0].y, a[i][1].y, b[i][t].x, b[i][t].y);
+                    mma_bf16(part[t][(2 * i + 1) % CHAINS], a[i][0].z, a[i][1].z, a[i][0].w, a[i][1].w, b[i][t].z, b[i][t].w);
                 }
         }
+        float acc[MT][4];
+#pragma unroll
+        for (int t = 0; t < MT; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float sum = part[t][0][e];
+#pragma unroll
+                for (int c = 1; c < CHAINS; ++c) sum += part[t][c][e];  // a fixed order
+                acc[t][e] = sum;
+            }
         if (group > 1) {
             // the members' partial sums meet in shared memory (two buffers by tile parity: the first member may
             // still be reading the tile before when the others write this one); the first member adds them up
