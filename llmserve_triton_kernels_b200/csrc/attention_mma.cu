@@ -111,12 +111,13 @@ int launch_all(AttnParams p, int requests, int n_tokens, const int* token_reques
 // scratch_o / scratch_ml: float32 [tokens, H, splits, D] and [tokens, H, splits, 2], needed when a
 // split count exceeds 1; counters: int32 [requests * KV], all zero before the launch and again
 // after it, needed when splits_small exceeds 1.  Returns LLM_ERR_UNSUPPORTED for head sizes other than 16/32/64/128.
-LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* pool,
-                                 const int* page_table, int table_width, const int* token_request, const int* cu_tokens,
-                                 const int* ctx_lens, int requests, int n_tokens, int H, int KV, int D, int page_size,
-                                 int window, float scale, int max_rows_large, int have_small, int splits_small,
-                                 int splits_large, float* scratch_o, float* scratch_ml, int* counters,
-                                 cudaStream_t stream) {
+// skip_tokens_from: requests that bring at least this many tokens are left to another kernel (0: none are).
+LLM_EXPORT int llm_attention_mma_routed(const void* q, int q_stride, void* out, int out_stride, const void* pool,
+                                        const int* page_table, int table_width, const int* token_request, const int* cu_tokens,
+                                        const int* ctx_lens, int requests, int n_tokens, int H, int KV, int D, int page_size,
+                                        int window, float scale, int max_rows_large, int have_small, int splits_small,
+                                        int splits_large, float* scratch_o, float* scratch_ml, int* counters,
+                                        int skip_tokens_from, cudaStream_t stream) {
     if (n_tokens <= 0 || requests <= 0) return 0;
     if (H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0 || splits_small < 1 || splits_large < 1)
         return LLM_ERR_BAD_ARGUMENT;
@@ -145,6 +146,7 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, void* out, int out
     p.part_o = scratch_o;
     p.part_ml = scratch_ml;
     p.counters = counters;
+    p.skip_tokens_from = skip_tokens_from;
     switch (D) {
         case 16: return launch_all<16>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
         case 32: return launch_all<32>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
@@ -152,4 +154,15 @@ LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, void* out, int out
         case 128: return launch_all<128>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
         default: return LLM_ERR_UNSUPPORTED;
     }
+}
+
+LLM_EXPORT int llm_attention_mma(const void* q, int q_stride, void* out, int out_stride, const void* pool,
+                                 const int* page_table, int table_width, const int* token_request, const int* cu_tokens,
+                                 const int* ctx_lens, int requests, int n_tokens, int H, int KV, int D, int page_size,
+                                 int window, float scale, int max_rows_large, int have_small, int splits_small,
+                                 int splits_large, float* scratch_o, float* scratch_ml, int* counters,
+                                 cudaStream_t stream) {
+    return llm_attention_mma_routed(q, q_stride, out, out_stride, pool, page_table, table_width, token_request, cu_tokens, ctx_lens,
+                                    requests, n_tokens, H, KV, D, page_size, window, scale, max_rows_large, have_small,
+                                    splits_small, splits_large, scratch_o, scratch_ml, counters, 0, stream);
 }

@@ -67,6 +67,7 @@ struct AttnParams {
     float* part_o;          // [tokens, H, splits, D], relative to the split's max
     float* part_ml;         // [tokens, H, splits, 2]: (max in the base-2 domain, sum)
     int* counters;          // [requests * KV] zeros: how many splits of a (request, kv head) have finished
+    int skip_tokens_from;   // requests that bring at least this many tokens are another kernel's (0: none are)
 };
 
 // Stages of the key/value ring: four where shared memory allows, three for the largest tiles.
@@ -91,6 +92,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     const int q_begin = p.cu_tokens[r], q_len = p.cu_tokens[r + 1] - q_begin;
     const int G = p.G, rows_total = q_len * G;
     if ((rows_total <= SMALL_ROWS) != SMALL) return;
+    if (p.skip_tokens_from > 0 && q_len >= p.skip_tokens_from) return;
     const int row0 = tile * BM;
     if (row0 >= rows_total) return;
     const int ctx = p.ctx_lens[r], pos0 = ctx - q_len;

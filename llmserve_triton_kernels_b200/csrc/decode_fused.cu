@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(THREADS) decode_fused_kernel(const FusedParams
             ap.part_o = p.part_o;
             ap.part_ml = p.part_ml;
             ap.counters = p.counters;
+            ap.skip_tokens_from = 0;
             const int items = M * p.KV * p.attn_splits;
             for (int item = blockIdx.x; item < items; item += gridDim.x) {
                 const int split = item % p.attn_splits, rest = item / p.attn_splits;

@@ -17,9 +17,7 @@
 // roles leave their loops, tensor memory is freed and the kernel returns.
 #include "common.cuh"
 #include "tma.cuh"
-
-#include <mutex>
-#include <unordered_map>
+#include "umma.cuh"
 
 namespace {
 
@@ -33,40 +31,6 @@ struct GemmParams {
     int up_offset;  // MODE_SWIGLU: row of w where the up matrix starts
     int* error_flag;
 };
-
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, atoms of 8 rows (1024 bytes) one after another
-__device__ __forceinline__ unsigned long long umma_desc(const void* smem) {
-    const unsigned addr = tma::smem_addr(smem);
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr >> 4) & 0x3fff);       // start address, 16-byte units
-    d |= (unsigned long long)1 << 16;                      // leading byte offset (not used by swizzled K-major)
-    d |= (unsigned long long)(1024 >> 4) << 32;            // stride byte offset: 8 rows of 128 bytes
-    d |= (unsigned long long)1 << 46;                      // descriptor version of this architecture
-    d |= (unsigned long long)2 << 61;                      // 128-byte swizzle
-    return d;
-}
-
-__device__ __forceinline__ void umma_bf16(unsigned d_tmem, unsigned long long a, unsigned long long b, unsigned idesc, bool accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"((unsigned)accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tma::smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
-    unsigned r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 template <typename TO>
 __device__ __forceinline__ void store32(TO* dst, const float (&v)[32], int valid);
@@ -113,7 +77,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     // 2 BN rows: one product of N = 2 BN fills columns [0, BN) with the gate's sums and [BN, 2 BN) with the up's
     constexpr int UMMA_N = NB * BN;
     static_assert(UMMA_N % 16 == 0 && UMMA_N >= 16 && UMMA_N <= 256, "tcgen05.mma with M = 128 takes N in steps of 16 up to 256");
-    constexpr unsigned IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(UMMA_N >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+    constexpr unsigned IDESC = umma::idesc_bf16(BM, UMMA_N, false);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) unsigned long long full[STAGES], empty[STAGES], acc_ready;
@@ -176,15 +140,15 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const unsigned char* slot = ring + (size_t)s * SLOT_BYTES;
-            const unsigned long long a = umma_desc(slot), b = umma_desc(slot + A_BYTES);
+            const unsigned long long a = umma::desc_sw128(slot), b = umma::desc_sw128(slot + A_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
                 // 16 k = 32 bytes further along the 128-byte rows: the start address moves by two 16-byte units
-                umma_bf16(d_tmem, a + 2 * k, b + 2 * k, IDESC, (kb | k) != 0);
+                umma::mma_bf16(d_tmem, a + 2 * k, b + 2 * k, IDESC, (kb | k) != 0);
             }
-            umma_commit(&empty[s]);  // arrives when the products above have read the slot
+            umma::commit(&empty[s]);  // arrives when the products above have read the slot
         }
-        umma_commit(&acc_ready);  // arrives when every product has landed in tensor memory
+        umma::commit(&acc_ready);  // arrives when every product has landed in tensor memory
     } else if (warp >= 2) {
         // ---- epilogue: warp w may touch the 32 lanes (warp % 4) * 32 .. of tensor memory ----
         const int quarter = warp & 3;
@@ -198,10 +162,10 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 float v[32];
-                tmem_ld32(lane_base + c, v);
+                umma::tmem_ld32(lane_base + c, v);
                 if (MODE == MODE_SWIGLU) {
                     float u[32];
-                    tmem_ld32(lane_base + BN + c, u);
+                    umma::tmem_ld32(lane_base + BN + c, u);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * u[i];
                 }
@@ -220,32 +184,6 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     }
 }
 
-struct MapKey {
-    const void* p;
-    int rows, cols, ld, box_rows;
-    bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
-};
-struct MapHash {
-    size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.p) ^ ((size_t)k.rows << 24) ^ ((size_t)k.cols << 8) ^ (size_t)k.box_rows ^ ((size_t)k.ld << 40);
-    }
-};
-
-// Maps are cached by (address, shape): weights live for the life of the model, and activations
-// of a shape come back to the same addresses from the caching allocator.
-const CUtensorMap* map_of(const void* base, int rows, int cols, int ld, int box_rows) {
-    static std::unordered_map<MapKey, CUtensorMap, MapHash> maps;
-    static std::mutex lock;
-    std::lock_guard<std::mutex> guard(lock);
-    const MapKey key{base, rows, cols, ld, box_rows};
-    auto it = maps.find(key);
-    if (it != maps.end()) return &it->second;
-    if (maps.size() > 4096) maps.clear();
-    CUtensorMap map;
-    if (!tma::make_map_2d_bf16(&map, base, rows, cols, ld, box_rows, BK, CU_TENSOR_MAP_SWIZZLE_128B)) return nullptr;
-    return &maps.emplace(key, map).first->second;
-}
-
 template <int BN, int MODE, int STAGES, typename TO>
 int launch(const void* x, int ldx, const void* w, int w_rows, const GemmParams& p, cudaStream_t stream) {
     constexpr int NB = MODE == MODE_SWIGLU ? 2 : 1;
@@ -257,8 +195,8 @@ int launch(const void* x, int ldx, const void* w, int w_rows, const GemmParams& 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const CUtensorMap* xmap = map_of(x, p.M, p.K, ldx, BM);
-    const CUtensorMap* wmap = map_of(w, w_rows, p.K, p.K, BN);
+    const CUtensorMap* xmap = tma::cached_map_2d_bf16(x, p.M, p.K, ldx, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    const CUtensorMap* wmap = tma::cached_map_2d_bf16(w, w_rows, p.K, p.K, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!xmap || !wmap) return LLM_ERR_UNSUPPORTED;
     dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM);
     if (grid.y > 65535) return LLM_ERR_UNSUPPORTED;

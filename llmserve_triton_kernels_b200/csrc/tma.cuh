@@ -8,6 +8,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+#include <unordered_map>
+
 namespace tma {
 
 // ---- host -------------------------------------------------------------------------------------
@@ -40,6 +43,38 @@ inline bool make_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, 
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Maps are cached by (address, shape, box): weights and cache pools live for the life of the model, and
+// activations of a shape come back to the same addresses from a caching allocator.  Null if the driver refuses.
+inline const CUtensorMap* cached_map_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                                             uint32_t box_cols, CUtensorMapSwizzle swizzle) {
+    struct Key {
+        const void* p;
+        uint64_t rows, cols, ld;
+        uint32_t box_rows, box_cols;
+        int swizzle;
+        bool operator==(const Key& o) const {
+            return p == o.p && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && box_cols == o.box_cols &&
+                   swizzle == o.swizzle;
+        }
+    };
+    struct Hash {
+        size_t operator()(const Key& k) const {
+            return std::hash<const void*>()(k.p) ^ (size_t)(k.rows * 0x9E3779B97F4A7C15ull) ^ (size_t)(k.cols << 8) ^ (size_t)(k.ld << 40) ^
+                   (size_t)(k.box_rows << 3) ^ (size_t)k.box_cols ^ ((size_t)k.swizzle << 60);
+        }
+    };
+    static std::unordered_map<Key, CUtensorMap, Hash> maps;
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    const Key key{base, rows, cols, ld, box_rows, box_cols, (int)swizzle};
+    auto it = maps.find(key);
+    if (it != maps.end()) return &it->second;
+    if (maps.size() > 4096) maps.clear();
+    CUtensorMap map;
+    if (!make_map_2d_bf16(&map, base, rows, cols, ld, box_rows, box_cols, swizzle)) return nullptr;
+    return &maps.emplace(key, map).first->second;
 }
 
 // ---- device -----------------------------------------------------------------------------------

@@ -1,0 +1,54 @@
+// tcgen05 (fifth-generation tensor cores) from plain CUDA: shared-memory operand descriptors, the
+// instruction descriptor, MMA issue and commit, and loads from tensor memory.  Shared by the matrix
+// product (gemm_tcgen05.cu) and the attention for prompt portions (attention_tcgen05.cu).
+#pragma once
+
+#include "tma.cuh"
+
+namespace umma {
+
+// Instruction descriptor of a bfloat16 x bfloat16 -> float32 product with M rows and N columns per instruction;
+// b_mn_major: the B operand lies in shared memory with N contiguous (rows are k), else with K contiguous.
+__host__ __device__ constexpr unsigned idesc_bf16(int M, int N, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((unsigned)(N >> 3) << 17) | ((unsigned)(M >> 4) << 24);
+}
+
+// Operand tile with 128-byte swizzle: rows of 128 bytes, atoms of 8 rows (1024 bytes) one after another.  K-major:
+// a row holds 64 k of one row of the operand; MN-major (B only): a row holds 64 columns of one k.  In both, the next
+// atom (8 more rows) lies 1024 bytes further (the stride offset).  The leading offset is not used by K-major swizzled
+// tiles (1 by convention); an MN-major tile one atom wide passes 1024 bytes there too, so that either reading of the
+// two fields gives the same tile.
+__device__ __forceinline__ unsigned long long desc_sw128(const void* smem, unsigned leading_16b = 1) {
+    const unsigned addr = tma::smem_addr(smem);
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr >> 4) & 0x3fff);       // start address, 16-byte units
+    d |= (unsigned long long)(leading_16b & 0x3fff) << 16;  // leading byte offset, 16-byte units
+    d |= (unsigned long long)(1024 >> 4) << 32;            // stride byte offset: 8 rows of 128 bytes
+    d |= (unsigned long long)1 << 46;                      // descriptor version of this architecture
+    d |= (unsigned long long)2 << 61;                      // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void mma_bf16(unsigned d_tmem, unsigned long long a, unsigned long long b, unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"((unsigned)accumulate) : "memory");
+}
+__device__ __forceinline__ void commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tma::smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+}  // namespace umma

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "llm_gemm_tcgen05": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_attention_generic": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "llm_attention_mma_routed": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    "llm_attention_tcgen05": [_vp, _i, _vp, _i, _vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp],
     "llm_argmax": [_vp, _i, _i, _vp, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -72,6 +74,10 @@ _MMA_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention; o
 _SMALL_ROWS = 16  # requests with at most this many (token, group member) rows take the split-key shape
 _SMALL_TILE_KEYS = 128  # keys one CTA of that shape covers per tile
 _SM_COUNT = 148
+_TC_ATTENTION_ENABLED = True
+_TC_ATTENTION_HEAD_DIM = 64
+_TC_ATTENTION_PAGE_SIZES = (8, 16, 32, 64)
+_TC_ATTENTION_MIN_TOKENS = 128  # a request with at least this many tokens in the step: attention on tcgen05
 _TCGEN05_MIN_ROWS = 128  # from this many rows a bfloat16 product runs on tcgen05 with TMA-fed tiles (own kernel)
 _DECODE_LINEAR_MAX_ROWS = 16  # up to this many rows a bfloat16 matrix product streams the weights once (own kernel)
 _FORCE_GENERIC_ATTENTION = False  # tests switch the tensor-core attention off to reach the general kernel in bfloat16
@@ -550,9 +556,30 @@ def paged_attention(
         cu = getattr(ctx, "host_cu_tokens", None)
         if cu is None:
             cu = ctx.cu_tokens.tolist()
-        rows = [(b - a) * group for a, b in zip(cu, cu[1:])]
+        lens = [b - a for a, b in zip(cu, cu[1:])]
+        # requests that bring at least 128 tokens: 128-token tiles of one head on tcgen05 (head size 64, pages of 8
+        # to 64 keys); the others: rows of (token, group member) on mma.sync, 64 rows a tile or the split-key shape
+        tc_min = 0
+        if head_dim == _TC_ATTENTION_HEAD_DIM and pool.shape[3] in _TC_ATTENTION_PAGE_SIZES and _TC_ATTENTION_ENABLED:
+            tc_min = _TC_ATTENTION_MIN_TOKENS
+        tc_longest = max((x for x in lens if tc_min and x >= tc_min), default=0)
+        if tc_longest:
+            code = _launch(
+                "llm_attention_tcgen05", _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), pool.shape[0],
+                _ptr(page_table), page_table.shape[1], _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), len(lens), n, num_heads,
+                num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), tc_min, tc_longest, _error_flag_ptr(),
+                _stream(),
+            )
+            if code == 10002:  # the kernel does not take this layout: all requests go the other way
+                add_launches(-1)
+                tc_min = tc_longest = 0
+            else:
+                _check(code, "paged_attention (tcgen05)")
+        rows = [x * group for x in lens if not (tc_longest and x >= tc_min)]
         small = sum(1 for x in rows if x <= _SMALL_ROWS)
         max_rows_large = max((x for x in rows if x > _SMALL_ROWS), default=0)
+        if not rows:
+            return out
         splits = 1
         if small:
             longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
@@ -560,14 +587,14 @@ def paged_attention(
             splits = max(1, min(useful, -(-_SM_COUNT // (small * num_kv_heads)), 32))  # about one CTA per SM
         scratch_o = scratch_ml = counters = None
         if splits > 1:
-            counters = _split_counters(qkv.device, len(rows) * num_kv_heads)
+            counters = _split_counters(qkv.device, len(lens) * num_kv_heads)
             scratch_o = torch.empty((n * num_heads * splits * head_dim,), dtype=torch.float32, device=qkv.device)
             scratch_ml = torch.empty((n * num_heads * splits * 2,), dtype=torch.float32, device=qkv.device)
         code = _launch(
-            "llm_attention_mma", _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _ptr(page_table),
-            page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), len(rows), n,
+            "llm_attention_mma_routed", _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _ptr(page_table),
+            page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), len(lens), n,
             num_heads, num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), max_rows_large,
-            int(small > 0), splits, 1, _ptr(scratch_o), _ptr(scratch_ml), _ptr(counters), _stream(),
+            int(small > 0), splits, 1, _ptr(scratch_o), _ptr(scratch_ml), _ptr(counters), tc_min if tc_longest else 0, _stream(),
         )
         add_launches((max_rows_large > 0) + (small > 0) - 1)
         _check(code, "paged_attention (tensor cores)")

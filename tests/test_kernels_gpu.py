@@ -246,6 +246,67 @@ def test_paged_attention_long_portions_bfloat16(H, KV, D, page_size, window, gen
     torch.testing.assert_close(got.float(), want.float(), **tol(torch.bfloat16))
 
 
+def _filled(ctx_lens, KV, D, page_size, seed, key_scale=1.0):
+    pool, table, keys, values = make_cache(ctx_lens, KV, D, page_size, torch.bfloat16, seed=seed)
+    filled = torch.zeros_like(pool)
+    for r, (k, v) in enumerate(zip(keys, values)):
+        j = torch.arange(k.shape[0], device=DEV)
+        page = table[r].long()[j // page_size]
+        filled[page, 0, :, j % page_size] = (k * key_scale).to(torch.bfloat16)
+        filled[page, 1, :, j % page_size] = v.to(torch.bfloat16)
+    return filled, table, keys, values
+
+
+@pytest.mark.parametrize("H,KV,page_size,window", [(32, 4, 16, None), (8, 8, 8, None), (6, 2, 32, 200), (4, 1, 64, 64), (2, 2, 16, 1),
+                                                   (3, 1, 16, 129)])
+def test_paged_attention_tcgen05_portions(H, KV, page_size, window, monkeypatch):
+    """Portions of 128 tokens and more at head size 64 run on tcgen05 (128-token tiles of one head, 64 keys a
+    time): whole prompts of exactly one and two tiles, portions behind hundreds of cached tokens, ragged ends,
+    windows that end inside a tile, beside short portions and decode tokens that take the other kernels."""
+    D = 64
+    ctx_lens, q_lens = [128, 700, 1700, 129, 5, 256, 40], [128, 572, 1000, 129, 1, 256, 40]
+    pool, table, _, _ = _filled(ctx_lens, KV, D, page_size, seed=31)
+    ctx = step_ctx(ctx_lens, q_lens)
+    q = rnd(sum(q_lens), (H + 2 * KV) * D, dtype=torch.bfloat16, seed=97)
+    kw = dict(num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5, window=window)
+    launched = {}
+    real = ops()._launch
+
+    def recording(name, *a):
+        launched[name] = real(name, *a)
+        return launched[name]
+
+    monkeypatch.setattr(ops(), "_launch", recording)
+    got = ops().paged_attention(q, pool, table, ctx, **kw)
+    assert launched == {"llm_attention_tcgen05": 0, "llm_attention_mma_routed": 0}
+    ops().check_device_errors()
+    want = plain_ops.paged_attention(q, pool, table, ctx, **kw)
+    torch.testing.assert_close(got.float(), want.float(), **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("far_key", [0, 63, 64, 499, 500, 563, 564, 627, 628, 899])
+def test_paged_attention_tcgen05_finds_one_far_key(far_key):
+    """A portion of 400 tokens behind 500 cached ones; one key is made to match every query.  Every token at or
+    behind that key must return the key's value, whichever tile, page or stage of the ring the key lies in."""
+    H, KV, D, page_size, n, q_len = 4, 2, 64, 16, 900, 400
+    pool, table, keys, values = make_cache([n], KV, D, page_size, torch.bfloat16, seed=3)
+    direction = torch.nn.functional.normalize(rnd(D, seed=6), dim=0)
+    keys[0][:] = keys[0] * 0.05
+    keys[0][far_key] = direction * 24
+    fill_pool(pool, table, keys, values, page_size)
+    q = rnd(q_len, H * D, dtype=torch.bfloat16, seed=5, std=0.1)
+    q.view(q_len, H, D)[:] = (direction * 24).to(torch.bfloat16)
+    ctx = step_ctx([n], [q_len])
+    kw = dict(num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5)
+    got = ops().paged_attention(q, pool, table, ctx, **kw).float()
+    ops().check_device_errors()
+    first = max(0, far_key - (n - q_len))  # the first token of the portion that sees the key
+    want = values[0][far_key].to(torch.bfloat16).float().repeat_interleave(H // KV, dim=0).reshape(1, H * D)
+    torch.testing.assert_close(got[first:], want.expand(q_len - first, -1), atol=2e-2, rtol=2e-2)
+    plain = plain_ops.paged_attention(q, pool, table, ctx, **kw).float()
+    torch.testing.assert_close(got, plain, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("far_key,n", [(0, 701), (15, 701), (16, 701), (511, 701), (512, 701), (700, 701), (0, 2101), (1023, 2101),
                                        (1024, 2101), (2100, 2101)])
