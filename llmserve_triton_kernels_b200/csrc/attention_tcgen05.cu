@@ -10,12 +10,12 @@
 //               the layout the next product reads, and folds the product's result into the 64 output
 //               values it keeps in registers (rescaled by the change of the maximum).
 //   warp 4    : producer.  Looks up pages (32 entries of the page table per load, handed round by
-//               shuffles) and issues one TMA box per page for keys and one for values into a ring of
-//               STAGES tiles.
+//               shuffles) and issues one TMA box per page for keys and one for values, each from a lane
+//               of its own, into a ring of STAGES tiles.
 //   warp 5    : one thread issues the products; the warp owns the allocation of tensor memory.
-// The scores of tile j+1 are computed while the softmax of tile j runs (the issuer needs only to know
-// that the scores of tile j have been read); two CTAs share an SM, so that one's softmax overlaps the
-// other's products.  Softmax, running sums and the output are 32-bit; probabilities are rounded to
+// Scores and probabilities have two buffers each: the scores of tile j+1 are computed while the softmax of
+// tile j runs, and the second product of tile j runs while the softmax of tile j+1 does (its result is
+// folded into the output one tile late).  Two CTAs share an SM.  Softmax, running sums and the output are 32-bit; probabilities are rounded to
 // bfloat16 for the second product, as in the mma.sync kernel.
 //
 // Keys past a request's length inside its last page, and pages outside the range a CTA needs, are
@@ -33,9 +33,9 @@ namespace {
 
 using attn::AttnParams;
 
-constexpr int BM = 128, BN = 64, HD = 64, STAGES = 4, THREADS = 192;
+constexpr int BM = 128, BN = 64, HD = 64, STAGES = 3, THREADS = 192;
 constexpr int Q_BYTES = BM * HD * 2, P_BYTES = BM * BN * 2, K_BYTES = BN * HD * 2, STAGE_BYTES = 2 * K_BYTES;
-constexpr int TMEM_COLS = 128;  // scores in columns [0, 64), the second product's result in [64, 128)
+constexpr int TMEM_COLS = 256;  // two tiles of scores in columns [0, 64) and [64, 128), the second product's result in [128, 192)
 
 struct TcParams {
     AttnParams a;
@@ -69,8 +69,8 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
     unsigned char* p_s = base + Q_BYTES;
-    unsigned char* kv_s = p_s + P_BYTES;  // [STAGES][keys | values]
-    __shared__ __align__(8) unsigned long long q_full, kv_full[STAGES], kv_empty[STAGES], s_full, s_empty, p_full, o_full;
+    unsigned char* kv_s = p_s + 2 * P_BYTES;  // [STAGES][keys | values]; before it, two tiles of probabilities
+    __shared__ __align__(8) unsigned long long q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], s_empty[2], p_full[2], o_full;
     __shared__ unsigned tmem_base;
     __shared__ int gave_up;
 
@@ -82,9 +82,12 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             tma::mbar_init(&kv_full[s], 1);
             tma::mbar_init(&kv_empty[s], 1);
         }
-        tma::mbar_init(&s_full, 1);
-        tma::mbar_init(&s_empty, 4);
-        tma::mbar_init(&p_full, 4);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            tma::mbar_init(&s_full[b], 1);
+            tma::mbar_init(&s_empty[b], 4);
+            tma::mbar_init(&p_full[b], 4);
+        }
         tma::mbar_init(&o_full, 1);
         gave_up = 0;
         tma::mbar_fence_init();
@@ -115,46 +118,45 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             tma::mbar_expect_tx(&q_full, Q_BYTES);
             tma::load_2d(q_s, &qmap, head * HD, q_begin + row0, &q_full);
         }
-        const int first_page = t_begin * pages_per_tile, total_pages = n_tiles * pages_per_tile;
+        // One box per page and per kind (keys, values): 2 * pages_per_tile boxes a tile, each issued by a lane of
+        // its own (a thread's TMA instructions follow one another slowly; several threads' overlap).  The page
+        // table is read 32 entries at a time; a page outside the needed range is replaced by one inside it.
+        const int first_page = t_begin * pages_per_tile;
+        int my_page = 0, loaded_from = -32;
         bool alive = true;
-        for (int pg0 = 0; pg0 < total_pages && alive; pg0 += 32) {
-            // 32 entries of the page table at once; a page outside the needed range is replaced by one inside it
-            const int lp = min(max(first_page + pg0 + lane, lp_lo), lp_hi);
-            const int my_page = table[lp];
-            const int n_here = min(32, total_pages - pg0);
-            for (int i = 0; i < n_here && alive; ++i) {
-                const int page = __shfl_sync(0xffffffffu, my_page, i);
-                const int idx = pg0 + i, j = idx / pages_per_tile, in_tile = idx - j * pages_per_tile, s = j % STAGES;
-                if (lane == 0) {
-                    if (in_tile == 0) {
-                        if (gave_up || (j >= STAGES && !tma::mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1))) {
-                            if (!gave_up) fail();
-                            alive = false;
-                        } else {
-                            tma::mbar_expect_tx(&kv_full[s], STAGE_BYTES);
-                        }
-                    }
-                    if (alive) {
-                        unsigned char* k_dst = kv_s + (size_t)s * STAGE_BYTES + (size_t)in_tile * ps * (HD * 2);
-                        const int row_k = ((page * 2) * p.KV + kvh) * ps, row_v = ((page * 2 + 1) * p.KV + kvh) * ps;
-                        tma::load_2d(k_dst, &kvmap, 0, row_k, &kv_full[s]);
-                        tma::load_2d(k_dst + K_BYTES, &kvmap, 0, row_v, &kv_full[s]);
-                    }
+        for (int j = 0; j < n_tiles && alive; ++j) {
+            const int s = j % STAGES, idx0 = j * pages_per_tile;
+            if (idx0 >= loaded_from + 32) {  // pages_per_tile divides 32: a tile's pages lie in one batch
+                loaded_from = idx0;
+                my_page = table[min(max(first_page + idx0 + lane, lp_lo), lp_hi)];
+            }
+            if (lane == 0) {
+                if (gave_up || (j >= STAGES && !tma::mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1))) {
+                    if (!gave_up) fail();
+                    alive = false;
+                } else {
+                    tma::mbar_expect_tx(&kv_full[s], STAGE_BYTES);
                 }
-                alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
+            }
+            alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
+            const int in_tile = lane >> 1, is_v = lane & 1;
+            const int page = __shfl_sync(0xffffffffu, my_page, (idx0 - loaded_from + in_tile) & 31);
+            if (alive && in_tile < pages_per_tile) {
+                unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (size_t)is_v * K_BYTES + (size_t)in_tile * ps * (HD * 2);
+                tma::load_2d(dst, &kvmap, 0, ((page * 2 + is_v) * p.KV + kvh) * ps, &kv_full[s]);
             }
         }
     } else if (warp == 5) {
         // ---- issuer of the products ----
         if (lane == 0) {
             constexpr unsigned IDESC_QK = umma::idesc_bf16(BM, BN, false), IDESC_PV = umma::idesc_bf16(BM, HD, true);
-            const unsigned s_tmem = tmem_base, o_tmem = tmem_base + BN;
-            const unsigned long long q_desc = umma::desc_sw128(q_s), p_desc = umma::desc_sw128(p_s);
-            auto scores = [&](int j) {  // S = Q K_j^T
+            const unsigned o_tmem = tmem_base + 2 * BN;
+            const unsigned long long q_desc = umma::desc_sw128(q_s);
+            auto scores = [&](int j) {  // S[j % 2] = Q K_j^T
                 const unsigned long long k_desc = umma::desc_sw128(kv_s + (size_t)(j % STAGES) * STAGE_BYTES);
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) umma::mma_bf16(s_tmem, q_desc + 2 * k, k_desc + 2 * k, IDESC_QK, k != 0);
-                umma::commit(&s_full);
+                for (int k = 0; k < HD / 16; ++k) umma::mma_bf16(tmem_base + (j & 1) * BN, q_desc + 2 * k, k_desc + 2 * k, IDESC_QK, k != 0);
+                umma::commit(&s_full[j & 1]);
             };
             bool ok = tma::mbar_wait(&q_full, 0) && tma::mbar_wait(&kv_full[0], 0);
             if (ok) {
@@ -164,16 +166,18 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             for (int j = 0; j < n_tiles && ok && !gave_up; ++j) {
                 const int s = j % STAGES;
                 if (j + 1 < n_tiles) {
-                    // the scores of the next tile, as soon as those of this one have been read
-                    ok = tma::mbar_wait(&s_empty, j & 1) && tma::mbar_wait(&kv_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1);
+                    // the scores of the next tile, as soon as its keys are there and the scores two tiles back have been read
+                    ok = tma::mbar_wait(&kv_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1) &&
+                         (j < 1 || tma::mbar_wait(&s_empty[(j + 1) & 1], (((j + 1) >> 1) - 1) & 1));
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     scores(j + 1);
                 }
-                ok = tma::mbar_wait(&p_full, j & 1);
+                ok = tma::mbar_wait(&p_full[j & 1], (j >> 1) & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 // the values lie [key][d]: B with N contiguous; 16 keys are two atoms of 8 rows, 2048 bytes further per step
+                const unsigned long long p_desc = umma::desc_sw128(p_s + (size_t)(j & 1) * P_BYTES);
                 const unsigned long long v_desc = umma::desc_sw128(kv_s + (size_t)s * STAGE_BYTES + K_BYTES, 1024 >> 4);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) umma::mma_bf16(o_tmem, p_desc + 2 * k, v_desc + (2048 >> 4) * k, IDESC_PV, k != 0);
@@ -192,32 +196,47 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
         float o[HD];
 #pragma unroll
         for (int i = 0; i < HD; ++i) o[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
         bool ok = true;
+        // the result of the second product of tile j is folded into the output one tile later, after the
+        // probabilities of tile j + 1 have been computed: the product runs meanwhile
+        auto fold = [&](int j) -> bool {  // o = o * alpha_j + P_j V_j
+            if (!__all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, j & 1))) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            static_assert(HD == 64, "the product's result is read with one 64-column load");
+            float pv[HD];
+            umma::tmem_ld64(lane_base + 2 * BN, pv);
+#pragma unroll
+            for (int i = 0; i < HD; ++i) o[i] = fmaf(o[i], alpha_prev, pv[i]);
+            return true;
+        };
         for (int j = 0; j < n_tiles; ++j) {
             const int key_base = (t_begin + j) * BN;
-            ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&s_full, j & 1));
+            ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&s_full[j & 1], (j >> 1) & 1));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const bool whole = key_base + BN - 1 <= tile_pos_min && key_base >= tile_lo_max && rows_here == BM;
             // the keys of this tile that the row sees are those with index (within the tile) in [see_lo, see_hi]
             const int see_lo = row_ok ? lo - key_base : BN, see_hi = row_ok ? pos - key_base : -1;
-            // first pass over the scores: the row's maximum (four chains, so that the comparisons do not wait for
-            // one another; the scale is positive and is applied to the maximum alone)
+            // the row's 64 scores in one load; once they are in registers the buffer may take the scores two tiles on
+            static_assert(BN == 64, "the softmax reads a tile's scores with one 64-column load");
+            float v[BN];
+            umma::tmem_ld64(lane_base + (j & 1) * BN, v);
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[j & 1]);
+            // the row's maximum (four chains, so that the comparisons do not wait for one another; the scale is
+            // positive and is applied to the maximum alone)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (whole) {
 #pragma unroll
-            for (int h = 0; h < BN / 32; ++h) {
-                float v[32];
-                umma::tmem_ld32(lane_base + h * 32, v);
-                if (whole) {
+                for (int i = 0; i < BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const bool visible = h * 32 + i >= see_lo && h * 32 + i <= see_hi;
-                        mx4[i & 3] = fmaxf(mx4[i & 3], visible ? v[i] : -INFINITY);
-                    }
+                for (int i = 0; i < BN; ++i) {
+                    const bool visible = i >= see_lo && i <= see_hi;
+                    v[i] = visible ? v[i] : -INFINITY;
+                    mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
                 }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
@@ -225,57 +244,36 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = attn::fast_exp2(m_run - m_use);
             m_run = m_new;
-            // second pass: the probabilities, into shared memory as the second product's A (K-major, 128-byte
-            // swizzle: row `row`, 16-byte piece c at c ^ (row % 8))
+            // the probabilities (a masked score is -inf: its probability is exactly 0), into shared memory as the
+            // second product's A (K-major, 128-byte swizzle: row `row`, 16-byte piece c at c ^ (row % 8))
+            unsigned char* p_tile = p_s + (size_t)(j & 1) * P_BYTES;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             const float shift = -m_use;
 #pragma unroll
-            for (int h = 0; h < BN / 32; ++h) {
-                float v[32];
-                umma::tmem_ld32(lane_base + h * 32, v);
-                if (whole) {
+            for (int c = 0; c < BN / 8; ++c) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = attn::fast_exp2(fmaf(v[i], p.scale_log2, shift));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const bool visible = h * 32 + i >= see_lo && h * 32 + i <= see_hi;
-                        v[i] = visible ? attn::fast_exp2(fmaf(v[i], p.scale_log2, shift)) : 0.f;
-                    }
+                for (int i = 0; i < 8; ++i) {
+                    v[c * 8 + i] = attn::fast_exp2(fmaf(v[c * 8 + i], p.scale_log2, shift));
+                    sum4[i & 3] += v[c * 8 + i];
                 }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sum4[i & 3] += v[i];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint4 u;
-                    u.x = attn::pack_bf16(v[c * 8], v[c * 8 + 1]);
-                    u.y = attn::pack_bf16(v[c * 8 + 2], v[c * 8 + 3]);
-                    u.z = attn::pack_bf16(v[c * 8 + 4], v[c * 8 + 5]);
-                    u.w = attn::pack_bf16(v[c * 8 + 6], v[c * 8 + 7]);
-                    *reinterpret_cast<uint4*>(p_s + row * 128 + (((h * 4 + c) ^ (row & 7)) << 4)) = u;
-                }
+                uint4 u;
+                u.x = attn::pack_bf16(v[c * 8], v[c * 8 + 1]);
+                u.y = attn::pack_bf16(v[c * 8 + 2], v[c * 8 + 3]);
+                u.z = attn::pack_bf16(v[c * 8 + 4], v[c * 8 + 5]);
+                u.w = attn::pack_bf16(v[c * 8 + 6], v[c * 8 + 7]);
+                *reinterpret_cast<uint4*>(p_tile + row * 128 + ((c ^ (row & 7)) << 4)) = u;
             }
-            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            l_run = l_run * alpha + sum;
-            // the scores have been read (the next tile's may overwrite them) and the probabilities are written
+            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            // the tile before: its product has had this tile's softmax to finish in; its result must be read before
+            // the issuer learns of this tile's probabilities (the next product overwrites the result)
+            if (j > 0 && !(ok = fold(j - 1))) break;
+            alpha_prev = alpha;
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&s_empty);
-                mbar_arrive(&p_full);
-            }
-            ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, j & 1));
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-            for (int h = 0; h < HD / 32; ++h) {
-                float v[32];
-                umma::tmem_ld32(lane_base + BN + h * 32, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[h * 32 + i] = o[h * 32 + i] * alpha + v[i];
-            }
+            if (lane == 0) mbar_arrive(&p_full[j & 1]);
         }
+        if (ok && n_tiles > 0) ok = fold(n_tiles - 1);
         if (!ok) {
             if (lane == 0) fail();
         } else if (row_ok) {
@@ -347,7 +345,7 @@ LLM_EXPORT int llm_attention_tcgen05(const void* q, int q_stride, void* out, int
     tp.error_flag = error_flag;
     const long long y = (long long)requests * tp.tiles_per_request;
     if (y > 65535) return LLM_ERR_UNSUPPORTED;
-    constexpr size_t smem = 1024 + Q_BYTES + P_BYTES + (size_t)STAGES * STAGE_BYTES;
+    constexpr size_t smem = 1024 + Q_BYTES + 2 * P_BYTES + (size_t)STAGES * STAGE_BYTES;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
