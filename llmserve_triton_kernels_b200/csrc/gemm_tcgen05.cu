@@ -2,7 +2,7 @@
 // many rows (prompt portions): operands staged in shared memory by TMA, accumulators in tensor
 // memory, read back with tcgen05.ld for the epilogue.
 //
-// One CTA computes one 128 x BN tile of y.  Three roles, chosen by warp:
+// One CTA per SM walks 128 x BN tiles of y (tile t, t + CTAs, ...).  Three roles, chosen by warp:
 //   warp 0, one thread : TMA producer — fills a ring of STAGES slots with a 128 x 64 tile of x and a
 //                        BN x 64 tile of w (two of them in MODE_SWIGLU: the gate's and the up's rows
 //                        of the same features), 128-byte swizzled, and arms the slot's mbarrier;
@@ -12,6 +12,8 @@
 //                        allocation of tensor memory;
 //   warps 2-5          : epilogue — each warp reads its 32 lanes of the accumulator, 32 columns at a
 //                        time, and writes bfloat16 or float32 rows (MODE_SWIGLU: silu(gate) * up).
+// Tensor memory holds two accumulators: the epilogue of a tile runs while the products of the CTA's next
+// tile fill the other one, and the producer runs on into the next tile's k-blocks without a pause.
 // Rows and columns beyond the matrices arrive as zeros from TMA and are masked at the store; K may
 // be any multiple of 8.  Every mbarrier wait is bounded; a wait that gives up sets *error_flag, the
 // roles leave their loops, tensor memory is freed and the kernel returns.
@@ -72,21 +74,24 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     constexpr int NB = MODE == MODE_SWIGLU ? 2 : 1;           // w tiles per slot
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     constexpr int SLOT_BYTES = A_BYTES + NB * B_BYTES;
-    constexpr int TMEM_COLS = NB * BN <= 32 ? 32 : NB * BN <= 64 ? 64 : NB * BN <= 128 ? 128 : 256;  // a power of two
     // MODE_SWIGLU: the gate's and the up's tiles lie one after the other in the slot, which is one K-major tile of
     // 2 BN rows: one product of N = 2 BN fills columns [0, BN) with the gate's sums and [BN, 2 BN) with the up's
     constexpr int UMMA_N = NB * BN;
     static_assert(UMMA_N % 16 == 0 && UMMA_N >= 16 && UMMA_N <= 256, "tcgen05.mma with M = 128 takes N in steps of 16 up to 256");
+    // two accumulators, so that the epilogue of a tile runs under the products of the next one
+    constexpr int ACC_COLS = UMMA_N <= 32 ? 32 : UMMA_N <= 64 ? 64 : UMMA_N <= 128 ? 128 : 256;
+    constexpr int TMEM_COLS = 2 * ACC_COLS;
     constexpr unsigned IDESC = umma::idesc_bf16(BM, UMMA_N, false);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) unsigned long long full[STAGES], empty[STAGES], acc_ready;
+    __shared__ __align__(8) unsigned long long full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     __shared__ unsigned tmem_base;
     __shared__ int gave_up;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int kblocks = (p.K + BK - 1) / BK;
+    // tiles in row-major order of (column tile, row tile): CTAs that run at the same time share their w tiles
+    const int row_tiles = (p.M + BM - 1) / BM, col_tiles = (p.N + BN - 1) / BN, tiles = row_tiles * col_tiles;
 
     if (threadIdx.x == 0) {
 #pragma unroll
@@ -94,7 +99,11 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             tma::mbar_init(&full[s], 1);
             tma::mbar_init(&empty[s], 1);
         }
-        tma::mbar_init(&acc_ready, 1);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            tma::mbar_init(&acc_full[b], 1);
+            tma::mbar_init(&acc_empty[b], 4);
+        }
         gave_up = 0;
         tma::mbar_fence_init();
         tma::prefetch_map(&xmap);
@@ -116,49 +125,67 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     };
 
     if (warp == 0 && lane == 0) {
-        // ---- producer ----
-        for (int kb = 0; kb < kblocks && !gave_up; ++kb) {
-            const int s = kb % STAGES;
-            if (kb >= STAGES && !tma::mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) {
-                fail();
-                break;
+        // ---- producer: the k-blocks of all of this CTA's tiles, one after the other through the ring ----
+        int it = 0;
+        for (int tile = blockIdx.x; tile < tiles && !gave_up; tile += gridDim.x) {
+            const int m0 = (tile % row_tiles) * BM, n0 = (tile / row_tiles) * BN;
+            for (int kb = 0; kb < kblocks && !gave_up; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !tma::mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) {
+                    fail();
+                    break;
+                }
+                unsigned char* slot = ring + (size_t)s * SLOT_BYTES;
+                tma::mbar_expect_tx(&full[s], SLOT_BYTES);
+                tma::load_2d(slot, &xmap, kb * BK, m0, &full[s]);
+                tma::load_2d(slot + A_BYTES, &wmap, kb * BK, n0, &full[s]);
+                if (NB == 2) tma::load_2d(slot + A_BYTES + B_BYTES, &wmap, kb * BK, p.up_offset + n0, &full[s]);
             }
-            unsigned char* slot = ring + (size_t)s * SLOT_BYTES;
-            tma::mbar_expect_tx(&full[s], SLOT_BYTES);
-            tma::load_2d(slot, &xmap, kb * BK, m0, &full[s]);
-            tma::load_2d(slot + A_BYTES, &wmap, kb * BK, n0, &full[s]);
-            if (NB == 2) tma::load_2d(slot + A_BYTES + B_BYTES, &wmap, kb * BK, p.up_offset + n0, &full[s]);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- tensor-core issuer ----
-        const unsigned d_tmem = tmem_base;
-        for (int kb = 0; kb < kblocks && !gave_up; ++kb) {
-            const int s = kb % STAGES;
-            if (!tma::mbar_wait(&full[s], (kb / STAGES) & 1)) {
+        int it = 0, i = 0;
+        for (int tile = blockIdx.x; tile < tiles && !gave_up; tile += gridDim.x, ++i) {
+            const int buf = i & 1;
+            const unsigned d_tmem = tmem_base + buf * ACC_COLS;
+            if (i >= 2 && !tma::mbar_wait(&acc_empty[buf], ((i >> 1) - 1) & 1)) {  // the epilogue has read this accumulator
                 fail();
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const unsigned char* slot = ring + (size_t)s * SLOT_BYTES;
-            const unsigned long long a = umma::desc_sw128(slot), b = umma::desc_sw128(slot + A_BYTES);
+            for (int kb = 0; kb < kblocks && !gave_up; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!tma::mbar_wait(&full[s], (it / STAGES) & 1)) {
+                    fail();
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned char* slot = ring + (size_t)s * SLOT_BYTES;
+                const unsigned long long a = umma::desc_sw128(slot), b = umma::desc_sw128(slot + A_BYTES);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-                // 16 k = 32 bytes further along the 128-byte rows: the start address moves by two 16-byte units
-                umma::mma_bf16(d_tmem, a + 2 * k, b + 2 * k, IDESC, (kb | k) != 0);
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 k = 32 bytes further along the 128-byte rows: the start address moves by two 16-byte units
+                    umma::mma_bf16(d_tmem, a + 2 * k, b + 2 * k, IDESC, (kb | k) != 0);
+                }
+                umma::commit(&empty[s]);  // arrives when the products above have read the slot
             }
-            umma::commit(&empty[s]);  // arrives when the products above have read the slot
+            umma::commit(&acc_full[buf]);  // arrives when every product of the tile has landed in tensor memory
         }
-        umma::commit(&acc_ready);  // arrives when every product has landed in tensor memory
     } else if (warp >= 2) {
         // ---- epilogue: warp w may touch the 32 lanes (warp % 4) * 32 .. of tensor memory ----
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        const bool ok = __all_sync(0xffffffffu, tma::mbar_wait(&acc_ready, 0));
-        if (!ok) {
-            if (lane == 0) fail();
-        } else {
+        int i = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++i) {
+            const int buf = i & 1;
+            const int m0 = (tile % row_tiles) * BM, n0 = (tile / row_tiles) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            const bool ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&acc_full[buf], (i >> 1) & 1));
+            if (!ok) {
+                if (lane == 0) fail();
+                break;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const unsigned lane_base = tmem_base + ((unsigned)(quarter * 32) << 16);
+            const unsigned lane_base = tmem_base + buf * ACC_COLS + ((unsigned)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 float v[32];
@@ -167,12 +194,16 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                     float u[32];
                     umma::tmem_ld32(lane_base + BN + c, u);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * u[i];
+                    for (int j = 0; j < 32; ++j) v[j] = __fdividef(v[j], 1.f + __expf(-v[j])) * u[j];
                 }
                 const int col = n0 + c;
                 if (row < p.M && col < p.N)
                     store32<TO>(reinterpret_cast<TO*>(p.out) + (size_t)row * p.ldo + col, v, min(32, p.N - col));
             }
+            // this warp has read its lanes of the accumulator: the tile after next may overwrite them
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tma::mbar_arrive(&acc_empty[buf]);
         }
     }
     // everyone is done with tensor memory: the allocating warp gives it back
@@ -182,6 +213,16 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
     }
+}
+
+int sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0) count = 148;
+    }
+    return count;
 }
 
 template <int BN, int MODE, int STAGES, typename TO>
@@ -198,9 +239,10 @@ int launch(const void* x, int ldx, const void* w, int w_rows, const GemmParams& 
     const CUtensorMap* xmap = tma::cached_map_2d_bf16(x, p.M, p.K, ldx, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
     const CUtensorMap* wmap = tma::cached_map_2d_bf16(w, w_rows, p.K, p.K, BN, BK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (!xmap || !wmap) return LLM_ERR_UNSUPPORTED;
-    dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM);
-    if (grid.y > 65535) return LLM_ERR_UNSUPPORTED;
-    return launch_pdl(kernel, grid, dim3(THREADS), smem, stream, p, *xmap, *wmap);
+    const long long tiles = (long long)((p.N + BN - 1) / BN) * ((p.M + BM - 1) / BM);
+    if (tiles > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());  // one CTA per SM walks its share of the tiles
+    return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, p, *xmap, *wmap);
 }
 
 }  // namespace
