@@ -25,13 +25,24 @@ namespace {
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr int MODE_PLAIN = 0, MODE_SWIGLU = 1;
+constexpr int MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_RESIDUAL = 2;
 
 struct GemmParams {
     void* out;
     int M, N, K, ldo;
     int up_offset;  // MODE_SWIGLU: row of w where the up matrix starts
     int* error_flag;
+    // input in factored normalised form (see llm_linear_decode): x holds v * norm_weight, in_ss [in_parts, M] partial
+    // sums of v^2 per row; the product's rows are scaled by rsqrt(sum / K + in_eps).  Null: x is what it is.
+    const float* in_ss;
+    int in_parts;
+    float in_eps;
+    // MODE_RESIDUAL: the product is added to resid [M, N] (float32, in place); xw_out [M, N] = resid * norm_w in
+    // bfloat16 and ss_out [column tiles, M] = partial sums of resid^2 hand the stream on for the next norm
+    float* resid;
+    const float* norm_w;
+    __nv_bfloat16* xw_out;
+    float* ss_out;
 };
 
 template <typename TO>
@@ -186,20 +197,60 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
             }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const unsigned lane_base = tmem_base + buf * ACC_COLS + ((unsigned)(quarter * 32) << 16);
+            float row_scale = 1.f;
+            if (p.in_ss && row < p.M) {
+                float sum = 0.f;
+                for (int part = 0; part < p.in_parts; ++part) sum += p.in_ss[(size_t)part * p.M + row];  // a fixed order
+                row_scale = rsqrtf(sum / (float)p.K + p.in_eps);
+            }
+            float squares = 0.f;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 float v[32];
                 umma::tmem_ld32(lane_base + c, v);
+                const int col = n0 + c;
                 if (MODE == MODE_SWIGLU) {
                     float u[32];
                     umma::tmem_ld32(lane_base + BN + c, u);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __fdividef(v[j], 1.f + __expf(-v[j])) * u[j];
+                    for (int j = 0; j < 32; ++j) {
+                        const float g = v[j] * row_scale;
+                        v[j] = __fdividef(g, 1.f + __expf(-g)) * (u[j] * row_scale);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] *= row_scale;
                 }
-                const int col = n0 + c;
-                if (row < p.M && col < p.N)
+                if (row >= p.M || col >= p.N) continue;
+                if constexpr (MODE == MODE_RESIDUAL) {
+                    // the stream's row of this thread, 32 columns at a time (N is a multiple of 8: whole 16-byte pieces)
+                    float* rrow = p.resid + (size_t)row * p.N + col;
+                    __nv_bfloat16* xrow = p.xw_out + (size_t)row * p.N + col;
+                    const int valid = min(32, p.N - col);
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (j >= valid) continue;
+                        float4 r0 = *reinterpret_cast<const float4*>(rrow + j), r1 = *reinterpret_cast<const float4*>(rrow + j + 4);
+                        const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + col + j), w1 = *reinterpret_cast<const float4*>(p.norm_w + col + j + 4);
+                        r0.x += v[j]; r0.y += v[j + 1]; r0.z += v[j + 2]; r0.w += v[j + 3];
+                        r1.x += v[j + 4]; r1.y += v[j + 5]; r1.z += v[j + 6]; r1.w += v[j + 7];
+                        *reinterpret_cast<float4*>(rrow + j) = r0;
+                        *reinterpret_cast<float4*>(rrow + j + 4) = r1;
+                        squares += r0.x * r0.x + r0.y * r0.y + r0.z * r0.z + r0.w * r0.w + r1.x * r1.x + r1.y * r1.y + r1.z * r1.z + r1.w * r1.w;
+                        uint4 out;
+                        __nv_bfloat162 a = __floats2bfloat162_rn(r0.x * w0.x, r0.y * w0.y), b = __floats2bfloat162_rn(r0.z * w0.z, r0.w * w0.w);
+                        __nv_bfloat162 c2 = __floats2bfloat162_rn(r1.x * w1.x, r1.y * w1.y), d = __floats2bfloat162_rn(r1.z * w1.z, r1.w * w1.w);
+                        out.x = *reinterpret_cast<unsigned*>(&a);
+                        out.y = *reinterpret_cast<unsigned*>(&b);
+                        out.z = *reinterpret_cast<unsigned*>(&c2);
+                        out.w = *reinterpret_cast<unsigned*>(&d);
+                        *reinterpret_cast<uint4*>(xrow + j) = out;
+                    }
+                } else {
                     store32<TO>(reinterpret_cast<TO*>(p.out) + (size_t)row * p.ldo + col, v, min(32, p.N - col));
+                }
             }
+            if (MODE == MODE_RESIDUAL && row < p.M) p.ss_out[(size_t)(tile / row_tiles) * p.M + row] = squares;
             // this warp has read its lanes of the accumulator: the tile after next may overwrite them
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
@@ -247,15 +298,22 @@ int launch(const void* x, int ldx, const void* w, int w_rows, const GemmParams& 
 
 }  // namespace
 
+// How many partial sums of squares per row mode 2 writes for N features (its tiles are 256 columns wide).
+LLM_EXPORT int llm_gemm_tcgen05_parts(int N) { return (N + 255) / 256; }
+
 // bfloat16 x [M, K] (row stride ldx, a multiple of 8) times w^T (w contiguous [N or up_offset + N, K]).
 //   mode 0: out [M, N] (row stride ldo) in bfloat16 or float32.
 //   mode 1: w = [gate | up], the up rows starting at row up_offset; out [M, N] bfloat16 = silu(gate) * up.
-// Needs K a multiple of 8 and 16-byte aligned bases; otherwise LLM_ERR_UNSUPPORTED.
-LLM_EXPORT int llm_gemm_tcgen05(const void* x, int ldx, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
-                                int mode, int up_offset, int* error_flag, cudaStream_t stream) {
+//   mode 2: resid [M, N] (float32) += product; xw_out [M, N] = resid * norm_w (bfloat16); ss_out
+//           [llm_gemm_tcgen05_parts(N), M] = partial sums of resid^2.  out is not used; N a multiple of 8.
+// in_ss (or null): [in_parts, M] partial sums of squares of the rows that x was made from; the product's rows are
+// scaled by rsqrt(sum / K + in_eps).  Needs K a multiple of 8 and 16-byte aligned bases; otherwise LLM_ERR_UNSUPPORTED.
+LLM_EXPORT int llm_gemm_tcgen05_fused(const void* x, int ldx, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
+                                      int mode, int up_offset, const float* in_ss, int in_parts, float in_eps, float* resid,
+                                      const float* norm_w, void* xw_out, float* ss_out, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return LLM_ERR_UNSUPPORTED;
-    GemmParams p;
+    GemmParams p = {};
     p.out = out;
     p.M = M;
     p.N = N;
@@ -263,6 +321,18 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* x, int ldx, const void* w, void* out
     p.ldo = ldo;
     p.up_offset = up_offset;
     p.error_flag = error_flag;
+    p.in_ss = in_ss;
+    p.in_parts = in_ss ? in_parts : 0;
+    p.in_eps = in_eps;
+    if (mode == MODE_RESIDUAL) {
+        if (!resid || !norm_w || !xw_out || !ss_out) return LLM_ERR_BAD_ARGUMENT;
+        if ((N & 7) || ((uintptr_t)resid & 15) || ((uintptr_t)norm_w & 15) || ((uintptr_t)xw_out & 15)) return LLM_ERR_UNSUPPORTED;
+        p.resid = resid;
+        p.norm_w = norm_w;
+        p.xw_out = (__nv_bfloat16*)xw_out;
+        p.ss_out = ss_out;
+        return launch<256, MODE_RESIDUAL, 4, __nv_bfloat16>(x, ldx, w, N, p, stream);
+    }
     if (mode == MODE_SWIGLU) {
         if (out_dtype != LLM_BF16) return LLM_ERR_BAD_ARGUMENT;
         return launch<128, MODE_SWIGLU, 4, __nv_bfloat16>(x, ldx, w, up_offset + N, p, stream);
@@ -293,4 +363,11 @@ LLM_EXPORT int llm_gemm_tcgen05(const void* x, int ldx, const void* w, void* out
         return launch<128, MODE_PLAIN, 6, float>(x, ldx, w, N, p, stream);
     }
     return LLM_ERR_BAD_ARGUMENT;
+}
+
+LLM_EXPORT int llm_gemm_tcgen05(const void* x, int ldx, const void* w, void* out, int out_dtype, int M, int N, int K, int ldo,
+                                int mode, int up_offset, int* error_flag, cudaStream_t stream) {
+    if (mode != MODE_PLAIN && mode != MODE_SWIGLU) return LLM_ERR_BAD_ARGUMENT;
+    return llm_gemm_tcgen05_fused(x, ldx, w, out, out_dtype, M, N, K, ldo, mode, up_offset, nullptr, 0, 0.f, nullptr, nullptr, nullptr,
+                                  nullptr, error_flag, stream);
 }

@@ -32,6 +32,8 @@ _SIGNATURES = {
     "llm_decode_fused": [_i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                          _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_gemm_tcgen05": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "llm_gemm_tcgen05_fused": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp],
+    "llm_gemm_tcgen05_parts": [_i],
     "llm_attention_generic": [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
     "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "llm_attention_mma_routed": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
@@ -78,6 +80,7 @@ _TC_ATTENTION_ENABLED = True
 _TC_ATTENTION_HEAD_DIM = 64
 _TC_ATTENTION_PAGE_SIZES = (8, 16, 32, 64)
 _TC_ATTENTION_MIN_TOKENS = 128  # a request with at least this many tokens in the step: attention on tcgen05
+_TCGEN05_RESIDUAL_SINK = False  # see ResidualSink.usable
 _TCGEN05_MIN_ROWS = 128  # from this many rows a bfloat16 product runs on tcgen05 with TMA-fed tiles (own kernel)
 _DECODE_LINEAR_MAX_ROWS = 16  # up to this many rows a bfloat16 matrix product streams the weights once (own kernel)
 _FORCE_GENERIC_ATTENTION = False  # tests switch the tensor-core attention off to reach the general kernel in bfloat16
@@ -245,14 +248,34 @@ class ResidualSink:
 
     @staticmethod
     def usable(num_tokens: int, dtype: torch.dtype) -> bool:
-        return dtype == torch.bfloat16 and num_tokens <= _DECODE_LINEAR_MAX_ROWS
+        """Steps of few rows end their products this way (the weight-streaming kernel).  The tcgen05 kernel
+        for many rows can too (``linear`` below takes any row count), but its epilogue walks the stream one
+        row per thread, which costs more than the norm kernel it saves (5.87 ms against 5.43 ms for a prompt
+        of 2,048 tokens on a 1.1B model): steps of many rows run the norms as kernels of their own."""
+        return dtype == torch.bfloat16 and (num_tokens <= _DECODE_LINEAR_MAX_ROWS or
+                                            (_TCGEN05_RESIDUAL_SINK and num_tokens >= _TCGEN05_MIN_ROWS))
 
     def linear(self, x: torch.Tensor, w: torch.Tensor) -> "NormedInput | None":
         """``resid += x @ w^T``; returns the stream normalised for ``norm``, or None if the
         fused kernel refuses the shape (then nothing was changed)."""
         m, k = x.shape
         n = w.shape[0]
-        if not (x.dtype == torch.bfloat16 and m <= _DECODE_LINEAR_MAX_ROWS and x.stride(1) == 1 and w.is_contiguous()):
+        if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()):
+            return None
+        if m >= _TCGEN05_MIN_ROWS:
+            parts = library().llm_gemm_tcgen05_parts(n)
+            xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+            ss = torch.empty((parts, m), dtype=torch.float32, device=x.device)
+            code = _launch(
+                "llm_gemm_tcgen05_fused", _ptr(x), x.stride(0), _ptr(w), None, _BF16, m, n, k, n, 2, 0, None, 0, 0.0,
+                _ptr(self.resid), _ptr(self.weight), _ptr(xw), _ptr(ss), _error_flag_ptr(), _stream(),
+            )
+            if code == 10002:
+                add_launches(-1)
+                return None
+            _check(code, "linear into the residual stream (tcgen05)")
+            return NormedInput(xw, ss, self.eps, self.norm)
+        if m > _DECODE_LINEAR_MAX_ROWS:
             return None
         parts = -(-n // 16)
         xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
@@ -294,7 +317,10 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Te
     through the weight-streaming kernel, many through the vendor's library.  ``x`` may be a
     :class:`NormedInput`."""
     if isinstance(x, NormedInput):
-        out = _decode_linear(x, w, out_dtype or x.dtype, 0, w.shape[0])
+        if x.shape[0] >= _TCGEN05_MIN_ROWS:
+            out = _tcgen05_linear(x, w, out_dtype or x.dtype, 0, w.shape[0])
+        else:
+            out = _decode_linear(x, w, out_dtype or x.dtype, 0, w.shape[0])
         return out if out is not None else linear(x.materialize(), w, out_dtype)
     _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1], f"linear: shapes {tuple(x.shape)} and {tuple(w.shape)} do not match")
     _need(x.dtype == w.dtype, f"linear: operand types differ ({x.dtype}, {w.dtype})")
@@ -323,14 +349,18 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Te
 
 
 def _tcgen05_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):
-    """The tcgen05 + TMA product for many rows; None if it refuses the shape."""
-    m, k = x.shape
-    if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()):
+    """The tcgen05 + TMA product for many rows (``x`` a tensor or a :class:`NormedInput`); None if
+    it refuses the shape."""
+    scaled = isinstance(x, NormedInput)
+    xt = x.xw if scaled else x
+    m, k = xt.shape
+    if not (xt.dtype == torch.bfloat16 and xt.stride(1) == 1 and w.is_contiguous()):
         return None
-    out = torch.empty((m, n_out), dtype=out_dtype, device=x.device)
+    out = torch.empty((m, n_out), dtype=out_dtype, device=xt.device)
     code = _launch(
-        "llm_gemm_tcgen05", _ptr(x), x.stride(0), _ptr(w), _ptr(out), _code(out_dtype), m, n_out, k, n_out, mode, up_offset,
-        _error_flag_ptr(), _stream(),
+        "llm_gemm_tcgen05_fused", _ptr(xt), xt.stride(0), _ptr(w), _ptr(out), _code(out_dtype), m, n_out, k, n_out, mode,
+        up_offset, _ptr(x.ss) if scaled else None, x.ss.shape[0] if scaled else 0, x.eps if scaled else 0.0, None, None, None,
+        None, _error_flag_ptr(), _stream(),
     )
     if code == 10002:
         add_launches(-1)
@@ -474,7 +504,7 @@ def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
         out = _decode_linear(x, w_gate_up, torch.bfloat16, 1, inter, up_offset=inter)
         if out is not None:
             return out
-    if xt.dtype == torch.bfloat16 and xt.shape[0] >= _TCGEN05_MIN_ROWS and not isinstance(x, NormedInput):
+    if xt.dtype == torch.bfloat16 and xt.shape[0] >= _TCGEN05_MIN_ROWS:
         out = _tcgen05_linear(x, w_gate_up, torch.bfloat16, 1, inter, up_offset=inter)
         if out is not None:
             return out

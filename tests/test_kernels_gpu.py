@@ -107,7 +107,8 @@ def test_linear_swiglu_fused_for_few_rows(m, inter, k):
     torch.testing.assert_close(got.double(), want, atol=2e-2 * 0.05 * k**0.5, rtol=2e-2)
 
 
-@pytest.mark.parametrize("m,hidden,k,n_next", [(1, 2048, 5632, 2560), (8, 2048, 2048, 11264), (16, 96, 256, 40), (3, 72, 24, 172)])
+@pytest.mark.parametrize("m,hidden,k,n_next", [(1, 2048, 5632, 2560), (8, 2048, 2048, 11264), (16, 96, 256, 40), (3, 72, 24, 172),
+                                              (128, 96, 256, 40), (300, 2048, 5632, 2560), (2048, 2048, 2048, 11264), (131, 72, 24, 172)])
 def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
     """A product that adds into the residual stream and hands it on in factored normalised form,
     and the next product that consumes that form: together they must equal
