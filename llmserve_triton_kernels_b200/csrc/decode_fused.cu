@@ -63,6 +63,8 @@ struct FusedParams {
     int timeline_len;
 };
 
+// The teams' partial sums have room for two tiles of a team (2 x WARPS x 4 x 32 floats): the host's choice of warps
+// per tile keeps to that.
 struct Smem {
     __nv_bfloat16* ring;
     float* red;
@@ -316,10 +318,10 @@ LLM_EXPORT int llm_fused_layer_fill(void* dst, const void* w_in, const void* w_o
     L.slot_map = slot_map;
     L.window = window;
     L.scale_log2 = scale * 1.4426950408889634f;
-    L.group_in = choose_group(qkv_rows / 16, kblocks_of(hidden), grid);
-    L.group_out = choose_group((hidden + 15) / 16, kblocks_of(H * D), grid);
-    L.group_gate_up = choose_group((inter + 7) / 8, kblocks_of(hidden), grid);
-    L.group_down = choose_group((hidden + 15) / 16, kblocks_of(inter), grid);
+    L.group_in = choose_group(qkv_rows / 16, kblocks_of(hidden), grid, 2);
+    L.group_out = choose_group((hidden + 15) / 16, kblocks_of(H * D), grid, 2);
+    L.group_gate_up = choose_group((inter + 7) / 8, kblocks_of(hidden), grid, 2);
+    L.group_down = choose_group((hidden + 15) / 16, kblocks_of(inter), grid, 2);
     memcpy(dst, &L, sizeof L);
     return 0;
 }
@@ -379,7 +381,7 @@ LLM_EXPORT int llm_decode_fused(int M, int hidden, int H, int KV, int D, int int
     p.part_ml = part_ml;
     p.counters = counters;
     p.layers = (const FusedLayer*)layers;
-    p.group_head = choose_group((vocab + 15) / 16, kblocks_of(hidden), sm_count());
+    p.group_head = choose_group((vocab + 15) / 16, kblocks_of(hidden), sm_count(), 2);
     p.logits = logits;
     p.barrier = barrier;
     p.error_flag = error_flag;

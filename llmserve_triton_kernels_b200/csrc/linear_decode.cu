@@ -37,8 +37,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [WARPS][SLOTS][SLOT_ELEMS]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)WARPS * SLOTS * SLOT_ELEMS * 2);  // [2][WARPS][MT * 4][32]
-    __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(red + 2 * WARPS * MT * 4 * 32);  // [8 MT][K + X_PAD]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)WARPS * SLOTS * SLOT_ELEMS * 2);  // [tiles of a team][WARPS][MT * 4][32]
+    __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(red + p.red_floats);  // [8 MT][K + X_PAD]
     __shared__ float row_scale[8 * MT];
     __shared__ __align__(8) unsigned long long full[WARPS][SLOTS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,9 +110,16 @@ constexpr size_t SMEM_LIMIT = 227 * 1024;
 template <int MT, int MODE, typename TO>
 int launch(const LinearParams& p, cudaStream_t stream) {
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
-    const size_t smem = (size_t)WARPS * SLOTS * SLOT_ELEMS * 2 + (size_t)2 * WARPS * MT * 4 * 32 * sizeof(float) +
-                        (size_t)8 * MT * (p.K + X_PAD) * 2;
-    if (smem > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;  // x does not fit beside the rings
+    const int tiles = (p.N + FEATURES - 1) / FEATURES;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    LinearParams q = p;
+    const size_t fixed = (size_t)WARPS * SLOTS * SLOT_ELEMS * 2 + (size_t)8 * MT * (p.K + X_PAD) * 2;
+    if (fixed > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;  // x does not fit beside the rings
+    // as many tiles of a team may be shared as their partial sums find room for
+    const int room = (int)((SMEM_LIMIT - fixed) / ((size_t)WARPS * MT * 4 * 32 * sizeof(float)));
+    q.group = choose_group(tiles, (p.K + BOXK - 1) / BOXK, grid, room);
+    q.red_floats = (int)red_floats(tiles, grid, q.group, MT);
+    const size_t smem = fixed + (size_t)q.red_floats * sizeof(float);
     auto kernel = linear_decode_kernel<MT, MODE, TO>;
     static size_t configured = 0;  // per instantiation: the most dynamic shared memory asked for so far
     if (smem > configured) {
@@ -122,10 +129,6 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     }
     const CUtensorMap* map = weight_map(p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, MODE == MODE_QKV ? 8 : FEATURES);
     if (!map) return LLM_ERR_UNSUPPORTED;
-    const int tiles = (p.N + FEATURES - 1) / FEATURES;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
-    LinearParams q = p;
-    q.group = choose_group(tiles, (p.K + BOXK - 1) / BOXK, grid);
     return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, *map);
 }
 

@@ -40,6 +40,7 @@ struct LinearParams {
     float* ss_out;          // MODE_RESIDUAL: [tiles of 16 features, M]
     int* error_flag;        // set to 1 if a wait for a copy gave up (host-visible memory), or null
     int group;              // warps that share a tile: 1, 2, 4 or 8
+    int red_floats;         // floats of shared memory for the teams' partial sums (red_floats() below)
     // MODE_QKV: w rows are [H query heads | KV key heads | KV value heads] x D; out is [M, H * D]
     const int* positions;   // [M]
     const float* rotary;    // [positions, D] = cos | sin halves, or null (no rotation)
@@ -64,21 +65,31 @@ constexpr int MT_MAX = 2;  // 8-token tiles a product may carry
 
 // How many warps share a tile (1, 2, 4 or 8, splitting its k-blocks): the choice that leaves the busiest warp the
 // fewest boxes to stream.  The warps of a CTA form WARPS / g teams, team j of CTA b takes tiles b + j grid,
-// b + (j + WARPS / g) grid, ...; a shared tile costs its team a meeting in shared memory, counted as one and a half
-// boxes (measured: 8 rows x 11264 x 2048 takes 10.8 us with one warp per tile and 12.7 us with eight).
-inline int choose_group(int tiles, int kblocks, int grid) {
+// b + (j + WARPS / g) grid, ...; a team's warps put their partial sums into shared memory and meet once, when all of
+// the team's tiles are done; a shared tile is counted as SHARE_COST boxes more.
+constexpr float SHARE_COST = 1.0f;  // measured: 8 x 11264 x 2048 takes 10.8 us unshared, 10.9 us shared by 4 warps, 11.4 us by 8
+
+inline int choose_group(int tiles, int kblocks, int grid, int max_shared_tiles_each = 1 << 30) {
     int best = 1;
     float best_cost = 1e30f;
     for (int g = 1; g <= WARPS; g *= 2) {
         const int teams = grid * (WARPS / g);
         const int tiles_each = (tiles + teams - 1) / teams, boxes_each = (kblocks + g - 1) / g;
-        const float cost = (float)tiles_each * ((float)boxes_each + (g > 1 ? 1.5f : 0.f));
+        if (g > 1 && tiles_each > max_shared_tiles_each) continue;  // the partial sums' place in shared memory is limited
+        const float cost = (float)tiles_each * ((float)boxes_each + (g > 1 ? SHARE_COST : 0.f));
         if (cost < best_cost) {
             best_cost = cost;
             best = g;
         }
     }
     return best;
+}
+
+// Floats of shared memory the teams' partial sums need: a place per (tile of a team, warp) when tiles are shared.
+inline size_t red_floats(int tiles, int grid, int group, int MT) {
+    if (group <= 1) return 0;
+    const int teams = grid * (WARPS / group);
+    return (size_t)((tiles + teams - 1) / teams) * WARPS * MT * 4 * 32;
 }
 
 struct StreamState {
@@ -264,6 +275,98 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
 #pragma unroll
     for (int t = 0; t < MT; ++t) xrow[t] = x_s + (size_t)(8 * t + qr) * x_pitch + qc * 8;
 
+    // what happens to a complete tile
+    auto finish = [&](int ti, float (&acc)[MT][4]) {
+    const int tile = first + ti * stride, n0 = tile * FEATURES;
+    if constexpr (MODE == MODE_QKV) {
+        // this thread: lanes j (e = 0, 1) and j + D/2 (e = 2, 3) of one head for tokens 8 t + 2 qc and + 1:
+        // a rotation pair.  Query heads go to `out` rotated, key heads rotated into their page, value heads as
+        // they are into theirs.
+        const int D = p.D, half = D >> 1, per_head = D >> 4;
+        const int head = tile / per_head, j = (tile - head * per_head) * 8 + qr;
+#pragma unroll
+        for (int t = 0; t < MT; ++t)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int m = 8 * t + 2 * qc + i;
+                if (m >= M) continue;
+                float a = acc[t][i] * row_scale[m], b = acc[t][2 + i] * row_scale[m];
+                if (head < p.H + p.KV && p.rotary) {
+                    float c, sn;
+                    if (ti == 0 && st.early) {
+                        c = st.e_cos[t][i];
+                        sn = st.e_sin[t][i];
+                    } else {
+                        const int pos = min(max(p.positions[m], 0), p.rotary_rows - 1);
+                        c = p.rotary[(size_t)pos * D + j];
+                        sn = p.rotary[(size_t)pos * D + half + j];
+                    }
+                    const float ra = a * c - b * sn, rb = b * c + a * sn;
+                    a = ra;
+                    b = rb;
+                }
+                __nv_bfloat16* dst;
+                if (head < p.H) {
+                    dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + head * D + j;
+                } else {
+                    const int slot = ti == 0 && st.early ? st.e_slot[t][i] : p.slot_map[m];
+                    const int page = slot / p.page_size, off = slot - page * p.page_size;
+                    const int is_v = head >= p.H + p.KV, kvh = head - p.H - (is_v ? p.KV : 0);
+                    dst = p.pool + (((size_t)(page * 2 + is_v) * p.KV + kvh) * p.page_size + off) * D + j;
+                }
+                dst[0] = __float2bfloat16_rn(a);
+                dst[half] = __float2bfloat16_rn(b);
+            }
+    } else if constexpr (MODE == MODE_SWIGLU) {
+        // this thread: gate (e = 0, 1) and up (e = 2, 3) sums of feature qr for tokens 8 t + 2 qc and + 1
+        const int n = n0 + qr;
+#pragma unroll
+        for (int t = 0; t < MT; ++t)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int m = 8 * t + 2 * qc + j;
+                const float g = acc[t][j] * row_scale[m], u = acc[t][2 + j] * row_scale[m];
+                if (m < M && n < N) reinterpret_cast<TO*>(p.out)[(size_t)m * p.ldo + n] = from_float<TO>(g / (1.f + expf(-g)) * u);
+            }
+    } else {
+        // this thread: features qr (e = 0, 1) and qr + 8 (e = 2, 3) of tokens 8 t + 2 qc and + 1
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+            float sq[2] = {0.f, 0.f};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int n = n0 + qr + 8 * (e >> 1), m = 8 * t + 2 * qc + (e & 1);
+                const bool live = m < M && n < N;
+                const float s = acc[t][e] * row_scale[m];
+                if constexpr (MODE == MODE_RESIDUAL) {
+                    if (live) {
+                        const bool have = ti == 0 && st.early;
+                        const float before = have && p.resid_early ? st.e_resid[t][e] : p.resid[(size_t)m * N + n];
+                        const float v = before + s;
+                        p.resid[(size_t)m * N + n] = v;
+                        p.xw_out[(size_t)m * N + n] = __float2bfloat16_rn(v * (have ? st.e_norm[e >> 1] : p.norm_w[n]));
+                        sq[e & 1] += v * v;
+                    }
+                } else {
+                    if (live) reinterpret_cast<TO*>(p.out)[(size_t)m * p.ldo + n] = from_float<TO>(s);
+                }
+            }
+            if constexpr (MODE == MODE_RESIDUAL) {
+                // sum of v^2 over the tile's 16 features of a token: over the 8 lanes that share qc
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    float v = sq[j];
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    v += __shfl_xor_sync(0xffffffffu, v, 8);
+                    v += __shfl_xor_sync(0xffffffffu, v, 16);
+                    const int m = 8 * t + 2 * qc + j;
+                    if (qr == 0 && m < M) p.ss_out[(size_t)tile * M + m] = v;
+                }
+            }
+        }
+    }
+    };
+
     int unit = 0;
     for (int ti = 0; ti < my_tiles; ++ti) {
         // CHAINS independent sums per token tile, joined when the tile is complete: an MMA waits for the one before it
@@ -316,111 +419,32 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 for (int c = 1; c < CHAINS; ++c) sum += part[t][c][e];  // a fixed order
                 acc[t][e] = sum;
             }
-        if (group > 1) {
-            // the members' partial sums meet in shared memory (two buffers by tile parity: the first member may
-            // still be reading the tile before when the others write this one); the first member adds them up
-            float* buf = red + (size_t)(ti & 1) * WARPS * (MT * 4) * 32;
-            if (member != 0) {
-#pragma unroll
-                for (int t = 0; t < MT; ++t)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) buf[((size_t)warp * (MT * 4) + t * 4 + e) * 32 + lane] = acc[t][e];
-            }
-            asm volatile("bar.sync %0, %1;\n" ::"r"(1 + warp / group), "r"(group * 32) : "memory");
-            if (member != 0) continue;
-            for (int w2 = warp + 1; w2 < warp + group; ++w2)
-#pragma unroll
-                for (int t = 0; t < MT; ++t)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[t][e] += buf[((size_t)w2 * (MT * 4) + t * 4 + e) * 32 + lane];
-        }
-        // the tile is complete
-        const int tile = first + ti * stride, n0 = tile * FEATURES;
-        if constexpr (MODE == MODE_QKV) {
-            // this thread: lanes j (e = 0, 1) and j + D/2 (e = 2, 3) of one head for tokens 8 t + 2 qc and + 1:
-            // a rotation pair.  Query heads go to `out` rotated, key heads rotated into their page, value heads as
-            // they are into theirs.
-            const int D = p.D, half = D >> 1, per_head = D >> 4;
-            const int head = tile / per_head, j = (tile - head * per_head) * 8 + qr;
-#pragma unroll
-            for (int t = 0; t < MT; ++t)
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int m = 8 * t + 2 * qc + i;
-                    if (m >= M) continue;
-                    float a = acc[t][i] * row_scale[m], b = acc[t][2 + i] * row_scale[m];
-                    if (head < p.H + p.KV && p.rotary) {
-                        float c, sn;
-                        if (ti == 0 && st.early) {
-                            c = st.e_cos[t][i];
-                            sn = st.e_sin[t][i];
-                        } else {
-                            const int pos = min(max(p.positions[m], 0), p.rotary_rows - 1);
-                            c = p.rotary[(size_t)pos * D + j];
-                            sn = p.rotary[(size_t)pos * D + half + j];
-                        }
-                        const float ra = a * c - b * sn, rb = b * c + a * sn;
-                        a = ra;
-                        b = rb;
-                    }
-                    __nv_bfloat16* dst;
-                    if (head < p.H) {
-                        dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + head * D + j;
-                    } else {
-                        const int slot = ti == 0 && st.early ? st.e_slot[t][i] : p.slot_map[m];
-                        const int page = slot / p.page_size, off = slot - page * p.page_size;
-                        const int is_v = head >= p.H + p.KV, kvh = head - p.H - (is_v ? p.KV : 0);
-                        dst = p.pool + (((size_t)(page * 2 + is_v) * p.KV + kvh) * p.page_size + off) * D + j;
-                    }
-                    dst[0] = __float2bfloat16_rn(a);
-                    dst[half] = __float2bfloat16_rn(b);
-                }
-        } else if constexpr (MODE == MODE_SWIGLU) {
-            // this thread: gate (e = 0, 1) and up (e = 2, 3) sums of feature qr for tokens 8 t + 2 qc and + 1
-            const int n = n0 + qr;
-#pragma unroll
-            for (int t = 0; t < MT; ++t)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int m = 8 * t + 2 * qc + j;
-                    const float g = acc[t][j] * row_scale[m], u = acc[t][2 + j] * row_scale[m];
-                    if (m < M && n < N) reinterpret_cast<TO*>(p.out)[(size_t)m * p.ldo + n] = from_float<TO>(g / (1.f + expf(-g)) * u);
-                }
+        if (group == 1) {
+            finish(ti, acc);
         } else {
-            // this thread: features qr (e = 0, 1) and qr + 8 (e = 2, 3) of tokens 8 t + 2 qc and + 1
+            // the members' partial sums wait in shared memory, a place per (tile of the team, warp), until all of the
+            // team's tiles are done: the warps of a team meet once, not once per tile
 #pragma unroll
-            for (int t = 0; t < MT; ++t) {
-                float sq[2] = {0.f, 0.f};
+            for (int t = 0; t < MT; ++t)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int n = n0 + qr + 8 * (e >> 1), m = 8 * t + 2 * qc + (e & 1);
-                    const bool live = m < M && n < N;
-                    const float s = acc[t][e] * row_scale[m];
-                    if constexpr (MODE == MODE_RESIDUAL) {
-                        if (live) {
-                            const bool have = ti == 0 && st.early;
-                            const float before = have && p.resid_early ? st.e_resid[t][e] : p.resid[(size_t)m * N + n];
-                            const float v = before + s;
-                            p.resid[(size_t)m * N + n] = v;
-                            p.xw_out[(size_t)m * N + n] = __float2bfloat16_rn(v * (have ? st.e_norm[e >> 1] : p.norm_w[n]));
-                            sq[e & 1] += v * v;
-                        }
-                    } else {
-                        if (live) reinterpret_cast<TO*>(p.out)[(size_t)m * p.ldo + n] = from_float<TO>(s);
-                    }
-                }
-                if constexpr (MODE == MODE_RESIDUAL) {
-                    // sum of v^2 over the tile's 16 features of a token: over the 8 lanes that share qc
+                for (int e = 0; e < 4; ++e) red[(((size_t)ti * WARPS + warp) * (MT * 4) + t * 4 + e) * 32 + lane] = acc[t][e];
+        }
+    }
+    if (group > 1) {
+        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + warp / group), "r"(group * 32) : "memory");
+        if (member == 0) {
+            for (int ti = 0; ti < my_tiles; ++ti) {
+                float acc[MT][4];
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        float v = sq[j];
-                        v += __shfl_xor_sync(0xffffffffu, v, 4);
-                        v += __shfl_xor_sync(0xffffffffu, v, 8);
-                        v += __shfl_xor_sync(0xffffffffu, v, 16);
-                        const int m = 8 * t + 2 * qc + j;
-                        if (qr == 0 && m < M) p.ss_out[(size_t)tile * M + m] = v;
-                    }
-                }
+                for (int t = 0; t < MT; ++t)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+                for (int w2 = warp; w2 < warp + group; ++w2)  // a fixed order
+#pragma unroll
+                    for (int t = 0; t < MT; ++t)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) acc[t][e] += red[(((size_t)ti * WARPS + w2) * (MT * 4) + t * 4 + e) * 32 + lane];
+                finish(ti, acc);
             }
         }
     }
