@@ -52,9 +52,24 @@ class Request:
     finish_reason: str | None = None  # "stop" | "length" | "abort"
     num_preemptions: int = 0
 
+    _all: list[int] | None = field(default=None, repr=False, compare=False)
+
     @property
     def all_ids(self) -> list[int]:
-        return self.prompt_ids + self.generated
+        """Prompt and generated tokens as one list, kept up to date by :meth:`append` (the scheduler asks for it
+        many times a step: it is not rebuilt each time)."""
+        if self._all is None or len(self._all) != len(self.prompt_ids) + len(self.generated):
+            self._all = self.prompt_ids + self.generated
+        return self._all
+
+    @property
+    def num_ids(self) -> int:
+        return len(self.prompt_ids) + len(self.generated)
+
+    def append(self, token: int) -> None:
+        self.generated.append(token)
+        if self._all is not None:
+            self._all.append(token)
 
     @property
     def first_token_time(self) -> float | None:
@@ -195,13 +210,13 @@ class Scheduler:
         logits = self.step_function(entries)
         sampled = []
         for req, n in plan:
-            decoding = n == 1 and req.num_computed + 1 == len(req.all_ids) and req.generated and req.num_computed >= len(req.prompt_ids)
+            decoding = n == 1 and req.num_computed + 1 == req.num_ids and req.generated and req.num_computed >= len(req.prompt_ids)
             if decoding:
                 self.stats.decode_tokens += 1
             else:
                 self.stats.prefill_tokens += n
             req.num_computed += n
-            if req.num_computed == len(req.all_ids):
+            if req.num_computed == req.num_ids:
                 sampled.append(req)
         self.stats.last_batch_tokens = sum(n for _, n in plan)
         self.stats.last_batch_requests = len(plan)
@@ -229,7 +244,7 @@ class Scheduler:
             self._finish(req, "abort", events, emit_token=None)
 
     def _portion(self, req: Request, budget: int) -> int:
-        remaining = len(req.all_ids) - req.num_computed
+        remaining = req.num_ids - req.num_computed
         return min(remaining, budget, self.chunk_size)
 
     def _plan(self) -> list[tuple[Request, int]]:
@@ -240,7 +255,7 @@ class Scheduler:
         # decoding requests first (one token each), then portions of prompts, oldest first
         for pick_decodes in (True, False):
             for req in self.running:
-                is_decode = len(req.all_ids) - req.num_computed == 1
+                is_decode = req.num_ids - req.num_computed == 1
                 if is_decode != pick_decodes or budget == 0:
                     continue
                 n = self._portion(req, budget)
@@ -289,7 +304,7 @@ class Scheduler:
     def _append(self, reqs: list[Request], tokens: list[int], events: list[TokenEvent]) -> None:
         now = perf_counter()
         for r, tok in zip(reqs, tokens):
-            r.generated.append(int(tok))
+            r.append(int(tok))
             r.token_times.append(now)
             self.stats.tokens_generated += 1
             reason = None
