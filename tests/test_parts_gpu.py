@@ -283,6 +283,202 @@ def test_toy_architecture_with_a_stateful_mixer_is_registered_built_and_stepped(
         unregister_architecture("ToyForCausalLM")
 
 
+# ------------------------------------------------------------------ a second toy: routing, another position encoding, another norm
+@dataclass(frozen=True)
+class RoutedConfig:
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    num_heads: int
+    num_kv_heads: int
+    num_experts: int
+    slope: float
+    eps: float
+    max_positions: int
+    architecture = "RoutedToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: d[k] for k in cls.__dataclass_fields__})
+
+    def to_dict(self):
+        return {**asdict(self), "architectures": [self.architecture]}
+
+
+def register_routed_toy():
+    """Parts that the framework does not have, defined here: a feed-forward that routes every token to the one
+    expert its 32-bit router prefers (gated by the router's softmax), a position encoding without a table (queries
+    grow and keys shrink with the position, so that a score falls with the distance), and a norm that centres
+    before it scales.  Layer 0 has a dense feed-forward and rotary positions, layer 1 the routed one and the toy
+    positions: one model, different parts per layer."""
+    from llmserve_triton_kernels_b200 import ops
+    from llmserve_triton_kernels_b200.config import register_architecture
+    from llmserve_triton_kernels_b200.models.plan import LayerRun, LayerSpec, ModelPlan
+    from llmserve_triton_kernels_b200.parts import FeedForward, Norm, PartSpec, PositionEncoding, TensorSpec, register_part
+
+    class RoutedExperts(FeedForward):
+        def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int):
+            self.h, self.i, self.e = hidden_size, intermediate_size, num_experts
+
+        def tensors(self):
+            specs = {"router.weight": TensorSpec((self.e, self.h))}
+            for j in range(self.e):
+                specs[f"experts.{j}.gate_up.weight"] = TensorSpec((2 * self.i, self.h))
+                specs[f"experts.{j}.down.weight"] = TensorSpec((self.h, self.i))
+            return specs
+
+        def bind(self, tensors, dtype, device):
+            self.router = tensors["router.weight"].to(device=device, dtype=torch.float32)  # router logits are 32-bit
+            self.gate_up = [tensors[f"experts.{j}.gate_up.weight"].to(device=device, dtype=dtype).contiguous() for j in range(self.e)]
+            self.down = [tensors[f"experts.{j}.down.weight"].to(device=device, dtype=dtype).contiguous() for j in range(self.e)]
+            self.dtype = dtype
+
+        def forward(self, x, ctx):
+            probs = torch.softmax(x.float() @ self.router.t(), dim=-1)
+            weight, choice = probs.max(dim=-1)
+            out = torch.zeros((x.shape[0], self.h), dtype=torch.float32, device=x.device)
+            for j in range(self.e):  # the framework's own kernels do an expert's products
+                rows = torch.nonzero(choice == j).flatten()
+                if rows.numel():
+                    y = ops.linear(ops.linear_swiglu(x[rows].contiguous(), self.gate_up[j]), self.down[j], out_dtype=torch.float32)
+                    out[rows] = y * weight[rows, None]
+            return out.to(self.dtype)
+
+    class DistanceDecay(PositionEncoding):
+        def __init__(self, slope: float, max_positions: int):
+            self.slope, self.max_positions = slope, max_positions
+
+        def apply(self, q, k, positions):
+            f = torch.exp(self.slope * positions.float() / self.max_positions)
+            q.mul_(f[:, None, None].to(q.dtype))
+            if k.shape[1]:
+                k.mul_((1.0 / f)[:, None, None].to(k.dtype))
+
+    class CentredNorm(Norm):
+        def __init__(self, size: int, eps: float):
+            self.size, self.eps = size, eps
+
+        def tensors(self):
+            return {"weight": TensorSpec((self.size,), init="ones_plus_normal")}
+
+        def bind(self, tensors, dtype, device):
+            self.weight = tensors["weight"].to(device=device, dtype=torch.float32)
+            self.out_dtype = dtype
+
+        def forward(self, x, rows=None):
+            v = (x if rows is None else x[rows.long()]).float()
+            v = v - v.mean(-1, keepdim=True)
+            return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight).to(self.out_dtype)
+
+    register_part("feed_forward", "routed_experts", RoutedExperts)
+    register_part("position", "distance_decay", DistanceDecay)
+    register_part("norm", "centred_norm", CentredNorm)
+
+    def plan(cfg: RoutedConfig) -> ModelPlan:
+        D = cfg.hidden_size // cfg.num_heads
+        rms = {"size": cfg.hidden_size, "eps": cfg.eps}
+        positions = (PartSpec("rotary", {"head_dim": D, "theta": 10000.0, "max_positions": cfg.max_positions}),
+                     PartSpec("distance_decay", {"slope": cfg.slope, "max_positions": cfg.max_positions}))
+        feed_forwards = (PartSpec("gated_mlp", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size}, "model.layers.0.mlp."),
+                         PartSpec("routed_experts", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
+                                                     "num_experts": cfg.num_experts}, "model.layers.1.moe."))
+        layers = []
+        for i in range(2):
+            p = f"model.layers.{i}."
+            attention = PartSpec("attention", {"hidden_size": cfg.hidden_size, "num_heads": cfg.num_heads, "num_kv_heads": cfg.num_kv_heads,
+                                               "head_dim": D, "scale": D**-0.5, "position": positions[i]}, p + "self_attn.")
+            ff_norm = PartSpec("rms_norm", rms, p + "post_attention_layernorm.") if i == 0 else PartSpec("centred_norm", rms, p + "ff_norm.")
+            layers.append(LayerSpec(PartSpec("pre_norm"), PartSpec("rms_norm", rms, p + "input_layernorm."), attention, ff_norm, feed_forwards[i]))
+        return ModelPlan(cfg.hidden_size, cfg.vocab_size, cfg.max_positions, "model.embed_tokens.weight", tuple(layers),
+                         (LayerRun(0), LayerRun(1)), PartSpec("rms_norm", rms, "model.norm."), "lm_head.weight")
+
+    register_architecture("RoutedToyForCausalLM", RoutedConfig, plan)
+
+
+def routed_plain_forward(cfg: RoutedConfig, w, tokens):
+    """The routed toy on a whole sequence in plain torch; attention by plain_llama.attention_scores."""
+    H, KV, D = cfg.num_heads, cfg.num_kv_heads, cfg.hidden_size // cfg.num_heads
+    n = len(tokens)
+    pos = torch.arange(n)
+    x = w["model.embed_tokens.weight"][torch.as_tensor(tokens)]
+    for i in range(2):
+        p = f"model.layers.{i}."
+        h = plain_llama.rms_norm(x, w[p + "input_layernorm.weight"], cfg.eps)
+        q = (h @ w[p + "self_attn.q_proj.weight"].T).view(n, H, D).transpose(0, 1)
+        k = (h @ w[p + "self_attn.k_proj.weight"].T).view(n, KV, D).transpose(0, 1)
+        v = (h @ w[p + "self_attn.v_proj.weight"].T).view(n, KV, D).transpose(0, 1)
+        if i == 0:
+            cos, sin = plain_llama.rope_cos_sin(pos, D, 10000.0)
+            q, k = plain_llama.apply_rope(q, cos, sin), plain_llama.apply_rope(k, cos, sin)
+        else:
+            f = torch.exp(cfg.slope * pos.float() / cfg.max_positions)[None, :, None]
+            q, k = q * f, k / f
+        a = plain_llama.attention_scores(q, k, v, D**-0.5)
+        x = x + a.transpose(0, 1).reshape(n, H * D) @ w[p + "self_attn.o_proj.weight"].T
+        if i == 0:
+            x = x + plain_llama.swiglu_mlp(plain_llama.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg.eps), w, p + "mlp.")
+        else:
+            c = x - x.mean(-1, keepdim=True)
+            hn = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + cfg.eps) * w[p + "ff_norm.weight"]
+            probs = torch.softmax(hn @ w[p + "moe.router.weight"].T, dim=-1)
+            weight, choice = probs.max(-1)
+            y = torch.zeros_like(x)
+            for t in range(n):
+                j = int(choice[t])
+                gu = hn[t] @ w[p + f"moe.experts.{j}.gate_up.weight"].T
+                half = gu.shape[0] // 2
+                y[t] = weight[t] * ((torch.nn.functional.silu(gu[:half]) * gu[half:]) @ w[p + f"moe.experts.{j}.down.weight"].T)
+            x = x + y
+    return plain_llama.rms_norm(x, w["model.norm.weight"], cfg.eps) @ w["lm_head.weight"].T
+
+
+def test_toy_architecture_with_routing_another_position_encoding_and_another_norm(tmp_path):
+    """32-bit only: the toy router takes the larger of two softmax values, and a 16-bit rounding of its input
+    can turn a near tie; the point here is that the parts are registered, built, cached and stepped."""
+    from llmserve_triton_kernels_b200 import LLM, SamplingParams
+    from llmserve_triton_kernels_b200.config import unregister_architecture
+    from llmserve_triton_kernels_b200.engine.batch import StepEntry
+    from llmserve_triton_kernels_b200.weights import write_random_model
+
+    register_routed_toy()
+    try:
+        cfg = RoutedConfig(vocab_size=160, hidden_size=48, intermediate_size=40, num_heads=3, num_kv_heads=1, num_experts=3,
+                           slope=1.5, eps=1e-5, max_positions=80)
+        folder = write_random_model(tmp_path, cfg, seed=5, std=0.08, dtype=torch.float32)
+        _, w = plain_llama.read_model(folder)
+        assert "model.layers.1.moe.experts.2.down.weight" in w and "model.layers.1.ff_norm.weight" in w
+        llm = LLM(folder, dtype="float32", device=DEV, block_size=4, num_blocks=48, max_batch_size=2, max_num_batched_tokens=32, chunk_size=8)
+        a, b = tiny_configs.seeded_tokens(160, [37, 20], 77)
+        ref_a, ref_b = routed_plain_forward(cfg, w, a), routed_plain_forward(cfg, w, b)
+        step = llm.step_function
+        got_a, got_b = [], []
+        ia = ib = 0
+        for na, nb in ((9, 1), (2, 7), (13, 2), (1, 1), (12, 9)):
+            entries = []
+            ta, tb = a[ia : ia + na], b[ib : ib + nb]
+            if ta:
+                entries.append(StepEntry("a", ta, list(range(len(ta)))))
+            if tb:
+                entries.append(StepEntry("b", tb, list(range(len(tb)))))
+            out = step(entries).float().cpu()
+            got_a.append(out[: len(ta)])
+            got_b.append(out[len(ta) :])
+            ia, ib = ia + na, ib + nb
+        for got, ref in ((torch.cat(got_a), ref_a), (torch.cat(got_b), ref_b)):
+            assert got.shape == ref.shape
+            assert float((got - ref).abs().max()) <= 5e-5 * float(ref.abs().max())
+        llm.cache.free_request("a")
+        llm.cache.free_request("b")
+        llm.cache.check()
+        out = llm.generate([a[:11]], SamplingParams(max_new_tokens=5))[0]
+        tokens = list(a[:11])
+        for _ in range(5):
+            tokens.append(int(torch.argmax(routed_plain_forward(cfg, w, tokens)[-1])))
+        assert out.token_ids == tokens[11:]
+    finally:
+        unregister_architecture("RoutedToyForCausalLM")
+
+
 @pytest.mark.parametrize("dtype,storage,rtol", [("float32", torch.float32, 3e-5), ("bfloat16", torch.bfloat16, 3e-2)])
 def test_llama_parts_in_another_order_windows_repeats_and_shared_caches(dtype, storage, rtol, model_folder):
     """The Llama parts under an order that Llama does not have, against plain_llama.forward with the
