@@ -21,10 +21,10 @@ namespace {
 
 using namespace attn;
 
-// D: head size.  ROW_WARPS x KEY_WARPS = 4 warps.  BN: keys per warp and tile.  blockIdx: (split, key/value
+// D: head size.  ROW_WARPS x KEY_WARPS warps.  BN: keys per warp and tile.  blockIdx: (split, key/value
 // head, request * tiles_per_request + row tile).
 template <int D, int ROW_WARPS, int KEY_WARPS, int BN, int STAGES>
-__global__ void __launch_bounds__(THREADS) attention_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(32 * ROW_WARPS * KEY_WARPS) attention_mma_kernel(const AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     attention_tile<D, ROW_WARPS, KEY_WARPS, BN, STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z / p.tiles_per_request,
                                                 blockIdx.z % p.tiles_per_request, smem_raw, true);
@@ -63,14 +63,14 @@ int launch_shape(const AttnParams& p, int requests, cudaStream_t stream) {
     const size_t merge = (size_t)KEY_WARPS * 16 * (D + 2) * sizeof(float);
     if (KEY_WARPS > 1 && merge > smem) smem = merge;
     auto kernel = attention_mma_kernel<D, ROW_WARPS, KEY_WARPS, BN, STAGES>;
-    if (smem > 48 * 1024) {
+    if (smem > 40 * 1024) {  // with the kernel's static shared memory beside it, more than the 48 KB that need no opt-in
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     const long long z = (long long)requests * p.tiles_per_request;
     if (z > 65535 || p.KV > 65535) return LLM_ERR_UNSUPPORTED;
     dim3 grid(p.splits, p.KV, (unsigned)z);
-    return launch_pdl(kernel, grid, dim3(THREADS), smem, stream, p);
+    return launch_pdl(kernel, grid, dim3(32 * ROW_WARPS * KEY_WARPS), smem, stream, p);
 }
 
 template <int D>
@@ -86,7 +86,10 @@ int launch_all(AttnParams p, int requests, int n_tokens, const int* token_reques
     if (have_small) {
         p.splits = splits_small;
         p.tiles_per_request = 1;
-        code = launch_shape<D, 1, 4, 32, stages_of(D, 4)>(p, requests, stream);
+        // few rows: sixteen warps (eight for the largest head size) share the keys of a tile, 16 keys each, so that a
+        // tile is a short step for every warp; the warps' shares are merged through shared memory at the end
+        if constexpr (D <= 64) code = launch_shape<D, 1, 16, 16, 3>(p, requests, stream);
+        else code = launch_shape<D, 1, 8, 16, 3>(p, requests, stream);
         if (code) return code;
     }
     const int merge_small = 0, merge_large = max_rows_large > 0 && splits_large > 1;  // the small shape merges in place

@@ -8,13 +8,13 @@
 namespace attn {
 
 
-constexpr int THREADS = 128;
 constexpr int SMALL_ROWS = 16;  // requests with at most this many rows go to the KEYS shape
 constexpr int SMALL_MIN_TILES = 8;  // tiles (of 128 keys) a split of that shape takes at least
 
-// The 128 threads that compute a tile meet here.  A named barrier, not __syncthreads: inside the fused decode
+// The threads that compute a tile meet here.  A named barrier, not __syncthreads: inside the fused decode
 // kernel the tile is computed by four of the CTA's eight warps.
-__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 9, 128;\n" ::: "memory"); }
+template <int THREADS>
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 9, %0;\n" ::"n"(THREADS) : "memory"); }
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
@@ -73,10 +73,11 @@ struct AttnParams {
 // Stages of the key/value ring: four where shared memory allows, three for the largest tiles.
 __host__ __device__ constexpr int stages_of(int D, int key_warps) { return D <= 64 ? 4 : 3; }
 
-// D: head size.  ROW_WARPS x KEY_WARPS = 4 warps.  BN: keys per warp and tile.
+// D: head size.  ROW_WARPS x KEY_WARPS warps.  BN: keys per warp and tile.
 template <int D, int ROW_WARPS, int KEY_WARPS, int BN, int STAGES = stages_of(D, KEY_WARPS)>
 __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, int kvh, int r, int tile, unsigned char* smem_raw,
                                                bool use_pdl) {
+    constexpr int THREADS = 32 * ROW_WARPS * KEY_WARPS;
     constexpr int BM = 16 * ROW_WARPS;   // rows of the CTA
     constexpr int BNC = BN * KEY_WARPS;  // keys of one CTA tile
     constexpr int CHUNKS = D / 8;        // 16-byte pieces of a key row
@@ -96,7 +97,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     const int row0 = tile * BM;
     if (row0 >= rows_total) return;
     const int ctx = p.ctx_lens[r], pos0 = ctx - q_len;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x & (THREADS - 1), warp = tid >> 5, lane = tid & 31;
     const int row_warp = warp % ROW_WARPS, key_warp = warp / ROW_WARPS;
     const int qr = lane >> 2, qc = lane & 3;
 
@@ -201,7 +202,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) % STAGES;
         cp_async_wait<STAGES - 2>();  // tile t has landed (this thread's copies) ...
-        cta_sync();              // ... everyone's; and the stage refilled next is no longer read
+        cta_sync<THREADS>();              // ... everyone's; and the stage refilled next is no longer read
         if (t + STAGES - 1 < t_end) load_tile(t + STAGES - 1, (t - t_begin + STAGES - 1) % STAGES, page_next);
         cp_async_commit();
         page_next = page_of(t + STAGES);
@@ -297,7 +298,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
         }
     }
     cp_async_wait<0>();
-    cta_sync();  // the ring is free (the small shape merges its warps through it)
+    cta_sync<THREADS>();  // the ring is free (the small shape merges its warps through it)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
@@ -346,7 +347,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
                 ml_sm[(key_warp * 16 + row) * 2 + 1] = l_run[i];
             }
         }
-        cta_sync();
+        cta_sync<THREADS>();
         for (int idx = tid; idx < 16 * D; idx += THREADS) {
             const int row = idx / D, d = idx - row * D;
             if (row >= rows_total) continue;
@@ -377,9 +378,9 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
             // the split that finishes last merges all of them: no second launch
             __shared__ int ticket;
             __threadfence();
-            cta_sync();
+            cta_sync<THREADS>();
             if (tid == 0) ticket = atomicAdd(&p.counters[r * p.KV + kvh], 1);
-            cta_sync();
+            cta_sync<THREADS>();
             if (ticket != active_splits - 1) return;
             __threadfence();
             // factors of every (row, split) first, side by side, then the weighted sums
@@ -399,7 +400,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
                 }
                 inv_sm[row] = 1.f / l;
             }
-            cta_sync();
+            cta_sync<THREADS>();
             for (int idx = tid; idx < rows_total * D; idx += THREADS) {
                 const int row = idx / D, d = idx - row * D;
                 const int tok = row / G, head = kvh * G + (row - tok * G);
