@@ -132,25 +132,6 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     const int t_end = min(tile_last + 1, t_begin + per_split);
     if (SMALL && split >= active_splits) return;
 
-    // up to here only the step's descriptor arrays were read, which no kernel writes; the queries and the
-    // cache come from the kernels before this one
-    if (use_pdl) {
-        pdl_trigger();
-        pdl_wait();
-    }
-
-    // query fragments, straight from global memory
-    unsigned qa[KSTEPS][4];
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int which = i & 1;
-            const __nv_bfloat16* src = p.q + (size_t)row_tok[which] * p.q_stride + (size_t)row_head[which] * D +
-                                       ks * 16 + (i >> 1) * 8 + qc * 2;
-            qa[ks][i] = row_ok[which] ? *reinterpret_cast<const unsigned*>(src) : 0u;
-        }
-
     const int* table = p.page_table + (size_t)r * p.table_width;
     const size_t head_stride = (size_t)p.page_size * D;
 
@@ -180,6 +161,39 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
         }
     };
 
+    // the pages of the first tiles: the page table is the step's own, written by no kernel, so the lookups go out
+    // before the wait for the kernel in front
+    int first_pages[STAGES - 1];
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) first_pages[i] = page_of(t_begin + i);
+    int page_next = page_of(t_begin + STAGES - 1);
+
+    // up to here only the step's descriptor arrays were read, which no kernel writes; the queries and the
+    // cache come from the kernels before this one
+    if (use_pdl) {
+        pdl_trigger();
+        pdl_wait();
+    }
+
+    // one commit group per tile, empty past the end, so that the wait below counts tiles
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        if (t_begin + i < t_end) load_tile(t_begin + i, i, first_pages[i]);
+        cp_async_commit();
+    }
+
+    // query fragments, straight from global memory
+    unsigned qa[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int which = i & 1;
+            const __nv_bfloat16* src = p.q + (size_t)row_tok[which] * p.q_stride + (size_t)row_head[which] * D +
+                                       ks * 16 + (i >> 1) * 8 + qc * 2;
+            qa[ks][i] = row_ok[which] ? *reinterpret_cast<const unsigned*>(src) : 0u;
+        }
+
     float oacc[NT_O][4];
 #pragma unroll
     for (int i = 0; i < NT_O; ++i)
@@ -187,18 +201,6 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
         for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    // one commit group per tile, empty past the end, so that the wait below counts tiles
-    {
-        int first_pages[STAGES - 1];
-#pragma unroll
-        for (int i = 0; i < STAGES - 1; ++i) first_pages[i] = page_of(t_begin + i);
-#pragma unroll
-        for (int i = 0; i < STAGES - 1; ++i) {
-            if (t_begin + i < t_end) load_tile(t_begin + i, i, first_pages[i]);
-            cp_async_commit();
-        }
-    }
-    int page_next = page_of(t_begin + STAGES - 1);
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) % STAGES;
         cp_async_wait<STAGES - 2>();  // tile t has landed (this thread's copies) ...
