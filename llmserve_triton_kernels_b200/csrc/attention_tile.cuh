@@ -168,16 +168,27 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     for (int i = 0; i < STAGES - 1; ++i) first_pages[i] = page_of(t_begin + i);
     int page_next = page_of(t_begin + STAGES - 1);
 
-    // up to here only the step's descriptor arrays were read, which no kernel writes; the queries and the
-    // cache come from the kernels before this one
+    // One commit group per tile, empty past the end, so that the wait in the loop counts tiles.  A tile whose keys
+    // all lie before the step's first position was written by earlier steps: its copies go out before the wait for
+    // the kernel in front too (such tiles are the first ones, so the groups stay in the order of the tiles).
+    bool asked[STAGES - 1];
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) {
+        asked[i] = use_pdl && t_begin + i < t_end && (t_begin + i + 1) * BNC <= pos0;
+        if (asked[i]) {
+            load_tile(t_begin + i, i, first_pages[i]);
+            cp_async_commit();
+        }
+    }
+    // up to here only the step's descriptor arrays and keys of earlier steps were read, which no kernel of this step
+    // writes; the queries and the step's own keys come from the kernels before this one
     if (use_pdl) {
         pdl_trigger();
         pdl_wait();
     }
-
-    // one commit group per tile, empty past the end, so that the wait below counts tiles
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
+        if (asked[i]) continue;
         if (t_begin + i < t_end) load_tile(t_begin + i, i, first_pages[i]);
         cp_async_commit();
     }
