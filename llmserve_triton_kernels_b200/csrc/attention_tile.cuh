@@ -9,7 +9,7 @@ namespace attn {
 
 
 constexpr int SMALL_ROWS = 16;  // requests with at most this many rows go to the KEYS shape
-constexpr int SMALL_MIN_TILES = 8;  // tiles (of 128 keys) a split of that shape takes at least
+constexpr int SMALL_MIN_TILES = 3;  // tiles (256 keys at head sizes up to 64) a split of that shape takes at least: measured best of 2, 3, 4, 8
 
 // The threads that compute a tile meet here.  A named barrier, not __syncthreads: inside the fused decode
 // kernel the tile is computed by four of the CTA's eight warps.
