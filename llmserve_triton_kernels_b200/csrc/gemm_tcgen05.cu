@@ -95,6 +95,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
     constexpr unsigned IDESC = umma::idesc_bf16(BM, UMMA_N, false);
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    float* epi_s = reinterpret_cast<float*>(ring + (size_t)STAGES * SLOT_BYTES);  // MODE_RESIDUAL: [4 warps][32][33]
     __shared__ __align__(8) unsigned long long full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
     __shared__ unsigned tmem_base;
     __shared__ int gave_up;
@@ -203,7 +204,9 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
                 for (int part = 0; part < p.in_parts; ++part) sum += p.in_ss[(size_t)part * p.M + row];  // a fixed order
                 row_scale = rsqrtf(sum / (float)p.K + p.in_eps);
             }
-            float squares = 0.f;
+            float squares[MODE == MODE_RESIDUAL ? 32 : 1];  // per row of the warp's 32, this lane's columns
+#pragma unroll
+            for (int rr = 0; rr < (MODE == MODE_RESIDUAL ? 32 : 1); ++rr) squares[rr] = 0.f;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 float v[32];
@@ -221,36 +224,49 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] *= row_scale;
                 }
-                if (row >= p.M || col >= p.N) continue;
                 if constexpr (MODE == MODE_RESIDUAL) {
-                    // the stream's row of this thread, 32 columns at a time (N is a multiple of 8: whole 16-byte pieces)
-                    float* rrow = p.resid + (size_t)row * p.N + col;
-                    __nv_bfloat16* xrow = p.xw_out + (size_t)row * p.N + col;
-                    const int valid = min(32, p.N - col);
+                    // The thread holds 32 columns of ONE row; the stream wants a warp on 32 columns of one row at a
+                    // time (128 bytes side by side).  The warp's 32 x 32 piece turns round in shared memory.
+                    float* turn = epi_s + (size_t)(warp - 2) * 32 * 33;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        if (j >= valid) continue;
-                        float4 r0 = *reinterpret_cast<const float4*>(rrow + j), r1 = *reinterpret_cast<const float4*>(rrow + j + 4);
-                        const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + col + j), w1 = *reinterpret_cast<const float4*>(p.norm_w + col + j + 4);
-                        r0.x += v[j]; r0.y += v[j + 1]; r0.z += v[j + 2]; r0.w += v[j + 3];
-                        r1.x += v[j + 4]; r1.y += v[j + 5]; r1.z += v[j + 6]; r1.w += v[j + 7];
-                        *reinterpret_cast<float4*>(rrow + j) = r0;
-                        *reinterpret_cast<float4*>(rrow + j + 4) = r1;
-                        squares += r0.x * r0.x + r0.y * r0.y + r0.z * r0.z + r0.w * r0.w + r1.x * r1.x + r1.y * r1.y + r1.z * r1.z + r1.w * r1.w;
-                        uint4 out;
-                        __nv_bfloat162 a = __floats2bfloat162_rn(r0.x * w0.x, r0.y * w0.y), b = __floats2bfloat162_rn(r0.z * w0.z, r0.w * w0.w);
-                        __nv_bfloat162 c2 = __floats2bfloat162_rn(r1.x * w1.x, r1.y * w1.y), d = __floats2bfloat162_rn(r1.z * w1.z, r1.w * w1.w);
-                        out.x = *reinterpret_cast<unsigned*>(&a);
-                        out.y = *reinterpret_cast<unsigned*>(&b);
-                        out.z = *reinterpret_cast<unsigned*>(&c2);
-                        out.w = *reinterpret_cast<unsigned*>(&d);
-                        *reinterpret_cast<uint4*>(xrow + j) = out;
+                    for (int j = 0; j < 32; ++j) turn[lane * 33 + j] = v[j];
+                    __syncwarp();
+                    const int my_col = col + lane;
+                    const bool col_ok = my_col < p.N;
+                    const float w_here = col_ok ? p.norm_w[my_col] : 0.f;
+                    // every load of the stream goes out before the first store (the compiler cannot know that the
+                    // stores do not touch what the later loads read)
+                    float before[32];
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) {
+                        const int r_g = m0 + quarter * 32 + rr;
+                        before[rr] = r_g < p.M && col_ok ? __ldcg(p.resid + (size_t)r_g * p.N + my_col) : 0.f;
                     }
-                } else {
-                    store32<TO>(reinterpret_cast<TO*>(p.out) + (size_t)row * p.ldo + col, v, min(32, p.N - col));
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr) {
+                        const int r_g = m0 + quarter * 32 + rr;
+                        if (r_g < p.M && col_ok) {
+                            const size_t at = (size_t)r_g * p.N + my_col;
+                            const float r = before[rr] + turn[rr * 33 + lane];
+                            p.resid[at] = r;
+                            p.xw_out[at] = __float2bfloat16_rn(r * w_here);
+                            squares[rr] += r * r;
+                        }
+                    }
+                    __syncwarp();
+                    continue;
+                }
+                if (row >= p.M || col >= p.N) continue;
+                store32<TO>(reinterpret_cast<TO*>(p.out) + (size_t)row * p.ldo + col, v, min(32, p.N - col));
+            }
+            if constexpr (MODE == MODE_RESIDUAL) {
+#pragma unroll
+                for (int rr = 0; rr < 32; ++rr) {
+                    const float total = warp_sum(squares[rr]);
+                    const int r_g = m0 + quarter * 32 + rr;
+                    if (lane == 0 && r_g < p.M) p.ss_out[(size_t)(tile / row_tiles) * p.M + r_g] = total;
                 }
             }
-            if (MODE == MODE_RESIDUAL && row < p.M) p.ss_out[(size_t)(tile / row_tiles) * p.M + row] = squares;
             // this warp has read its lanes of the accumulator: the tile after next may overwrite them
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
@@ -279,7 +295,7 @@ int sm_count() {
 template <int BN, int MODE, int STAGES, typename TO>
 int launch(const void* x, int ldx, const void* w, int w_rows, const GemmParams& p, cudaStream_t stream) {
     constexpr int NB = MODE == MODE_SWIGLU ? 2 : 1;
-    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + NB * BN * BK * 2) + 1024;
+    constexpr size_t smem = (size_t)STAGES * (BM * BK * 2 + NB * BN * BK * 2) + 1024 + (MODE == MODE_RESIDUAL ? 4 * 32 * 33 * sizeof(float) : 0);
     auto kernel = gemm_tcgen05_kernel<BN, MODE, STAGES, TO>;
     static bool configured = false;
     if (!configured) {

@@ -249,9 +249,10 @@ class ResidualSink:
     @staticmethod
     def usable(num_tokens: int, dtype: torch.dtype) -> bool:
         """Steps of few rows end their products this way (the weight-streaming kernel).  The tcgen05 kernel
-        for many rows can too (``linear`` below takes any row count), but its epilogue walks the stream one
-        row per thread, which costs more than the norm kernel it saves (5.87 ms against 5.43 ms for a prompt
-        of 2,048 tokens on a 1.1B model): steps of many rows run the norms as kernels of their own."""
+        for many rows can too (``linear`` below takes any row count; its four epilogue warps turn each 32 x 32
+        piece round in shared memory so that the 32-bit stream is read and written 128 bytes at a time), but four
+        warps per SM do not keep enough of the stream in flight: 6.04 ms against 5.46 ms with the norm as a kernel of
+        its own for a prompt of 2,048 tokens on a 1.1B model.  Steps of many rows run the norms as kernels."""
         return dtype == torch.bfloat16 and (num_tokens <= _DECODE_LINEAR_MAX_ROWS or
                                             (_TCGEN05_RESIDUAL_SINK and num_tokens >= _TCGEN05_MIN_ROWS))
 
