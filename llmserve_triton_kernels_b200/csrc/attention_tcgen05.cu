@@ -206,8 +206,14 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             static_assert(HD == 64, "the product's result is read with one 64-column load");
             float pv[HD];
             umma::tmem_ld64(lane_base + 2 * BN, pv);
+            // two values per instruction (packed 32-bit arithmetic): the same roundings as one by one
+            const float2 a2 = make_float2(alpha_prev, alpha_prev);
 #pragma unroll
-            for (int i = 0; i < HD; ++i) o[i] = fmaf(o[i], alpha_prev, pv[i]);
+            for (int i = 0; i < HD; i += 2) {
+                const float2 r = __ffma2_rn(make_float2(o[i], o[i + 1]), a2, make_float2(pv[i], pv[i + 1]));
+                o[i] = r.x;
+                o[i + 1] = r.y;
+            }
             return true;
         };
         for (int j = 0; j < n_tiles; ++j) {
@@ -247,14 +253,16 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             // the probabilities (a masked score is -inf: its probability is exactly 0), into shared memory as the
             // second product's A (K-major, 128-byte swizzle: row `row`, 16-byte piece c at c ^ (row % 8))
             unsigned char* p_tile = p_s + (size_t)(j & 1) * P_BYTES;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            const float shift = -m_use;
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};  // four chains, two per packed add
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
 #pragma unroll
             for (int c = 0; c < BN / 8; ++c) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    v[c * 8 + i] = attn::fast_exp2(fmaf(v[c * 8 + i], p.scale_log2, shift));
-                    sum4[i & 3] += v[c * 8 + i];
+                for (int i = 0; i < 8; i += 2) {
+                    const float2 x = __ffma2_rn(make_float2(v[c * 8 + i], v[c * 8 + i + 1]), scale2, shift2);
+                    v[c * 8 + i] = attn::fast_exp2(x.x);
+                    v[c * 8 + i + 1] = attn::fast_exp2(x.y);
+                    sum2[(i >> 1) & 1] = __fadd2_rn(sum2[(i >> 1) & 1], make_float2(v[c * 8 + i], v[c * 8 + i + 1]));
                 }
                 uint4 u;
                 u.x = attn::pack_bf16(v[c * 8], v[c * 8 + 1]);
@@ -263,7 +271,7 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                 u.w = attn::pack_bf16(v[c * 8 + 6], v[c * 8 + 7]);
                 *reinterpret_cast<uint4*>(p_tile + row * 128 + ((c ^ (row & 7)) << 4)) = u;
             }
-            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            l_run = l_run * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
             // the tile before: its product has had this tile's softmax to finish in; its result must be read before
             // the issuer learns of this tile's probabilities (the next product overwrites the result)
             if (j > 0 && !(ok = fold(j - 1))) break;
