@@ -423,3 +423,23 @@ def test_sample_follows_the_distribution():
     freq = torch.bincount(got, minlength=vocab).double() / draws
     assert freq[probs == 0].sum() == 0  # nothing outside the top 10
     assert (freq - probs.double()).abs().max() < 0.03
+
+
+def test_grid_barrier_of_the_one_kernel_decode_step():
+    """The grid-wide barrier that the one-kernel decode step is built on (one CTA per SM, launched
+    cooperatively; its wait is bounded): 200 barriers in a row complete, the counter holds every arrival and
+    no CTA gave up."""
+    import ctypes
+
+    o = ops()
+    lib = o.library()
+    lib.llm_grid_barrier_probe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    lib.llm_grid_barrier_probe.restype = ctypes.c_int
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rounds = 200
+    code = lib.llm_grid_barrier_probe(counter.data_ptr(), rounds, flag.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert code == 0
+    torch.cuda.synchronize()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert int(flag) == 0 and int(counter) == rounds * sms
