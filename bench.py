@@ -240,10 +240,25 @@ def main() -> int:
         tokens = [p[-1] for p in prompts]
         launches0 = ops.launch_count()
 
+        # As the scheduler does it: a step's chosen tokens stay on the device and feed the next step, which is launched
+        # before the host reads them (through pinned memory, one step late); every token reaches the host in the loop.
+        ahead = None  # (tokens on the device, their copy in pinned host memory, event after the copy)
+
         def one_step():
-            nonlocal tokens
-            logits = step([StepEntry(n, [t], [0]) for n, t in zip(names, tokens)])
-            tokens = sampler(logits, greedy, [0] * batch, [0] * batch)
+            nonlocal tokens, ahead
+            if ahead is None:
+                logits = step([StepEntry(n, [t], [0]) for n, t in zip(names, tokens)])
+            else:
+                logits = step.decode_ahead(names, ahead[0])
+            chosen = sampler.on_device(logits, greedy, [0] * batch, [0] * batch)
+            host = torch.empty(chosen.shape, dtype=chosen.dtype, pin_memory=True)
+            host.copy_(chosen, non_blocking=True)
+            copied = torch.cuda.Event()
+            copied.record()
+            if ahead is not None:
+                ahead[2].synchronize()
+                tokens = ahead[1].tolist()
+            ahead = (chosen, host, copied)
 
         for _ in range(w):
             one_step()
@@ -256,6 +271,8 @@ def main() -> int:
             start.record()
             for _ in range(k):
                 one_step()
+            ahead[2].synchronize()  # the last step's tokens reach the host inside the timed region too
+            tokens = ahead[1].tolist()
             end.record()
             torch.cuda.synchronize()
         ms = start.elapsed_time(end)

@@ -65,11 +65,14 @@ class DecodeGraph:
     def _piece_np(self, i: int) -> np.ndarray:
         return self.host_np[self.offsets[i] : self.offsets[i] + self.sizes[i]]
 
-    def fill(self, tokens: list[int], lengths: list[int], state_slots: np.ndarray, group_arrays) -> None:
-        """Write the step's arrays into the pinned buffer and start their copy to the device."""
+    def fill(self, tokens, lengths: list[int], state_slots: np.ndarray, group_arrays) -> None:
+        """Write the step's arrays into the pinned buffer and start their copy to the device.  ``tokens``: a list
+        of ids on the host, or an int32 tensor ``[R]`` on the device (the step before has put its choices there and
+        the host has not seen them yet), which is copied over the token ids on the device after the host's arrays."""
         self.copied.synchronize()  # the previous copy has left the pinned buffer
         R = self.R
-        self._piece_np(0)[:] = tokens
+        on_device = isinstance(tokens, torch.Tensor)
+        self._piece_np(0)[:] = 0 if on_device else tokens
         self._piece_np(1)[:] = lengths
         self._piece_np(4)[:] = np.asarray(lengths, dtype=np.int32) + 1
         self._piece_np(6)[:] = state_slots
@@ -79,6 +82,8 @@ class DecodeGraph:
             self._piece_np(8 + 2 * g)[:] = slot_map
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
+        if on_device:
+            self._piece(0).copy_(tokens, non_blocking=True)
 
     def run(self) -> torch.Tensor:
         """Logits ``[R, vocab]`` of the step whose arrays were filled last.  The tensor is

@@ -27,6 +27,8 @@ from enum import Enum
 from time import perf_counter
 
 from ..cache import CacheManager, OutOfPages
+import torch
+
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 
@@ -96,6 +98,16 @@ class EngineStats:
     last_batch_requests: int = 0
 
 
+@dataclass
+class _Ahead:
+    """A decode step that has been launched and whose tokens the host has not read yet."""
+
+    reqs: list  # the requests of the step, in the order of its rows
+    device_tokens: object  # int32 [rows] on the device: what the step chose
+    host_tokens: object  # the same on the host (pinned memory), valid once `copied` has happened
+    copied: object  # event after the copy to the host
+
+
 class Scheduler:
     def __init__(
         self,
@@ -130,6 +142,11 @@ class Scheduler:
         self._next_id = 0
         self._aborts: set[int] = set()
         self._lock = threading.Lock()
+        # Decode steps that replay a graph run one step ahead of the host: the next step is fed the chosen tokens
+        # on the device and launched before the host reads them, so the GPU does not wait for the host between
+        # steps.  The host sees a step's tokens one call of step() later.
+        self.run_ahead = bool(getattr(step_function, "use_graphs", False))
+        self._ahead: _Ahead | None = None
 
     # ------------------------------------------------------------------ public
     def validate_request(self, prompt_len: int, max_new_tokens: int) -> None:
@@ -174,6 +191,7 @@ class Scheduler:
                 self.cache.free_request(r.req_id)
         self.running.clear()
         self.waiting.clear()
+        self._ahead = None
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
@@ -192,12 +210,20 @@ class Scheduler:
     def run_until_complete(self) -> dict[int, Request]:
         while self.has_unfinished():
             self.step()
+        self._ahead = None  # a step too many of requests that ended by their end-of-sequence token: nobody reads it
         return self.finished
 
     # ------------------------------------------------------------------ one step
     def step(self) -> list[TokenEvent]:
         events: list[TokenEvent] = []
         self.stats.steps += 1
+        if self._ahead is not None:
+            ahead, self._ahead = self._ahead, None
+            if self._can_run_ahead(ahead):
+                self._ahead = self._launch_ahead(ahead)  # the GPU goes on while the host catches up
+            self._collect(ahead, events)
+            if self._ahead is not None:
+                return events
         self._process_aborts(events)
         plan = self._plan()
         if not plan:
@@ -221,11 +247,54 @@ class Scheduler:
         self.stats.last_batch_tokens = sum(n for _, n in plan)
         self.stats.last_batch_requests = len(plan)
         if sampled:
-            tokens = self.sampler(
-                logits, [r.params for r in sampled], [r.seed for r in sampled], [len(r.generated) for r in sampled]
-            )
-            self._append(sampled, tokens, events)
+            params, seeds = [r.params for r in sampled], [r.seed for r in sampled]
+            counters = [len(r.generated) for r in sampled]
+            if self.run_ahead and getattr(self.step_function, "last_was_graph", False) and len(sampled) == len(plan):
+                # a decode step of every running request: its tokens stay on the device for now
+                self._ahead = self._remember(sampled, self.sampler.on_device(logits, params, seeds, counters))
+            else:
+                self._append(sampled, self.sampler(logits, params, seeds, counters), events)
         return events
+
+    # ------------------------------------------------------------------ one step ahead of the host
+    def _remember(self, reqs: list[Request], device_tokens) -> _Ahead:
+        host = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=True)
+        host.copy_(device_tokens, non_blocking=True)
+        copied = torch.cuda.Event()
+        copied.record()
+        return _Ahead(reqs, device_tokens, host, copied)
+
+    def _can_run_ahead(self, ahead: _Ahead) -> bool:
+        """The step after ``ahead`` can be launched before ``ahead``'s tokens are known: the same requests decode on
+        (none ends by its length with the token that is on its way; one that ends by its end-of-sequence token
+        does a step too many, whose result is dropped), nobody waits to be admitted or aborted, pages suffice."""
+        with self._lock:
+            if self._aborts:
+                return False
+        if self.waiting or len(ahead.reqs) != len(self.running) or any(a is not b for a, b in zip(ahead.reqs, self.running)):
+            return False
+        if any(len(r.generated) + 2 > r.params.max_new_tokens for r in ahead.reqs):
+            return False
+        need = sum(self.cache.extra_pages_needed(r.req_id, 1) for r in ahead.reqs)
+        return need <= self.cache.num_free_pages
+
+    def _launch_ahead(self, ahead: _Ahead) -> _Ahead:
+        reqs = ahead.reqs
+        logits = self.step_function.decode_ahead([r.req_id for r in reqs], ahead.device_tokens)
+        for r in reqs:
+            r.num_computed += 1
+        self.stats.decode_tokens += len(reqs)
+        self.stats.last_batch_tokens = self.stats.last_batch_requests = len(reqs)
+        tokens = self.sampler.on_device(logits, [r.params for r in reqs], [r.seed for r in reqs], [len(r.generated) + 1 for r in reqs])
+        return self._remember(reqs, tokens)
+
+    def _collect(self, ahead: _Ahead, events: list[TokenEvent]) -> None:
+        """The host reads the tokens of a step launched earlier.  A request that has ended meanwhile (its
+        end-of-sequence token came with the step before, or it was aborted) drops its token."""
+        ahead.copied.synchronize()
+        tokens = ahead.host_tokens.tolist()
+        live = [(r, t) for r, t in zip(ahead.reqs, tokens) if r.status is Status.RUNNING and r in self.running]
+        self._append([r for r, _ in live], [t for _, t in live], events)
 
     # ------------------------------------------------------------------ internals
     def _process_aborts(self, events: list[TokenEvent]) -> None:

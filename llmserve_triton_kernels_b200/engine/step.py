@@ -30,6 +30,7 @@ class StepFunction:
             use_graphs = cache.device.type == "cuda" and model.graph_safe
         self.use_graphs = bool(use_graphs)
         self.graphs: dict[int, DecodeGraph] = {}
+        self.last_was_graph = False  # the last step replayed a graph
 
     def __call__(self, entries: list[StepEntry]) -> torch.Tensor:
         """Returns 32-bit logits ``[wanted places, vocab]`` on the device, in the order of the
@@ -56,18 +57,39 @@ class StepFunction:
         cache.reserve(pairs)
         group_arrays, state_slots = cache.step_tables(pairs)
         lengths = [cache.lengths[req] for req, _ in pairs]
+        self.last_was_graph = False
         if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            graph = self.graphs.get(len(entries))
-            if graph is None:
-                graph = self.graphs[len(entries)] = DecodeGraph(self.model, cache, len(entries))
-            graph.fill([e.tokens[0] for e in entries], lengths, state_slots, group_arrays)
-            logits = graph.run()
-            cache.commit(pairs)
-            self.h2d_bytes, self.last_context = graph.h2d_bytes, graph.ctx
-            return logits
+            return self._replay(pairs, [e.tokens[0] for e in entries], lengths, state_slots, group_arrays)
         ctx, group_tensors, self.h2d_bytes = pack_step(entries, lengths, state_slots, group_arrays, cache.device)
         views = cache.views(group_tensors, ctx.state_slots, ctx.host_state_slots)
         logits = self.model.forward(ctx, views)
         cache.commit(pairs)
         self.last_context = ctx
         return logits
+
+    def _replay(self, pairs, tokens, lengths, state_slots, group_arrays) -> torch.Tensor:
+        cache = self.cache
+        graph = self.graphs.get(len(pairs))
+        if graph is None:
+            graph = self.graphs[len(pairs)] = DecodeGraph(self.model, cache, len(pairs))
+        graph.fill(tokens, lengths, state_slots, group_arrays)
+        logits = graph.run()
+        cache.commit(pairs)
+        self.h2d_bytes, self.last_context, self.last_was_graph = graph.h2d_bytes, graph.ctx, True
+        return logits
+
+    def decode_ahead(self, requests: list, device_tokens: torch.Tensor) -> torch.Tensor:
+        """One decode step (one token per request, its logits wanted) whose token ids are not on the host yet:
+        ``device_tokens`` (int32 ``[len(requests)]``, in the order of ``requests``) holds what the step before chose.
+        Only for steps that replay a graph; the requests must be live and have room for one more token."""
+        if not self.use_graphs:
+            raise RuntimeError("decode_ahead needs decode steps that replay a graph")
+        cache, limit = self.cache, self.model.plan.max_positions
+        for r in requests:
+            if cache.lengths[r] + 1 > limit:
+                raise ValueError(f"request {r!r} would hold {cache.lengths[r] + 1} tokens, beyond the model's {limit} positions")
+        pairs = [(r, 1) for r in requests]
+        cache.reserve(pairs)
+        group_arrays, state_slots = cache.step_tables(pairs)
+        lengths = [cache.lengths[r] for r in requests]
+        return self._replay(pairs, device_tokens, lengths, state_slots, group_arrays)

@@ -25,9 +25,14 @@ class Sampler:
 
     def __call__(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int], counters: list[int]) -> list[int]:
         """``logits [rows, vocab]`` float32 on the device -> one token id per row, on the host."""
-        rows = logits.shape[0]
-        if rows == 0:
+        if logits.shape[0] == 0:
             return []
+        return self.on_device(logits, params, seeds, counters).tolist()
+
+    def on_device(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int], counters: list[int]) -> torch.Tensor:
+        """The same, but the token ids stay on the device (int32 ``[rows]``): the next step can be fed from there
+        before the host has seen them."""
+        rows = logits.shape[0]
         self.h2d_bytes = 0
         if all(p.greedy for p in params):
             tokens = ops.argmax(logits)
@@ -53,4 +58,4 @@ class Sampler:
                 dev[6 * rows : 8 * rows].view(torch.int64),
             )
         self.d2h_bytes = rows * 4
-        return tokens.tolist()
+        return tokens
