@@ -120,6 +120,7 @@ class Scheduler:
         max_num_batched_tokens: int = 4096,
         chunk_size: int | None = None,
         policy: str = "continuous",
+        run_ahead: bool | None = None,
     ):
         if policy not in ("continuous", "static"):
             raise ValueError("policy must be 'continuous' or 'static'")
@@ -145,7 +146,7 @@ class Scheduler:
         # Decode steps that replay a graph run one step ahead of the host: the next step is fed the chosen tokens
         # on the device and launched before the host reads them, so the GPU does not wait for the host between
         # steps.  The host sees a step's tokens one call of step() later.
-        self.run_ahead = bool(getattr(step_function, "use_graphs", False))
+        self.run_ahead = bool(getattr(step_function, "use_graphs", False)) if run_ahead is None else bool(run_ahead)
         self._ahead: _Ahead | None = None
 
     # ------------------------------------------------------------------ public
@@ -249,7 +250,7 @@ class Scheduler:
         if sampled:
             params, seeds = [r.params for r in sampled], [r.seed for r in sampled]
             counters = [len(r.generated) for r in sampled]
-            if self.run_ahead and getattr(self.step_function, "last_was_graph", False) and len(sampled) == len(plan):
+            if self.run_ahead and len(sampled) == len(plan) and all(n == 1 for _, n in plan):
                 # a decode step of every running request: its tokens stay on the device for now
                 self._ahead = self._remember(sampled, self.sampler.on_device(logits, params, seeds, counters))
             else:
@@ -258,6 +259,8 @@ class Scheduler:
 
     # ------------------------------------------------------------------ one step ahead of the host
     def _remember(self, reqs: list[Request], device_tokens) -> _Ahead:
+        if not device_tokens.is_cuda:
+            return _Ahead(reqs, device_tokens, device_tokens.clone(), None)
         host = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=True)
         host.copy_(device_tokens, non_blocking=True)
         copied = torch.cuda.Event()
@@ -291,7 +294,8 @@ class Scheduler:
     def _collect(self, ahead: _Ahead, events: list[TokenEvent]) -> None:
         """The host reads the tokens of a step launched earlier.  A request that has ended meanwhile (its
         end-of-sequence token came with the step before, or it was aborted) drops its token."""
-        ahead.copied.synchronize()
+        if ahead.copied is not None:
+            ahead.copied.synchronize()
         tokens = ahead.host_tokens.tolist()
         live = [(r, t) for r, t in zip(ahead.reqs, tokens) if r.status is Status.RUNNING and r in self.running]
         self._append([r for r, _ in live], [t for _, t in live], events)

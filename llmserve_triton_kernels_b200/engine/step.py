@@ -81,9 +81,10 @@ class StepFunction:
     def decode_ahead(self, requests: list, device_tokens: torch.Tensor) -> torch.Tensor:
         """One decode step (one token per request, its logits wanted) whose token ids are not on the host yet:
         ``device_tokens`` (int32 ``[len(requests)]``, in the order of ``requests``) holds what the step before chose.
-        Only for steps that replay a graph; the requests must be live and have room for one more token."""
-        if not self.use_graphs:
-            raise RuntimeError("decode_ahead needs decode steps that replay a graph")
+        The requests must be live and have room for one more token.  Where decode steps replay a graph the host
+        never reads the tokens here; elsewhere this is an ordinary step on tokens read from the tensor."""
+        if not self.use_graphs:  # no graphs (a model that cannot be captured, or the CPU under test): the plain way
+            return self([StepEntry(r, [int(t)], [0]) for r, t in zip(requests, device_tokens.tolist())])
         cache, limit = self.cache, self.model.plan.max_positions
         for r in requests:
             if cache.lengths[r] + 1 > limit:

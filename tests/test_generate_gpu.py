@@ -86,6 +86,41 @@ def test_bfloat16_generation_follows_the_plain_one(name, model_folder):
     assert llm.step_function.graphs, "no decode step was captured"
 
 
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_requests_that_end_while_the_engine_runs_ahead_of_the_host(name, model_folder):
+    """Decode steps are launched one step before the host reads the tokens of the step before.  Requests that end
+    at different steps — by an end-of-sequence token, which the host learns a step late (the request has done a
+    step too many by then, whose token must be dropped), and by different lengths — must give what the plain
+    implementation gives, and every page must come back."""
+    from llmserve_triton_kernels_b200 import SamplingParams
+
+    cfg, seed, _, _ = tiny_configs.TINY[name]
+    folder = model_folder(cfg, seed, torch.float32)
+    plain_cfg, w = plain_llama.read_model(folder)
+    prompts = tiny_configs.prompts(name)
+    llm = engine(folder, "float32")
+    assert llm.scheduler.run_ahead
+    free = plain_llama.generate(plain_cfg, w, prompts[0], 12)
+    params, want = [], []
+    for i, prompt in enumerate(prompts):
+        if i == 0:  # ends by the token it would choose sixth
+            eos = free[5]
+            params.append(SamplingParams(max_new_tokens=12, eos_token_id=eos))
+            want.append(plain_llama.generate(plain_cfg, w, prompt, 12, eos=eos))
+            assert want[-1][-1] == eos and len(want[-1]) <= 6
+        else:  # end by lengths of their own
+            params.append(SamplingParams(max_new_tokens=3 + 4 * i))
+            want.append(plain_llama.generate(plain_cfg, w, prompt, 3 + 4 * i))
+    outs = llm.generate(prompts, params)
+    assert [o.token_ids for o in outs] == want
+    assert outs[0].finish_reason == "stop" and all(o.finish_reason == "length" for o in outs[1:])
+    assert llm.cache.num_free_pages == llm.cache.num_pages
+    # and once more on the same engine: nothing of the last run's step too many is left over
+    outs = llm.generate(prompts, params)
+    assert [o.token_ids for o in outs] == want
+    assert llm.cache.num_free_pages == llm.cache.num_pages
+
+
 @pytest.mark.parametrize("name", ["c", "d"])
 def test_one_kernel_decode_step_equals_the_step_kernel_by_kernel(name, model_folder, monkeypatch):
     """Head sizes 64 and 128 with up to 8 requests can decode through one cooperative kernel (an

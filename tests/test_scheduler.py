@@ -170,3 +170,73 @@ def test_snapshot_and_seed_reproducibility(model_folder, plain_ops_engine):
     assert first == again and first != other
     snap = llm.scheduler.snapshot()
     assert snap["running"] == 0 and snap["free_blocks"] == snap["total_blocks"] and snap["tokens_generated"] == 48
+
+
+# ------------------------------------------------------------------ one step ahead of the host
+def ahead(llm):
+    """On a GPU decode steps are launched before the host has read the tokens of the step before; the same logic
+    runs here on the CPU (the step function then reads the tokens from the tensor, which changes nothing)."""
+    llm.scheduler.run_ahead = True
+    return llm
+
+
+@pytest.mark.parametrize("policy", ["continuous", "static"])
+def test_running_ahead_of_the_host_changes_no_token(model_folder, plain_ops_engine, policy):
+    llm, plain = make(model_folder, policy=policy)
+    ahead(llm)
+    prompts = tiny_configs.seeded_tokens(256, [p for p, _ in REQUESTS], 11)
+    outs = llm.generate(prompts, [SamplingParams(max_new_tokens=n) for _, n in REQUESTS])
+    for out, prompt, (_, n) in zip(outs, prompts, REQUESTS):
+        assert out.token_ids == plain_tokens(plain, prompt, n)
+        assert out.finish_reason == "length"
+    assert llm.cache.num_free_pages == llm.cache.num_pages
+    llm.cache.check()
+    assert llm.scheduler._ahead is None
+
+
+def test_running_ahead_a_stop_token_is_learnt_a_step_late(model_folder, plain_ops_engine):
+    llm, plain = make(model_folder)
+    ahead(llm)
+    prompts = tiny_configs.seeded_tokens(256, [8, 5], 16)
+    free_run = plain_tokens(plain, prompts[0], 10)
+    eos = free_run[4]
+    sched = llm.scheduler
+    a = sched.add_request(prompts[0], SamplingParams(max_new_tokens=10, eos_token_id=eos))
+    b = sched.add_request(prompts[1], SamplingParams(max_new_tokens=10))
+    launched_too_many = False
+    while sched.has_unfinished():
+        sched.step()
+        fin = sched.finished.get(a)
+        if fin is not None and sched._ahead is not None and fin in sched._ahead.reqs:
+            launched_too_many = True  # a's step too many is in flight; its token must never show
+    assert launched_too_many
+    cut = free_run.index(eos) + 1
+    assert sched.finished[a].generated == free_run[:cut] and sched.finished[a].finish_reason == "stop"
+    assert sched.finished[b].generated == plain_tokens(plain, prompts[1], 10)
+    assert llm.cache.num_free_pages == llm.cache.num_pages
+    llm.cache.check()
+
+
+def test_running_ahead_with_few_pages_and_an_abort(model_folder, plain_ops_engine):
+    llm, plain = make(model_folder, block_size=4, num_blocks=10, max_batch_size=3)
+    ahead(llm)
+    prompts = tiny_configs.seeded_tokens(256, [9, 10, 11], 12)
+    outs = llm.generate(prompts, SamplingParams(max_new_tokens=12))
+    assert llm.scheduler.stats.preemptions > 0
+    for out, prompt in zip(outs, prompts):
+        assert out.token_ids == plain_tokens(plain, prompt, 12)
+    assert llm.cache.num_free_pages == llm.cache.num_pages
+    # an abort while a step is in flight ahead of the host
+    sched = llm.scheduler
+    a = sched.add_request(prompts[0], SamplingParams(max_new_tokens=30))
+    while sched._ahead is None:
+        sched.step()
+    sched.abort(a)
+    events = []
+    while sched.has_unfinished():
+        events += sched.step()
+    assert [(e.req_id, e.finish_reason) for e in events if e.finished] == [(a, "abort")]
+    got = sched.finished[a].generated
+    assert got == plain_tokens(plain, prompts[0], 30)[: len(got)]
+    assert llm.cache.num_free_pages == llm.cache.num_pages
+    llm.cache.check()
