@@ -88,7 +88,13 @@ int launch_all(AttnParams p, int requests, int n_tokens, const int* token_reques
         p.tiles_per_request = 1;
         // few rows: sixteen warps (eight for the largest head size) share the keys of a tile, 16 keys each, so that a
         // tile is a short step for every warp; the warps' shares are merged through shared memory at the end
-        if constexpr (D <= 64) code = launch_shape<D, 1, 16, 16, 3>(p, requests, stream);
+        // More (request, kv head) pairs than SMs: eight warps and tiles of 128 keys, so that two CTAs share an SM and all
+        // pairs run at once.
+        int sms = 0, dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        const bool many = (long long)requests * p.KV > sms;
+        if constexpr (D <= 64) code = many ? launch_shape<D, 1, 8, 16, 3>(p, requests, stream) : launch_shape<D, 1, 16, 16, 3>(p, requests, stream);
         else code = launch_shape<D, 1, 8, 16, 3>(p, requests, stream);
         if (code) return code;
     }
