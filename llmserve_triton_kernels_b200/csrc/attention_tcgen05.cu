@@ -15,8 +15,8 @@
 //   warp 5    : one thread issues the products; the warp owns the allocation of tensor memory.
 // Scores and probabilities have two buffers each: the scores of tile j+1 are computed while the softmax of
 // tile j runs, and the second product of tile j runs while the softmax of tile j+1 does (its result is
-// folded into the output one tile late).  Two CTAs share an SM.  Softmax, running sums and the output are 32-bit; probabilities are rounded to
-// bfloat16 for the second product, as in the mma.sync kernel.
+// folded into the output one tile late).  Two CTAs share an SM.  Softmax, running sums and the output are
+// 32-bit; probabilities are rounded to bfloat16 for the second product, as in the mma.sync kernel.
 //
 // Keys past a request's length inside its last page, and pages outside the range a CTA needs, are
 // never looked at: a score outside [window start, position] is -inf before the exponential, and the

@@ -5,7 +5,7 @@ shapes every time, so the whole pass — some hundred and fifty launches for 22 
 captured once per batch size and replayed.  Only the step's integer arrays change: they are
 written into a pinned buffer of fixed layout and copied to the device with one copy before the
 replay.  The reference notes launch and host overhead as its next bottleneck and CUDA graphs as
-the cure (docs/PROFILING.md:19-20, docs/DESIGN.md:79-80) but does not build them.
+the cure (its docs/PROFILING.md:19-20 and the closing notes of its design document) but does not build them.
 
 Page tables have the model's full width in a graph (``ceil(max_positions / page_size)``), and
 ``StepContext.max_context_len`` is the model's limit, so no launch depends on how long the
