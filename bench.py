@@ -67,12 +67,13 @@ class ClockSampler:
     def __init__(self, index: int = 0):
         self.index = index
         self.proc = None
-        self.lines: list[str] = []
+        self.lines: list[tuple[float, str]] = []
+        self.window = [0.0, float("inf")]  # only samples taken while the timed region ran are counted
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -82,11 +83,16 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def begin(self):
+        self.window[0] = time.time()
+
+    def end(self):
+        self.window[1] = time.time()
 
     def __exit__(self, *exc):
         if self.proc is not None:
-            time.sleep(0.15)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
@@ -96,7 +102,9 @@ class ClockSampler:
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for stamp, line in self.lines:
+            if not self.window[0] <= stamp <= self.window[1] + 0.02:
+                continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -265,9 +273,11 @@ def main() -> int:
         torch.cuda.synchronize()
         launches0 = ops.launch_count()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        flush.fill_(1)
-        torch.cuda.synchronize()
         with ClockSampler() as clocks:
+            time.sleep(0.3)  # nvidia-smi is up and sampling before the timed region starts
+            flush.fill_(1)
+            torch.cuda.synchronize()
+            clocks.begin()
             start.record()
             for _ in range(k):
                 one_step()
@@ -275,6 +285,7 @@ def main() -> int:
             tokens = ahead[1].tolist()
             end.record()
             torch.cuda.synchronize()
+            clocks.end()
         ms = start.elapsed_time(end)
         context = PROMPT_LEN + w + (k + 1) / 2.0  # mean number of cached tokens a timed step reads per request
         bytes_per_step = weight_bytes + batch * context * numbers["kv_bytes_per_token"]
