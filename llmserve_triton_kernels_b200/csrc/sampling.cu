@@ -11,9 +11,22 @@
 // nothing but its logits, its parameters, its seed and how many tokens it has drawn before.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
 namespace {
 
-constexpr int THREADS = 512;
+// A row is shared out over a thread-block cluster of up to eight blocks (fewer when there are many
+// rows): one block alone takes some 8 us to pull a row of 32,000 logits out of L2, and a search pass
+// is bound by the instructions one SM can issue.  Block `rank` of a cluster owns the tokens of
+// `runs_per_block` runs of 32 consecutive tokens; what the blocks have to agree on (the largest
+// logit, the weight in the bins of a search pass, their share of the probability mass) every block
+// writes into every block's shared memory and then adds up in the same order.
+constexpr int THREADS = 1024;
+constexpr int WARPS = THREADS / 32;
+constexpr int MAX_CLUSTER = 8;
+constexpr int BINS = 16;
 
 __device__ __forceinline__ unsigned ordered_key(float v) {
     const unsigned b = __float_as_uint(v);
@@ -37,6 +50,24 @@ __device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {
     if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
     return a;
 }
+
+// The tokens [lo, hi) of a row that block `rank` of `blocks` owns: whole runs of 32.
+struct Slice {
+    int lo, hi, runs;
+};
+__device__ __forceinline__ Slice slice_of(int vocab, int rank, int blocks) {
+    const int runs_all = (vocab + 31) / 32, per = (runs_all + blocks - 1) / blocks;
+    const int r0 = min(runs_all, rank * per), r1 = min(runs_all, r0 + per);
+    return Slice{r0 * 32, min(vocab, r1 * 32), r1 - r0};
+}
+
+struct Shared {
+    MaxIdx warp_best[33];
+    MaxIdx block_best[MAX_CLUSTER];          // written by every block of the cluster
+    float sum[33];
+    float group[WARPS];
+    float shared_out[2][MAX_CLUSTER][WARPS];  // written by every block of the cluster; two copies used in turn
+};
 
 // Largest value and its lowest index over the block; every thread gets the result.
 __device__ MaxIdx block_argmax(MaxIdx mine, MaxIdx* scratch) {
@@ -63,148 +94,165 @@ __device__ MaxIdx block_argmax(MaxIdx mine, MaxIdx* scratch) {
     return scratch[32];
 }
 
-__device__ MaxIdx row_argmax(const float* row, int vocab, MaxIdx* scratch) {
-    MaxIdx mine{-INFINITY, 0x7fffffff};
-    if ((vocab & 3) == 0 && ((uintptr_t)row & 15) == 0) {
-        // four loads of 16 bytes in flight per thread: the scan is bound by load latency, not by comparisons
-        const float4* row4 = reinterpret_cast<const float4*>(row);
-        const int n4 = vocab >> 2, step = blockDim.x;
-        for (int i = threadIdx.x; i < n4; i += 4 * step) {
-            float4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = i + u * step < n4 ? row4[i + u * step] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int base = (i + u * step) * 4;
-                mine = better(mine, MaxIdx{v[u].x, base});
-                mine = better(mine, MaxIdx{v[u].y, base + 1});
-                mine = better(mine, MaxIdx{v[u].z, base + 2});
-                mine = better(mine, MaxIdx{v[u].w, base + 3});
-            }
-        }
-    } else {
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) mine = better(mine, MaxIdx{row[i], i});
-    }
-    return block_argmax(mine, scratch);
+// ... and over the cluster.  One use per kernel.
+__device__ MaxIdx cluster_argmax(cg::cluster_group& cluster, MaxIdx mine, Shared& sh) {
+    const MaxIdx block = block_argmax(mine, sh.warp_best);
+    const int rank = (int)cluster.block_rank(), blocks = (int)cluster.num_blocks();
+    if ((int)threadIdx.x < blocks) *cluster.map_shared_rank(&sh.block_best[rank], threadIdx.x) = block;
+    cluster.sync();
+    MaxIdx best = sh.block_best[0];
+    for (int r = 1; r < blocks; ++r) best = better(best, sh.block_best[r]);
+    if (best.i == 0x7fffffff) best.i = 0;  // a row without a single number: still a token of the vocabulary
+    return best;
+}
+
+// Every block gives up to 32 numbers (one per warp, from lane 0) and gets the numbers of all blocks:
+// `sh.shared_out[copy][block][warp]` after the call.  The two copies are used in turn: a block can be one call
+// ahead of another, never two, because no block passes the barrier before all have read the call before.
+__device__ __forceinline__ void cluster_share(cg::cluster_group& cluster, Shared& sh, int& copy, float value) {
+    copy ^= 1;
+    const int rank = (int)cluster.block_rank(), blocks = (int)cluster.num_blocks();
+    if ((threadIdx.x & 31) == 0)
+        for (int r = 0; r < blocks; ++r) *cluster.map_shared_rank(&sh.shared_out[copy][rank][threadIdx.x >> 5], r) = value;
+    cluster.sync();
+}
+
+// Sum over the cluster of one number per block, the same in every thread of every block.
+__device__ __forceinline__ float cluster_sum(cg::cluster_group& cluster, Shared& sh, int& copy, float thread_value) {
+    const float block = block_sum(thread_value, sh.sum);
+    cluster_share(cluster, sh, copy, block);  // every warp sends the same number; the first is read
+    float s = 0.f;
+    for (int r = 0; r < (int)cluster.num_blocks(); ++r) s += sh.shared_out[copy][r][0];
+    return s;
 }
 
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
-    __shared__ MaxIdx scratch[33];
+    __shared__ Shared sh;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int blocks = (int)cluster.num_blocks(), rowi = blockIdx.x / blocks;
+    const Slice mine_of = slice_of(vocab, (int)cluster.block_rank(), blocks);
+    const float* row = logits + (size_t)rowi * vocab;
     pdl_trigger();
     pdl_wait();
-    const MaxIdx best = row_argmax(logits + (size_t)blockIdx.x * vocab, vocab, scratch);
-    if (threadIdx.x == 0) out[blockIdx.x] = best.i;
+    MaxIdx mine{-INFINITY, 0x7fffffff};
+    for (int i0 = mine_of.lo + threadIdx.x; i0 < mine_of.hi; i0 += 8 * THREADS) {
+        float v[8];  // eight loads in flight per thread: the scan is bound by their latency
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = i0 + u * THREADS < mine_of.hi ? row[i0 + u * THREADS] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mine = better(mine, MaxIdx{v[u], i0 + u * THREADS});
+    }
+    const MaxIdx best = cluster_argmax(cluster, mine, sh);
+    if (threadIdx.x == 0 && cluster.block_rank() == 0) out[rowi] = best.i;
 }
 
 // ---- temperature sampling -----------------------------------------------------------------------
 //
-// One block of 1024 threads per row.  The row, divided by its temperature, is kept in shared memory
-// where it fits (a vocabulary of up to about 40,000); a larger one is read again from global memory
-// (it lies in L2) in every pass.  Both cuts are radix searches over the keys, four bits a pass: a
-// pass adds the weight of every element whose higher bits match the prefix found so far into the
-// bin of its next four bits, and the prefix grows by the largest digit whose weight at and above it
-// still passes the threshold.  Weights are 1 for top-k and exp(x - max) for top-p.  Every thread
-// has its own sixteen bins in shared memory, so the additions need no atomics and their order is
-// fixed.  After the first passes few elements match the prefix, so the later ones cost little.
-constexpr int S_THREADS = 1024;
-constexpr int S_WARPS = S_THREADS / 32;
-constexpr int BINS = 16;
-
-struct SampleShared {
-    MaxIdx best[33];
-    float sum[33];
-    float halves[2 * BINS];
-    float group[S_WARPS];
-};
-
+// A block keeps its tokens of the row, divided by the temperature, in shared memory where they fit
+// (with a cluster of eight: a vocabulary of up to some 300,000); otherwise it reads them again from
+// global memory (they lie in L2) in every pass.  Both cuts are radix searches over the keys, four
+// bits a pass: a pass adds the weight of every element whose higher bits match the prefix found so
+// far into the bin of its next four bits, and the prefix grows by the largest digit whose weight at
+// and above it still passes the threshold.  Weights are 1 for top-k and exp(x - max) for top-p.
+// Every thread has its own sixteen bins in shared memory, so the additions need no atomics and
+// their order is fixed.  After the first passes few elements match the prefix, so the later ones
+// cost little.
 template <bool IN_SMEM>
-__device__ __forceinline__ float scaled(const float* xs, const float* row, float temp, int i) {
-    return IN_SMEM ? xs[i] : row[i] / temp;
+__device__ __forceinline__ float scaled(const float* xs, const float* row, float temp, int lo, int i) {
+    return IN_SMEM ? xs[i - lo] : row[i] / temp;
 }
 
-// The largest key T for which G(T) > threshold, where G(T) is the summed weight of the elements
-// that are kept (key >= floor_key) and have key >= T.  G(0) is taken to pass.
+// The largest key T for which G(T) > threshold, where G(T) is the summed weight of the elements of
+// the row that are kept (key >= floor_key) and have key >= T.  G(0) is taken to pass.
 template <bool IN_SMEM, bool WEIGHTED>
-__device__ unsigned radix_search(const float* xs, const float* row, float temp, int vocab, unsigned floor_key,
-                                 float x_max, float threshold, float* bins, SampleShared& sh) {
-    static_assert(2 * BINS == S_WARPS, "two warps add up one bin");
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float* mine = bins + threadIdx.x;  // this thread's share of bin j is mine[j * S_THREADS]: no two threads meet in a bank
+__device__ unsigned radix_search(cg::cluster_group& cluster, const float* xs, const float* row, float temp, Slice part,
+                                 unsigned floor_key, float x_max, float threshold, float* bins, Shared& sh, int& copy) {
+    static_assert(2 * BINS == WARPS, "two warps add up one bin");
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, blocks = (int)cluster.num_blocks();
+    float* mine = bins + threadIdx.x;  // this thread's share of bin j is mine[j * THREADS]: no two threads meet in a bank
     unsigned t = 0u;
     float base = 0.f;  // weight of the elements whose higher bits lie above the prefix
     for (int shift = 28; shift >= 0; shift -= 4) {
 #pragma unroll
-        for (int j = 0; j < BINS; ++j) mine[j * S_THREADS] = 0.f;
-        for (int i = threadIdx.x; i < vocab; i += S_THREADS) {
-            const float x = scaled<IN_SMEM>(xs, row, temp, i);
+        for (int j = 0; j < BINS; ++j) mine[j * THREADS] = 0.f;
+        for (int i = part.lo + threadIdx.x; i < part.hi; i += THREADS) {
+            const float x = scaled<IN_SMEM>(xs, row, temp, part.lo, i);
             const unsigned key = ordered_key(x);
             if (key < floor_key) continue;
             if (shift < 28 && (key >> (shift + 4)) != (t >> (shift + 4))) continue;
-            mine[((key >> shift) & 15u) * S_THREADS] += WEIGHTED ? expf(x - x_max) : 1.f;
+            mine[((key >> shift) & 15u) * THREADS] += WEIGHTED ? expf(x - x_max) : 1.f;
         }
         __syncthreads();
-        {  // bin j: warps 2j and 2j+1 add half of the threads' shares each
-            const float* b = bins + (warp >> 1) * S_THREADS + (warp & 1) * (S_THREADS / 2);
-            float s = 0.f;
+        // bin j: warps 2j and 2j+1 add half of the threads' shares each, and all blocks get both halves
+        const float* b = bins + (warp >> 1) * THREADS + (warp & 1) * (THREADS / 2);
+        float half = 0.f;
 #pragma unroll
-            for (int u = 0; u < S_THREADS / 64; ++u) s += b[u * 32 + lane];
-            s = warp_sum(s);
-            if (lane == 0) sh.halves[warp] = s;
-        }
-        __syncthreads();
+        for (int u = 0; u < THREADS / 64; ++u) half += b[u * 32 + lane];
+        cluster_share(cluster, sh, copy, warp_sum(half));
+        float total = 0.f;  // lane j < 16: bin j over the cluster
+        if (lane < BINS)
+            for (int r = 0; r < blocks; ++r) total += sh.shared_out[copy][r][2 * lane] + sh.shared_out[copy][r][2 * lane + 1];
         float above = base;  // weight above digit j, from the top digit down
+        float with_digit = 0.f;
         int digit = 0;
-        for (int j = BINS - 1; j >= 1; --j) {
-            const float with_j = above + (sh.halves[2 * j] + sh.halves[2 * j + 1]);
-            if (with_j > threshold) {
-                digit = j;
-                break;
+        bool found = false;
+#pragma unroll
+        for (int j = BINS - 1; j >= 0; --j) {
+            const float with_j = above + __shfl_sync(0xffffffffu, total, j);
+            if (!found) {
+                if (with_j > threshold || j == 0) digit = j, found = true, with_digit = with_j;
+                else above = with_j;
             }
-            above = with_j;
         }
         base = above;
         t |= (unsigned)digit << shift;
+        // counting: as soon as exactly k elements lie at or above the prefix, they are the k largest, and the
+        // prefix cuts where the k-th largest value would (the counts are whole numbers, exact in 32-bit floats)
+        if (!WEIGHTED && with_digit == threshold + 0.5f) break;
     }
     return t;
 }
 
 template <bool IN_SMEM>
-__global__ void __launch_bounds__(S_THREADS)
+__global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
               int* __restrict__ out) {
     extern __shared__ __align__(16) float dyn[];
-    __shared__ SampleShared sh;
-    const int nseg = (vocab + 31) / 32;  // runs of 32 consecutive tokens
+    __shared__ Shared sh;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int blocks = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    const int rowi = blockIdx.x / blocks;
+    const Slice part = slice_of(vocab, rank, blocks);
     float* bins = dyn;
-    float* seg = bins + BINS * S_THREADS;
-    float* xs = seg + nseg;
+    float* run_mass = bins + BINS * THREADS;                   // [runs of this block]
+    float* xs = run_mass + slice_of(vocab, 0, blocks).runs;    // [tokens of this block]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int rowi = blockIdx.x;
     const float* row = logits + (size_t)rowi * vocab;
     const float temp = temperature[rowi];
     const bool greedy = !(temp > 0.f);
+    int copy = 0;
 
-    // the largest logit, and the scaled row into shared memory; eight loads in flight per thread
+    // the largest logit, and the scaled tokens into shared memory; eight loads in flight per thread
     MaxIdx mine{-INFINITY, 0x7fffffff};
-    for (int i0 = threadIdx.x; i0 < vocab; i0 += 8 * S_THREADS) {
+    for (int i0 = part.lo + threadIdx.x; i0 < part.hi; i0 += 8 * THREADS) {
         float v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = i0 + u * S_THREADS < vocab ? row[i0 + u * S_THREADS] : -INFINITY;
+        for (int u = 0; u < 8; ++u) v[u] = i0 + u * THREADS < part.hi ? row[i0 + u * THREADS] : -INFINITY;
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * S_THREADS;
-            if (i < vocab) {
+            const int i = i0 + u * THREADS;
+            if (i < part.hi) {
                 mine = better(mine, MaxIdx{v[u], i});
-                if (IN_SMEM && !greedy) xs[i] = v[u] / temp;
+                if (IN_SMEM && !greedy) xs[i - part.lo] = v[u] / temp;
             }
         }
     }
-    const MaxIdx best = block_argmax(mine, sh.best);  // its barriers also publish xs
+    const MaxIdx best = cluster_argmax(cluster, mine, sh);  // its barriers also publish xs
     if (greedy) {
-        if (threadIdx.x == 0) out[rowi] = best.i;
+        if (threadIdx.x == 0 && rank == 0) out[rowi] = best.i;
         return;
     }
     const float x_max = best.v / temp;
@@ -212,107 +260,168 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     // lowest key that stays after top-k: the k-th largest value (ties with it stay)
     unsigned floor_key = 0u;
     const int k = top_k[rowi];
-    if (k > 0 && k < vocab) floor_key = radix_search<IN_SMEM, false>(xs, row, temp, vocab, 0u, x_max, (float)k - 0.5f, bins, sh);
+    if (k > 0 && k < vocab)
+        floor_key = radix_search<IN_SMEM, false>(cluster, xs, row, temp, part, 0u, x_max, (float)k - 0.5f, bins, sh, copy);
 
     // top-p: a token stays iff the mass of strictly larger values is <= top_p, that is, iff its key is at
     // least the largest key T whose mass at and above T still exceeds top_p
     const float p_cut = top_p[rowi];
     if (p_cut < 1.f) {
         float z = 0.f;
-        for (int i = threadIdx.x; i < vocab; i += S_THREADS) {
-            const float x = scaled<IN_SMEM>(xs, row, temp, i);
+        for (int i = part.lo + threadIdx.x; i < part.hi; i += THREADS) {
+            const float x = scaled<IN_SMEM>(xs, row, temp, part.lo, i);
             if (ordered_key(x) >= floor_key) z += expf(x - x_max);
         }
-        z = block_sum(z, sh.sum);
-        floor_key = max(floor_key, radix_search<IN_SMEM, true>(xs, row, temp, vocab, floor_key, x_max, p_cut * z, bins, sh));
+        z = cluster_sum(cluster, sh, copy, z);
+        floor_key = max(floor_key, radix_search<IN_SMEM, true>(cluster, xs, row, temp, part, floor_key, x_max, p_cut * z, bins, sh, copy));
     }
 
-    // Inverse of the cumulative distribution in vocabulary order, in three levels: the mass of every run of 32
-    // tokens, of every group of runs (one group per warp), then a walk through one group and one run.
-    for (int s = warp; s < nseg; s += S_WARPS) {
-        const int i = s * 32 + lane;
+    // Inverse of the cumulative distribution in vocabulary order, level by level: the mass of every block's
+    // tokens, of every group of runs in a block (one group per warp), of every run of 32 tokens, then one run.
+    for (int s = warp; s < part.runs; s += WARPS) {
+        const int i = part.lo + s * 32 + lane;
         float e = 0.f;
-        if (i < vocab) {
-            const float x = scaled<IN_SMEM>(xs, row, temp, i);
+        if (i < part.hi) {
+            const float x = scaled<IN_SMEM>(xs, row, temp, part.lo, i);
             if (ordered_key(x) >= floor_key) e = expf(x - x_max);
         }
         e = warp_sum(e);
-        if (lane == 0) seg[s] = e;
+        if (lane == 0) run_mass[s] = e;
     }
     __syncthreads();
-    const int per = (nseg + S_WARPS - 1) / S_WARPS;  // runs per group
-    {
-        float g = 0.f;
-        for (int j = lane; j < per; j += 32) {
-            const int s = warp * per + j;
-            if (s < nseg) g += seg[s];
-        }
-        g = warp_sum(g);
-        if (lane == 0) sh.group[warp] = g;
+    const int per = (part.runs + WARPS - 1) / WARPS;  // runs per group
+    float group = 0.f;
+    for (int j = lane; j < per; j += 32) {
+        const int s = warp * per + j;
+        if (s < part.runs) group += run_mass[s];
     }
+    group = warp_sum(group);
+    if (lane == 0) sh.group[warp] = group;
     __syncthreads();
-    if (warp != 0) return;
+    float block_mass = 0.f;
+    for (int w = 0; w < WARPS; ++w) block_mass += sh.group[w];
+    cluster_share(cluster, sh, copy, block_mass);
+    if (warp != 0) return;  // no block touches another's shared memory from here on
+
+    // At every level: the first member at which the running sum passes the target; where rounding lets the
+    // target slip through a level, the last member of that level that has any mass.
     float z = 0.f;
-    for (int w = 0; w < S_WARPS; ++w) z += sh.group[w];
+    for (int r = 0; r < blocks; ++r) z += sh.shared_out[copy][r][0];
     const float target = uniform_from(seeds[rowi], counters[rowi]) * z;
-    // the first group, run and token at which the running sum passes the target; where rounding lets it slip
-    // through a level, the last one of that level that has any mass
-    float run = 0.f;
-    int g_found = -1, g_last = -1;
-    float run_at_last = 0.f;
-    for (int w = 0; w < S_WARPS; ++w) {
-        const float g = sh.group[w];
-        if (g > 0.f) {
-            g_last = w;
-            run_at_last = run;
-            if (run + g > target) {
-                g_found = w;
+    float run = 0.f, run_at_last = 0.f;
+    int found = -1, last = -1;
+    for (int r = 0; r < blocks; ++r) {
+        const float m = sh.shared_out[copy][r][0];
+        if (m > 0.f) {
+            last = r, run_at_last = run;
+            if (run + m > target) {
+                found = r;
                 break;
             }
         }
-        run += g;
+        run += m;
     }
-    if (g_found < 0) g_found = g_last, run = run_at_last;
-    int token = best.i;
-    if (g_found >= 0) {
-        int s_found = -1, s_last = -1;
-        for (int j = 0; j < per; ++j) {
-            const int s = g_found * per + j;
-            if (s >= nseg) break;
-            const float m = seg[s];
-            if (m > 0.f) {
-                s_last = s;
-                run_at_last = run;
-                if (run + m > target) {
-                    s_found = s;
-                    break;
-                }
+    if (found < 0) found = last, run = run_at_last;
+    if (found < 0) {  // no mass anywhere: the largest logit always stays, so only if the logits are not numbers
+        if (rank == 0 && lane == 0) out[rowi] = best.i;
+        return;
+    }
+    if (found != rank) return;
+
+    found = last = -1;
+    for (int w = 0; w < WARPS; ++w) {
+        const float m = sh.group[w];
+        if (m > 0.f) {
+            last = w, run_at_last = run;
+            if (run + m > target) {
+                found = w;
+                break;
             }
+        }
+        run += m;
+    }
+    if (found < 0) found = last, run = run_at_last;
+    if (found < 0) {  // only if the logits are not numbers
+        if (lane == 0) out[rowi] = best.i;
+        return;
+    }
+    const int first_run = found * per;
+    found = last = -1;
+    for (int s = first_run; s < min(part.runs, first_run + per); ++s) {
+        const float m = run_mass[s];
+        if (m > 0.f) {
+            last = s, run_at_last = run;
+            if (run + m > target) {
+                found = s;
+                break;
+            }
+        }
+        run += m;
+    }
+    if (found < 0) found = last, run = run_at_last;
+    if (found < 0) {
+        if (lane == 0) out[rowi] = best.i;
+        return;
+    }
+    const int i = part.lo + found * 32 + lane;
+    float e = 0.f;
+    if (i < part.hi) {
+        const float x = scaled<IN_SMEM>(xs, row, temp, part.lo, i);
+        if (ordered_key(x) >= floor_key) e = expf(x - x_max);
+    }
+    int token = -1, last_token = -1;
+#pragma unroll 1
+    for (int l = 0; l < 32; ++l) {
+        const float m = __shfl_sync(0xffffffffu, e, l);
+        if (token < 0 && m > 0.f) {
+            last_token = l;
+            if (run + m > target) token = l;
             run += m;
         }
-        if (s_found < 0) s_found = s_last, run = run_at_last;
-        if (s_found >= 0) {
-            const int i = s_found * 32 + lane;
-            float e = 0.f;
-            if (i < vocab) {
-                const float x = scaled<IN_SMEM>(xs, row, temp, i);
-                if (ordered_key(x) >= floor_key) e = expf(x - x_max);
-            }
-            int l_found = -1, l_last = -1;
-            for (int l = 0; l < 32; ++l) {
-                const float m = __shfl_sync(0xffffffffu, e, l);
-                if (l_found >= 0) continue;
-                if (m > 0.f) {
-                    l_last = l;
-                    if (run + m > target) l_found = l;
-                }
-                run += m;
-            }
-            if (l_found < 0) l_found = l_last;
-            if (l_found >= 0) token = s_found * 32 + l_found;
-        }
     }
-    if (lane == 0) out[rowi] = token;
+    if (token < 0) token = last_token;
+    if (lane == 0) out[rowi] = token < 0 ? best.i : part.lo + found * 32 + token;
+}
+
+struct Device {
+    int sms = 0, smem = 0;
+};
+const Device& device() {
+    static const Device d = [] {
+        Device v;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v.sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&v.smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        return v;
+    }();
+    return d;
+}
+
+// As many blocks per row as keep about half of the SMs busy, eight at most.
+int blocks_per_row(int rows) {
+    int blocks = 1;
+    while (blocks < MAX_CLUSTER && rows * blocks * 2 <= device().sms) blocks *= 2;
+    return blocks;
+}
+
+template <typename... KArgs, typename... Args>
+int launch_cluster(void (*kernel)(KArgs...), int rows, int blocks, size_t smem, bool pdl, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * blocks);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = blocks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace
@@ -320,7 +429,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 LLM_EXPORT int llm_argmax(const float* logits, int rows, int vocab, int* out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return LLM_ERR_BAD_ARGUMENT;
-    return launch_pdl(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, vocab, out);
+    return launch_cluster(argmax_kernel, rows, blocks_per_row(rows), 0, true, stream, logits, vocab, out);
 }
 
 LLM_EXPORT int llm_sample(const float* logits, int rows, int vocab, const float* temperature, const int* top_k,
@@ -328,25 +437,20 @@ LLM_EXPORT int llm_sample(const float* logits, int rows, int vocab, const float*
                           int* out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return LLM_ERR_BAD_ARGUMENT;
-    static const int smem_limit = [] {
-        int dev = 0, v = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-        return v - (int)sizeof(SampleShared) - 1024;
-    }();
-    const size_t seg_bytes = (size_t)(BINS * S_THREADS + (vocab + 31) / 32) * sizeof(float);
-    const size_t row_bytes = (size_t)vocab * sizeof(float);
-    if ((long long)(seg_bytes + row_bytes) <= (long long)smem_limit) {
-        static const cudaError_t opted =
-            cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
-        if (opted != cudaSuccess) return (int)opted;
-        sample_kernel<true><<<rows, S_THREADS, seg_bytes + row_bytes, stream>>>(logits, vocab, temperature, top_k, top_p, seeds, counters, out);
-    } else {
-        if ((long long)seg_bytes > (long long)smem_limit) return LLM_ERR_UNSUPPORTED;
-        static const cudaError_t opted =
-            cudaFuncSetAttribute(sample_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_limit);
-        if (opted != cudaSuccess) return (int)opted;
-        sample_kernel<false><<<rows, S_THREADS, seg_bytes, stream>>>(logits, vocab, temperature, top_k, top_p, seeds, counters, out);
-    }
-    return launch_status();
+    const long long room = device().smem - (long long)sizeof(Shared) - 1024;
+    auto bytes = [&](int blocks, bool with_tokens) {
+        const long long runs = ((vocab + 31) / 32 + blocks - 1) / blocks;
+        return (long long)sizeof(float) * (BINS * THREADS + runs + (with_tokens ? runs * 32 : 0));
+    };
+    int blocks = blocks_per_row(rows);
+    while (blocks < MAX_CLUSTER && bytes(blocks, true) > room) blocks *= 2;  // more blocks, so that the tokens fit
+    const bool in_smem = bytes(blocks, true) <= room;
+    if (bytes(blocks, in_smem) > room) return LLM_ERR_UNSUPPORTED;
+    static const cudaError_t opted[2] = {
+        cudaFuncSetAttribute(sample_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, device().smem - (int)sizeof(Shared) - 1024),
+        cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, device().smem - (int)sizeof(Shared) - 1024)};
+    if (opted[0] != cudaSuccess || opted[1] != cudaSuccess) return (int)(opted[0] != cudaSuccess ? opted[0] : opted[1]);
+    if (in_smem)
+        return launch_cluster(sample_kernel<true>, rows, blocks, (size_t)bytes(blocks, true), false, stream, logits, vocab, temperature, top_k, top_p, seeds, counters, out);
+    return launch_cluster(sample_kernel<false>, rows, blocks, (size_t)bytes(blocks, false), false, stream, logits, vocab, temperature, top_k, top_p, seeds, counters, out);
 }
