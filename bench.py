@@ -250,7 +250,7 @@ def main() -> int:
 
         # As the scheduler does it: a step's chosen tokens stay on the device and feed the next step, which is launched
         # before the host reads them (through pinned memory, one step late); every token reaches the host in the loop.
-        ahead = None  # (tokens on the device, their copy in pinned host memory, event after the copy)
+        ahead = None  # (tokens on the device, the same in pinned host memory, event after the kernel that wrote both)
 
         def one_step():
             nonlocal tokens, ahead
@@ -258,9 +258,8 @@ def main() -> int:
                 logits = step([StepEntry(n, [t], [0]) for n, t in zip(names, tokens)])
             else:
                 logits = step.decode_ahead(names, ahead[0])
-            chosen = sampler.on_device(logits, greedy, [0] * batch, [0] * batch)
-            host = torch.empty(chosen.shape, dtype=chosen.dtype, pin_memory=True)
-            host.copy_(chosen, non_blocking=True)
+            host = torch.empty((batch,), dtype=torch.int32, pin_memory=True)
+            chosen = sampler.on_device(logits, greedy, [0] * batch, [0] * batch, host_out=host)
             copied = torch.cuda.Event()
             copied.record()
             if ahead is not None:

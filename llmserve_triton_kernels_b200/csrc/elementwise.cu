@@ -279,3 +279,28 @@ LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int 
                           (__nv_bfloat16*)out, inter, total);
     return LLM_ERR_BAD_ARGUMENT;
 }
+
+// ---------------------------------------------------------------------------------------------
+// A step's integer arrays from pinned host memory to the device, read by the kernel itself: for a
+// few kilobytes one round trip over the bus is shorter than a copy by the copy engine, which the
+// stream has to hand over to and take back from.  `words` 32-bit words; the first `head_words`
+// come from `head` on the device instead where it is given (token ids that the step before chose
+// and the host has not seen yet).
+// ---------------------------------------------------------------------------------------------
+__global__ void fetch_words_kernel(const int* __restrict__ host, int* __restrict__ dev, const int* __restrict__ head,
+                                   int head_words, int words) {
+    pdl_trigger();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool from_head = head != nullptr && i < head_words;
+    // the host's memory does not change while the kernel runs, but no cached copy of it may outlive the kernel
+    const int v = i < words && !from_head ? __ldcv(host + i) : 0;
+    pdl_wait();  // the kernels before may still read the arrays of their step, and one of them writes `head`
+    if (i < words) dev[i] = from_head ? head[i] : v;
+}
+
+LLM_EXPORT int llm_fetch_words(const int* host, int* dev, const int* head, int head_words, int words, cudaStream_t stream) {
+    if (words <= 0) return 0;
+    if (head_words < 0 || head_words > words) return LLM_ERR_BAD_ARGUMENT;
+    const int threads = 256;
+    return launch_pdl(fetch_words_kernel, dim3((words + threads - 1) / threads), dim3(threads), 0, stream, host, dev, head, head_words, words);
+}

@@ -69,6 +69,13 @@ struct Shared {
     float shared_out[2][MAX_CLUSTER][WARPS];  // written by every block of the cluster; two copies used in turn
 };
 
+// A row's token: to the device, and where asked for also straight into pinned host memory, which
+// spares the stream a copy after the kernel.
+__device__ __forceinline__ void put(int* out, int* host_out, int row, int token) {
+    out[row] = token;
+    if (host_out != nullptr) host_out[row] = token;
+}
+
 // Largest value and its lowest index over the block; every thread gets the result.
 __device__ MaxIdx block_argmax(MaxIdx mine, MaxIdx* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -127,7 +134,7 @@ __device__ __forceinline__ float cluster_sum(cg::cluster_group& cluster, Shared&
 }
 
 __global__ void __launch_bounds__(THREADS)
-argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out, int* __restrict__ host_out) {
     __shared__ Shared sh;
     cg::cluster_group cluster = cg::this_cluster();
     const int blocks = (int)cluster.num_blocks(), rowi = blockIdx.x / blocks;
@@ -144,7 +151,7 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
         for (int u = 0; u < 8; ++u) mine = better(mine, MaxIdx{v[u], i0 + u * THREADS});
     }
     const MaxIdx best = cluster_argmax(cluster, mine, sh);
-    if (threadIdx.x == 0 && cluster.block_rank() == 0) out[rowi] = best.i;
+    if (threadIdx.x == 0 && cluster.block_rank() == 0) put(out, host_out, rowi, best.i);
 }
 
 // ---- temperature sampling -----------------------------------------------------------------------
@@ -219,7 +226,7 @@ __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
-              int* __restrict__ out) {
+              int* __restrict__ out, int* __restrict__ host_out) {
     extern __shared__ __align__(16) float dyn[];
     __shared__ Shared sh;
     cg::cluster_group cluster = cg::this_cluster();
@@ -252,7 +259,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     }
     const MaxIdx best = cluster_argmax(cluster, mine, sh);  // its barriers also publish xs
     if (greedy) {
-        if (threadIdx.x == 0 && rank == 0) out[rowi] = best.i;
+        if (threadIdx.x == 0 && rank == 0) put(out, host_out, rowi, best.i);
         return;
     }
     const float x_max = best.v / temp;
@@ -323,7 +330,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     }
     if (found < 0) found = last, run = run_at_last;
     if (found < 0) {  // no mass anywhere: the largest logit always stays, so only if the logits are not numbers
-        if (rank == 0 && lane == 0) out[rowi] = best.i;
+        if (rank == 0 && lane == 0) put(out, host_out, rowi, best.i);
         return;
     }
     if (found != rank) return;
@@ -342,7 +349,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     }
     if (found < 0) found = last, run = run_at_last;
     if (found < 0) {  // only if the logits are not numbers
-        if (lane == 0) out[rowi] = best.i;
+        if (lane == 0) put(out, host_out, rowi, best.i);
         return;
     }
     const int first_run = found * per;
@@ -360,7 +367,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     }
     if (found < 0) found = last, run = run_at_last;
     if (found < 0) {
-        if (lane == 0) out[rowi] = best.i;
+        if (lane == 0) put(out, host_out, rowi, best.i);
         return;
     }
     const int i = part.lo + found * 32 + lane;
@@ -380,7 +387,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         }
     }
     if (token < 0) token = last_token;
-    if (lane == 0) out[rowi] = token < 0 ? best.i : part.lo + found * 32 + token;
+    if (lane == 0) put(out, host_out, rowi, token < 0 ? best.i : part.lo + found * 32 + token);
 }
 
 struct Device {
@@ -426,15 +433,16 @@ int launch_cluster(void (*kernel)(KArgs...), int rows, int blocks, size_t smem, 
 
 }  // namespace
 
-LLM_EXPORT int llm_argmax(const float* logits, int rows, int vocab, int* out, cudaStream_t stream) {
+// `host_out` (may be null): pinned host memory that gets the tokens too, valid once the stream has passed the kernel.
+LLM_EXPORT int llm_argmax(const float* logits, int rows, int vocab, int* out, int* host_out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return LLM_ERR_BAD_ARGUMENT;
-    return launch_cluster(argmax_kernel, rows, blocks_per_row(rows), 0, true, stream, logits, vocab, out);
+    return launch_cluster(argmax_kernel, rows, blocks_per_row(rows), 0, true, stream, logits, vocab, out, host_out);
 }
 
 LLM_EXPORT int llm_sample(const float* logits, int rows, int vocab, const float* temperature, const int* top_k,
                           const float* top_p, const unsigned long long* seeds, const unsigned long long* counters,
-                          int* out, cudaStream_t stream) {
+                          int* out, int* host_out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return LLM_ERR_BAD_ARGUMENT;
     const long long room = device().smem - (long long)sizeof(Shared) - 1024;
@@ -451,6 +459,6 @@ LLM_EXPORT int llm_sample(const float* logits, int rows, int vocab, const float*
         cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, device().smem - (int)sizeof(Shared) - 1024)};
     if (opted[0] != cudaSuccess || opted[1] != cudaSuccess) return (int)(opted[0] != cudaSuccess ? opted[0] : opted[1]);
     if (in_smem)
-        return launch_cluster(sample_kernel<true>, rows, blocks, (size_t)bytes(blocks, true), false, stream, logits, vocab, temperature, top_k, top_p, seeds, counters, out);
-    return launch_cluster(sample_kernel<false>, rows, blocks, (size_t)bytes(blocks, false), false, stream, logits, vocab, temperature, top_k, top_p, seeds, counters, out);
+        return launch_cluster(sample_kernel<true>, rows, blocks, (size_t)bytes(blocks, true), false, stream, logits, vocab, temperature, top_k, top_p, seeds, counters, out, host_out);
+    return launch_cluster(sample_kernel<false>, rows, blocks, (size_t)bytes(blocks, false), false, stream, logits, vocab, temperature, top_k, top_p, seeds, counters, out, host_out);
 }

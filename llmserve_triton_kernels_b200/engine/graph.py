@@ -3,7 +3,7 @@
 A step in which every request brings exactly one token and wants its logits has the same
 shapes every time, so the whole pass — some hundred and fifty launches for 22 layers — is
 captured once per batch size and replayed.  Only the step's integer arrays change: they are
-written into a pinned buffer of fixed layout and copied to the device with one copy before the
+written into a pinned buffer of fixed layout and brought to the device in one piece before the
 replay.  The reference notes launch and host overhead as its next bottleneck and CUDA graphs as
 the cure (its docs/PROFILING.md:19-20 and the closing notes of its design document) but does not build them.
 
@@ -68,7 +68,7 @@ class DecodeGraph:
     def fill(self, tokens, lengths: list[int], state_slots: np.ndarray, group_arrays) -> None:
         """Write the step's arrays into the pinned buffer and start their copy to the device.  ``tokens``: a list
         of ids on the host, or an int32 tensor ``[R]`` on the device (the step before has put its choices there and
-        the host has not seen them yet), which is copied over the token ids on the device after the host's arrays."""
+        the host has not seen them yet), which takes the place of the host's token ids on the way."""
         self.copied.synchronize()  # the previous copy has left the pinned buffer
         R = self.R
         on_device = isinstance(tokens, torch.Tensor)
@@ -80,10 +80,10 @@ class DecodeGraph:
             dst = self._piece_np(7 + 2 * g).reshape(R, self.widths[g])
             dst[:, : table.shape[1]] = table
             self._piece_np(8 + 2 * g)[:] = slot_map
-        self.dev.copy_(self.host, non_blocking=True)
+        # a kernel that reads the pinned buffer (shorter than a copy by the copy engine) and takes the token ids
+        # from the device where they are there
+        ops.fetch_words(self.host, self.dev, tokens if on_device else None)
         self.copied.record()
-        if on_device:
-            self._piece(0).copy_(tokens, non_blocking=True)
 
     def run(self) -> torch.Tensor:
         """Logits ``[R, vocab]`` of the step whose arrays were filled last.  The tensor is

@@ -104,8 +104,8 @@ class _Ahead:
 
     reqs: list  # the requests of the step, in the order of its rows
     device_tokens: object  # int32 [rows] on the device: what the step chose
-    host_tokens: object  # the same on the host (pinned memory), valid once `copied` has happened
-    copied: object  # event after the copy to the host
+    host_tokens: object  # the same on the host (pinned memory, written by the sampling kernel), valid once `copied` has happened
+    copied: object  # event after that kernel
 
 
 class Scheduler:
@@ -252,20 +252,23 @@ class Scheduler:
             counters = [len(r.generated) for r in sampled]
             if self.run_ahead and len(sampled) == len(plan) and all(n == 1 for _, n in plan):
                 # a decode step of every running request: its tokens stay on the device for now
-                self._ahead = self._remember(sampled, self.sampler.on_device(logits, params, seeds, counters))
+                self._ahead = self._sample_ahead(sampled, logits, params, seeds, counters)
             else:
                 self._append(sampled, self.sampler(logits, params, seeds, counters), events)
         return events
 
     # ------------------------------------------------------------------ one step ahead of the host
-    def _remember(self, reqs: list[Request], device_tokens) -> _Ahead:
-        if not device_tokens.is_cuda:
-            return _Ahead(reqs, device_tokens, device_tokens.clone(), None)
-        host = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=True)
-        host.copy_(device_tokens, non_blocking=True)
-        copied = torch.cuda.Event()
-        copied.record()
-        return _Ahead(reqs, device_tokens, host, copied)
+    def _sample_ahead(self, reqs: list[Request], logits, params, seeds, counters) -> _Ahead:
+        """Tokens chosen and left on the device; the sampling kernel writes them into pinned host memory as well,
+        where the host may read them once the event has happened."""
+        if not logits.is_cuda:
+            tokens = self.sampler.on_device(logits, params, seeds, counters)
+            return _Ahead(reqs, tokens, tokens.clone(), None)
+        host = torch.empty((logits.shape[0],), dtype=torch.int32, pin_memory=True)
+        tokens = self.sampler.on_device(logits, params, seeds, counters, host_out=host)
+        written = torch.cuda.Event()
+        written.record()
+        return _Ahead(reqs, tokens, host, written)
 
     def _can_run_ahead(self, ahead: _Ahead) -> bool:
         """The step after ``ahead`` can be launched before ``ahead``'s tokens are known: the same requests decode on
@@ -288,8 +291,7 @@ class Scheduler:
             r.num_computed += 1
         self.stats.decode_tokens += len(reqs)
         self.stats.last_batch_tokens = self.stats.last_batch_requests = len(reqs)
-        tokens = self.sampler.on_device(logits, [r.params for r in reqs], [r.seed for r in reqs], [len(r.generated) + 1 for r in reqs])
-        return self._remember(reqs, tokens)
+        return self._sample_ahead(reqs, logits, [r.params for r in reqs], [r.seed for r in reqs], [len(r.generated) + 1 for r in reqs])
 
     def _collect(self, ahead: _Ahead, events: list[TokenEvent]) -> None:
         """The host reads the tokens of a step launched earlier.  A request that has ended meanwhile (its

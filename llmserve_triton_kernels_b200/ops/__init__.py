@@ -25,6 +25,7 @@ _SIGNATURES = {
     "llm_rmsnorm": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
     "llm_rope_kv_write": [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "llm_fetch_words": [_vp, _vp, _vp, _i, _i, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_ulonglong, _vp],
     "llm_linear_decode_qkv": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
@@ -38,8 +39,8 @@ _SIGNATURES = {
     "llm_attention_mma": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     "llm_attention_mma_routed": [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
     "llm_attention_tcgen05": [_vp, _i, _vp, _i, _vp, ctypes.c_longlong, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp],
-    "llm_argmax": [_vp, _i, _i, _vp, _vp],
-    "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "llm_argmax": [_vp, _i, _i, _vp, _vp, _vp],
+    "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 
 
@@ -661,11 +662,33 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
-    """Index of the largest logit of each row (the lowest index among equals) -> int32 ``[rows]``."""
+def fetch_words(host: torch.Tensor, dev: torch.Tensor, head: torch.Tensor | None = None) -> None:
+    """``dev[:] = host`` for int32 arrays of one size, ``host`` in pinned host memory: the kernel reads the host's
+    memory itself.  Where ``head`` (int32, on the device) is given, the first ``len(head)`` words come from it
+    instead.  The host must leave ``host`` alone until the stream has passed this point."""
+    _need(host.dtype == torch.int32 and dev.dtype == torch.int32 and host.numel() == dev.numel(), "two int32 arrays of one size")
+    _need(host.is_pinned() and dev.is_cuda and host.is_contiguous() and dev.is_contiguous(), "from pinned host memory to the device")
+    if head is not None:
+        _need(head.dtype == torch.int32 and head.is_cuda and head.is_contiguous() and head.numel() <= dev.numel(), "head: int32 on the device")
+    code = _launch("llm_fetch_words", _ptr(host), _ptr(dev), _ptr(head), 0 if head is None else head.numel(), host.numel(), _stream())
+    _check(code, "fetch_words")
+
+
+def _host_out(host_out: torch.Tensor | None, rows: int) -> int | None:
+    if host_out is None:
+        return None
+    _need(host_out.dtype == torch.int32 and host_out.numel() == rows and host_out.is_pinned() and host_out.is_contiguous(),
+          "host_out must be int32 [rows] in pinned host memory")
+    return host_out.data_ptr()
+
+
+def argmax(logits: torch.Tensor, host_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Index of the largest logit of each row (the lowest index among equals) -> int32 ``[rows]``.  ``host_out``
+    (int32 ``[rows]`` in pinned host memory) gets the same from the kernel itself, valid once the stream has
+    passed this point."""
     _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous float32 matrix")
     out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    _check(_launch("llm_argmax", _ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _stream()), "argmax")
+    _check(_launch("llm_argmax", _ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _host_out(host_out, logits.shape[0]), _stream()), "argmax")
     return out
 
 
@@ -676,11 +699,12 @@ def sample(
     top_p: torch.Tensor,
     seeds: torch.Tensor,
     counters: torch.Tensor,
+    host_out: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """One token per row: argmax where ``temperature <= 0``, else a draw from
     ``softmax(logits / temperature)`` cut by ``top_k`` (0: off) and ``top_p`` (1: off) at the
     uniform number that ``(seed, counter)`` gives.  All parameter tensors are ``[rows]`` on the
-    device: float32, int32, float32, int64, int64."""
+    device: float32, int32, float32, int64, int64.  ``host_out``: as for ``argmax``."""
     _need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous float32 matrix")
     rows = logits.shape[0]
     for t, dt, name in ((temperature, torch.float32, "temperature"), (top_k, torch.int32, "top_k"), (top_p, torch.float32, "top_p"), (seeds, torch.int64, "seeds"), (counters, torch.int64, "counters")):
@@ -688,7 +712,7 @@ def sample(
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     code = _launch("llm_sample", 
         _ptr(logits), rows, logits.shape[1], _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(seeds), _ptr(counters),
-        _ptr(out), _stream(),
+        _ptr(out), _host_out(host_out, rows), _stream(),
     )
     _check(code, "sample")
     return out

@@ -29,13 +29,16 @@ class Sampler:
             return []
         return self.on_device(logits, params, seeds, counters).tolist()
 
-    def on_device(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int], counters: list[int]) -> torch.Tensor:
+    def on_device(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int], counters: list[int],
+                  host_out: torch.Tensor | None = None) -> torch.Tensor:
         """The same, but the token ids stay on the device (int32 ``[rows]``): the next step can be fed from there
-        before the host has seen them."""
+        before the host has seen them.  ``host_out`` (int32 ``[rows]``, pinned host memory) gets them too, written by
+        the kernel, and may be read once the stream has passed this point."""
         rows = logits.shape[0]
         self.h2d_bytes = 0
+        extra = {} if host_out is None else {"host_out": host_out}
         if all(p.greedy for p in params):
-            tokens = ops.argmax(logits)
+            tokens = ops.argmax(logits, **extra)
         else:
             # one buffer, one copy: [temperature | top_k | top_p | - | seeds (64-bit) | counters (64-bit)]
             packed = np.zeros(8 * rows, dtype=np.int32)
@@ -56,6 +59,7 @@ class Sampler:
                 dev[2 * rows : 3 * rows].view(torch.float32),
                 dev[4 * rows : 6 * rows].view(torch.int64),
                 dev[6 * rows : 8 * rows].view(torch.int64),
+                **extra,
             )
         self.d2h_bytes = rows * 4
         return tokens

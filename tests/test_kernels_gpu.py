@@ -410,6 +410,38 @@ def test_sample_matches_plain_sampler(vocab):
     assert got[9] == int(torch.argmax(logits[9]).item())  # a tiny top_p keeps the top token only
 
 
+def test_tokens_also_written_to_pinned_host_memory():
+    rows, vocab = 6, 1000
+    logits = rnd(rows, vocab, seed=16)
+    host = torch.full((rows,), -1, dtype=torch.int32).pin_memory()
+    got = ops().argmax(logits, host_out=host)
+    torch.cuda.synchronize()
+    assert host.tolist() == got.tolist() == torch.argmax(logits.cpu(), dim=-1).tolist()
+    host.fill_(-1)
+    t = torch.full((rows,), 0.7, device=DEV)
+    k = torch.full((rows,), 20, dtype=torch.int32, device=DEV)
+    p = torch.full((rows,), 0.9, device=DEV)
+    seeds = torch.arange(rows, dtype=torch.int64, device=DEV)
+    counters = torch.zeros(rows, dtype=torch.int64, device=DEV)
+    got = ops().sample(logits, t, k, p, seeds, counters, host_out=host)
+    torch.cuda.synchronize()
+    assert host.tolist() == got.tolist() == plain_ops.sample(logits, t, k, p, seeds, counters).tolist()
+
+
+@pytest.mark.parametrize("words,head", [(5, 0), (1092, 8), (70000, 64), (300, 300)])
+def test_fetch_words_from_pinned_memory(words, head):
+    host = torch.randint(-(2**31), 2**31 - 1, (words,), dtype=torch.int32).pin_memory()
+    dev = torch.zeros(words, dtype=torch.int32, device=DEV)
+    for round_ in range(2):  # the same addresses with new contents: nothing stale may be read
+        host.copy_(torch.randint(-(2**31), 2**31 - 1, (words,), dtype=torch.int32))
+        first = torch.arange(head, dtype=torch.int32, device=DEV) + 7 * round_
+        ops().fetch_words(host, dev, first if head else None)
+        torch.cuda.synchronize()
+        want = host.clone()
+        want[:head] = first.cpu()
+        assert torch.equal(dev.cpu(), want)
+
+
 def test_sample_follows_the_distribution():
     vocab, draws = 50, 4000
     logits = rnd(1, vocab, seed=15).repeat(draws, 1).contiguous()
