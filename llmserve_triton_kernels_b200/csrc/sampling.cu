@@ -200,19 +200,17 @@ __device__ unsigned radix_search(cg::cluster_group& cluster, const float* xs, co
         float total = 0.f;  // lane j < 16: bin j over the cluster
         if (lane < BINS)
             for (int r = 0; r < blocks; ++r) total += sh.shared_out[copy][r][2 * lane] + sh.shared_out[copy][r][2 * lane + 1];
-        float above = base;  // weight above digit j, from the top digit down
-        float with_digit = 0.f;
-        int digit = 0;
-        bool found = false;
+        // lane j < 16: the weight at and above digit j within the prefix; the largest digit that still passes
+        float at_and_above = total;
 #pragma unroll
-        for (int j = BINS - 1; j >= 0; --j) {
-            const float with_j = above + __shfl_sync(0xffffffffu, total, j);
-            if (!found) {
-                if (with_j > threshold || j == 0) digit = j, found = true, with_digit = with_j;
-                else above = with_j;
-            }
+        for (int o = 1; o < BINS; o <<= 1) {
+            const float v = __shfl_down_sync(0xffffffffu, at_and_above, o);
+            if (lane + o < BINS) at_and_above += v;
         }
-        base = above;
+        const unsigned passing = __ballot_sync(0xffffffffu, lane >= 1 && lane < BINS && base + at_and_above > threshold);
+        const int digit = passing ? 31 - __clz(passing) : 0;
+        const float with_digit = base + __shfl_sync(0xffffffffu, at_and_above, digit);
+        base += __shfl_sync(0xffffffffu, lane < BINS ? at_and_above : 0.f, digit + 1);  // what lies above the digit
         t |= (unsigned)digit << shift;
         // counting: as soon as exactly k elements lie at or above the prefix, they are the k largest, and the
         // prefix cuts where the k-th largest value would (the counts are whole numbers, exact in 32-bit floats)
