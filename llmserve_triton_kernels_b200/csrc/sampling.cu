@@ -236,7 +236,9 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     float* xs = run_mass + slice_of(vocab, 0, blocks).runs;    // [tokens of this block]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* row = logits + (size_t)rowi * vocab;
-    const float temp = temperature[rowi];
+    const float temp = temperature[rowi], p_cut = top_p[rowi];
+    const int k = top_k[rowi];
+    const unsigned long long seed = seeds[rowi], counter = counters[rowi];
     const bool greedy = !(temp > 0.f);
     int copy = 0;
 
@@ -264,13 +266,11 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 
     // lowest key that stays after top-k: the k-th largest value (ties with it stay)
     unsigned floor_key = 0u;
-    const int k = top_k[rowi];
     if (k > 0 && k < vocab)
         floor_key = radix_search<IN_SMEM, false>(cluster, xs, row, temp, part, 0u, x_max, (float)k - 0.5f, bins, sh, copy);
 
     // top-p: a token stays iff the mass of strictly larger values is <= top_p, that is, iff its key is at
     // least the largest key T whose mass at and above T still exceeds top_p
-    const float p_cut = top_p[rowi];
     if (p_cut < 1.f) {
         float z = 0.f;
         for (int i = part.lo + threadIdx.x; i < part.hi; i += THREADS) {
@@ -312,7 +312,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     // target slip through a level, the last member of that level that has any mass.
     float z = 0.f;
     for (int r = 0; r < blocks; ++r) z += sh.shared_out[copy][r][0];
-    const float target = uniform_from(seeds[rowi], counters[rowi]) * z;
+    const float target = uniform_from(seed, counter) * z;
     float run = 0.f, run_at_last = 0.f;
     int found = -1, last = -1;
     for (int r = 0; r < blocks; ++r) {
