@@ -39,7 +39,7 @@ class Status(Enum):
     FINISHED = "finished"
 
 
-@dataclass
+@dataclass(eq=False)  # a request is itself: `in` and `remove` go by identity, not by comparing every field
 class Request:
     req_id: int
     prompt_ids: list[int]
