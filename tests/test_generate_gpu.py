@@ -58,9 +58,10 @@ def test_temperature_sampling_matches_the_plain_sampler(name, model_folder):
     plain_cfg, w = plain_llama.read_model(folder)
     prompts = tiny_configs.prompts(name)
     llm = engine(folder, "float32")
-    outs = llm.generate(prompts, SamplingParams(max_new_tokens=16, temperature=0.8, seed=31))
-    for out, prompt in zip(outs, prompts):
-        assert out.token_ids == plain_llama.generate(plain_cfg, w, prompt, 16, temperature=0.8, seed=31)
+    for temperature, top_k, top_p in ((0.8, 0, 1.0), (1.3, 7, 0.85)):
+        outs = llm.generate(prompts, SamplingParams(max_new_tokens=16, temperature=temperature, top_k=top_k, top_p=top_p, seed=31))
+        for out, prompt in zip(outs, prompts):
+            assert out.token_ids == plain_llama.generate(plain_cfg, w, prompt, 16, temperature=temperature, top_k=top_k, top_p=top_p, seed=31)
 
 
 @pytest.mark.parametrize("name", ["a", "b"])
