@@ -122,7 +122,14 @@ def _code(dtype: torch.dtype) -> int:
     raise KernelError(f"element type {dtype} is not supported (float32 or bfloat16)")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle.  Asked once per launch, so by the short way where torch has one (the Stream
+    object of ``torch.cuda.current_stream()`` costs several microseconds to build)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
