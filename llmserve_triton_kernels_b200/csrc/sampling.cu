@@ -403,10 +403,12 @@ const Device& device() {
     return d;
 }
 
-// As many blocks per row as keep about half of the SMs busy, eight at most.
-int blocks_per_row(int rows) {
+// Blocks per row: doubled while all blocks still find a place at once (`per_sm` blocks fit on an SM), `most` at most.
+// Measured in a graph, 32,000 logits a row: argmax of 8 rows 4.0 / 3.0 / 2.6 / 3.0 us with 1 / 2 / 4 / 8 blocks, of 64
+// rows 6.1 / 4.4 / 3.8 / 8.5 us; sampling with both cuts 69 / 50 / 41 / 41 us for 8 rows, 77 / 53 / 81 / 185 us for 64.
+int blocks_per_row(int rows, int per_sm, int most) {
     int blocks = 1;
-    while (blocks < MAX_CLUSTER && rows * blocks * 2 <= device().sms) blocks *= 2;
+    while (blocks < most && rows * blocks * 2 <= device().sms * per_sm) blocks *= 2;
     return blocks;
 }
 
@@ -435,7 +437,7 @@ int launch_cluster(void (*kernel)(KArgs...), int rows, int blocks, size_t smem, 
 LLM_EXPORT int llm_argmax(const float* logits, int rows, int vocab, int* out, int* host_out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return LLM_ERR_BAD_ARGUMENT;
-    return launch_cluster(argmax_kernel, rows, blocks_per_row(rows), 0, true, stream, logits, vocab, out, host_out);
+    return launch_cluster(argmax_kernel, rows, blocks_per_row(rows, 2, 4), 0, true, stream, logits, vocab, out, host_out);
 }
 
 LLM_EXPORT int llm_sample(const float* logits, int rows, int vocab, const float* temperature, const int* top_k,
@@ -448,7 +450,7 @@ LLM_EXPORT int llm_sample(const float* logits, int rows, int vocab, const float*
         const long long runs = ((vocab + 31) / 32 + blocks - 1) / blocks;
         return (long long)sizeof(float) * (BINS * THREADS + runs + (with_tokens ? runs * 32 : 0));
     };
-    int blocks = blocks_per_row(rows);
+    int blocks = blocks_per_row(rows, 1, MAX_CLUSTER);
     while (blocks < MAX_CLUSTER && bytes(blocks, true) > room) blocks *= 2;  // more blocks, so that the tokens fit
     const bool in_smem = bytes(blocks, true) <= room;
     if (bytes(blocks, in_smem) > room) return LLM_ERR_UNSUPPORTED;
