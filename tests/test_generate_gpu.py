@@ -122,6 +122,58 @@ def test_requests_that_end_while_the_engine_runs_ahead_of_the_host(name, model_f
     assert llm.cache.num_free_pages == llm.cache.num_pages
 
 
+@pytest.mark.parametrize("name,stream_seed", [("a", 0), ("b", 1), ("a", 2)])
+def test_requests_that_come_go_and_are_put_back_at_random(name, stream_seed, model_folder):
+    """A stream of requests driven step by step: they arrive while others decode (so graph steps that run ahead of the
+    host alternate with mixed steps), some are aborted, pages are so few that the newest request is put back and
+    computed again, half of them sample.  What every request that is not aborted generates is what the plain
+    implementation generates for it alone, and in the end every page is free."""
+    import random
+
+    from llmserve_triton_kernels_b200 import SamplingParams
+
+    cfg, seed, _, _ = tiny_configs.TINY[name]
+    folder = model_folder(cfg, seed, torch.float32)
+    plain_cfg, w = plain_llama.read_model(folder)
+    rng = random.Random(stream_seed)
+    llm = engine(folder, "float32", num_blocks=9, max_batch_size=3, max_num_batched_tokens=24, chunk_size=8)
+    sched = llm.scheduler
+    assert sched.run_ahead
+    arrivals = []  # (step at which it arrives, prompt, params)
+    for i in range(10):
+        prompt = [rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(2, 24))]
+        new = rng.randint(4, 24)
+        sampled = i % 2 == 1
+        params = SamplingParams(max_new_tokens=new, temperature=0.9 if sampled else 0.0, top_k=rng.choice([0, 6]) if sampled else 0,
+                                top_p=rng.choice([1.0, 0.9]) if sampled else 1.0, seed=100 + i)
+        arrivals.append((rng.randint(0, 14), prompt, params))
+    arrivals.sort(key=lambda a: a[0])
+    abort_at = {arrivals[3][0] + 2: 3, arrivals[7][0] + 1: 7}  # step -> which arrival is aborted then
+    ids, preempted_before, step_no = {}, sched.stats.preemptions, 0
+    while step_no < 400 and (len(ids) < len(arrivals) or sched.has_unfinished()):
+        for i, (at, prompt, params) in enumerate(arrivals):
+            if at == step_no:
+                ids[i] = sched.add_request(prompt, params)
+        if step_no in abort_at and abort_at[step_no] in ids:
+            sched.abort(ids[abort_at[step_no]])
+        sched.step()
+        step_no += 1
+    assert not sched.has_unfinished()
+    aborted = 0
+    for i, (at, prompt, params) in enumerate(arrivals):
+        r = sched.finished[ids[i]]
+        if r.finish_reason == "abort":
+            aborted += 1
+            continue
+        want = plain_llama.generate(plain_cfg, w, prompt, params.max_new_tokens, temperature=params.temperature, top_k=params.top_k,
+                                    top_p=params.top_p, seed=params.seed)
+        assert r.generated == want, f"request {i}"
+    assert aborted <= 2
+    assert sched.stats.preemptions > preempted_before  # the pages were few enough
+    assert llm.cache.num_free_pages == llm.cache.num_pages
+    llm.cache.check()
+
+
 @pytest.mark.parametrize("name", ["c", "d"])
 def test_one_kernel_decode_step_equals_the_step_kernel_by_kernel(name, model_folder, monkeypatch):
     """Head sizes 64 and 128 with up to 8 requests can decode through one cooperative kernel (an
