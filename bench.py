@@ -13,6 +13,9 @@ tokens; ``roofline`` relates the bytes a decode step has to read (every weight o
 cache of the live requests) to its time; ``points`` holds decode at batch 1 and 64.
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from an earlier
 measurement on the same pool (and the line says which).
+
+``python bench.py --sweep [--steps K]`` prints no JSON line but two tables: decode steps over batch sizes and
+context lengths, and prefills over prompt lengths, timed the same way.
 """
 
 from __future__ import annotations
@@ -194,6 +197,8 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (recorded in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the end-to-end run")
+    ap.add_argument("--sweep", action="store_true",
+                    help="instead of the one line: a table of decode steps over batch sizes and context lengths and of prefills over prompt lengths")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")
@@ -227,24 +232,25 @@ def main() -> int:
         return [torch.randint(0, cfg_dict["vocab_size"], (length,), generator=g).tolist() for _ in range(batch)]
 
     llm = LLM(cfg_dict, dtype="bfloat16", device=device, seed=0, block_size=page_size,
-              num_blocks=64 * (-(-(PROMPT_LEN + NEW_TOKENS + 64) // page_size)) + 256, max_batch_size=64,
+              num_blocks=64 * (-(-((1536 if args.sweep else PROMPT_LEN) + max(NEW_TOKENS, total_new) + 64) // page_size)) + 256, max_batch_size=64,
               max_num_batched_tokens=8192)
     cfg = llm.config
     numbers = model_numbers(cfg)
     weight_bytes = llm.model.weight_bytes()
     flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=device)  # larger than the 126 MB L2
 
-    def decode_run(batch: int, k: int, w: int) -> dict:
+    def decode_run(batch: int, k: int, w: int, prompt_len: int = PROMPT_LEN) -> dict:
         """Prefill ``batch`` prompts (untimed), then w warm-up and k timed decode steps through the
         step function and the device sampler; the next token never leaves the device between steps
         except for the read that the engine itself does."""
         llm.cache.reset()
         step, sampler = llm.step_function, llm.sampler
         names = [f"b{i}" for i in range(batch)]
-        prompts = tokens_for(batch, PROMPT_LEN, seed=1)
+        prompts = tokens_for(batch, prompt_len, seed=1)
         greedy = [SamplingParams()] * batch
-        for i in range(0, batch, 8):  # prefill eight at a time
-            step([StepEntry(n, p, []) for n, p in zip(names[i : i + 8], prompts[i : i + 8])])
+        per_step = max(1, 4096 // prompt_len)  # prefill eight prompts of 512 tokens at a time
+        for i in range(0, batch, per_step):
+            step([StepEntry(n, p, []) for n, p in zip(names[i : i + per_step], prompts[i : i + per_step])])
         tokens = [p[-1] for p in prompts]
         launches0 = ops.launch_count()
 
@@ -286,7 +292,7 @@ def main() -> int:
             torch.cuda.synchronize()
             clocks.end()
         ms = start.elapsed_time(end)
-        context = PROMPT_LEN + w + (k + 1) / 2.0  # mean number of cached tokens a timed step reads per request
+        context = prompt_len + w + (k + 1) / 2.0  # mean number of cached tokens a timed step reads per request
         bytes_per_step = weight_bytes + batch * context * numbers["kv_bytes_per_token"]
         out = {
             "tokens_per_s": batch * k / (ms / 1e3), "ms_per_step": ms / k, "bytes_per_step": bytes_per_step,
@@ -297,16 +303,16 @@ def main() -> int:
             llm.cache.free_request(n)
         return out
 
-    def prefill_run() -> dict:
+    def prefill_run(n_tokens: int = PREFILL_TOKENS) -> dict:
         llm.cache.reset()
-        prompt = tokens_for(1, PREFILL_TOKENS, seed=2)[0]
+        prompt = tokens_for(1, n_tokens, seed=2)[0]
         times = []
         for i in range(3 + 3):
             flush.fill_(1)
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             start.record()
-            logits = llm.step_function([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+            logits = llm.step_function([StepEntry("p", prompt, [n_tokens - 1])])
             ops.argmax(logits)
             end.record()
             torch.cuda.synchronize()
@@ -314,8 +320,8 @@ def main() -> int:
             if i >= 3:
                 times.append(start.elapsed_time(end))
         ms = statistics.median(times)
-        flops = prefill_flops(cfg, PREFILL_TOKENS)
-        return {"value": PREFILL_TOKENS / (ms / 1e3), "tokens": PREFILL_TOKENS, "ms": ms,
+        flops = prefill_flops(cfg, n_tokens)
+        return {"value": n_tokens / (ms / 1e3), "tokens": n_tokens, "ms": ms,
                 "frac": flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "tflops": flops / (ms / 1e3) / 1e12}
 
     def e2e_run(batch: int) -> dict:
@@ -331,6 +337,23 @@ def main() -> int:
         return {"value": decoded / (last - first), "unit": "tokens/s", "h2d_bytes_per_step": llm.step_function.h2d_bytes,
                 "d2h_bytes_per_step": llm.sampler.d2h_bytes, "ttft_ms": first * 1e3, "new_tokens": NEW_TOKENS}
 
+    if args.sweep:
+        print(f"decode steps (bf16, {cfg.num_hidden_layers} layers, {steps} steps each; bytes = weights + cache of the live requests; peak {peaks['hbm_gbs']:.0f} GB/s {peaks_from})")
+        print("| requests | cached tokens each | ms/step | tokens/s | GB/s | of peak |")
+        print("|---:|---:|---:|---:|---:|---:|")
+        for batch in (1, 8, 16, 32, 64):
+            for prompt_len in (128, 512, 1536):
+                if prompt_len + total_new > cfg.max_position_embeddings:
+                    continue
+                r = decode_run(batch, steps, warmup, prompt_len)
+                print(f"| {batch} | {prompt_len + warmup}-{prompt_len + total_new - 1} | {r['ms_per_step']:.3f} | {r['tokens_per_s']:.0f} | {r['gbs']:.0f} | {r['gbs'] / peaks['hbm_gbs']:.2f} |")
+        print(f"prefill of one prompt (peak {peaks['bf16_tflops']:.0f} TFLOP/s {peaks_from})")
+        print("| tokens | ms | tokens/s | TFLOP/s | of peak |")
+        print("|---:|---:|---:|---:|---:|")
+        for n_tokens in (128, 512, 1024, 2048):
+            r = prefill_run(n_tokens)
+            print(f"| {n_tokens} | {r['ms']:.3f} | {r['value']:.0f} | {r['tflops']:.0f} | {r['frac']:.2f} |")
+        return 0
     main_run = decode_run(8, steps, warmup)
     clocks = main_run["clocks"]
     rejected = [r for r in clocks["reasons"] if r != "sw_power_cap"]

@@ -623,7 +623,7 @@ def paged_attention(
         if small:
             longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
             useful = -(-longest // _SMALL_TILE_KEYS)
-            splits = max(1, min(useful, -(-_SM_COUNT // (small * num_kv_heads)), 32))  # about one CTA per SM
+            splits = max(1, min(useful, _SM_COUNT // (small * num_kv_heads), 32))  # one CTA per SM at most: all run at once
         scratch_o = scratch_ml = counters = None
         if splits > 1:
             counters = _split_counters(qkv.device, len(lens) * num_kv_heads)
