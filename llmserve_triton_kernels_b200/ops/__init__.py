@@ -592,32 +592,26 @@ def paged_attention(
     out = torch.empty((n, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     if qkv.dtype == torch.bfloat16 and head_dim in _MMA_HEAD_DIMS and not _FORCE_GENERIC_ATTENTION:
         group = num_heads // num_kv_heads
-        cu = getattr(ctx, "host_cu_tokens", None)
-        if cu is None:
-            cu = ctx.cu_tokens.tolist()
-        lens = [b - a for a, b in zip(cu, cu[1:])]
         # requests that bring at least 128 tokens: 128-token tiles of one head on tcgen05 (head size 64, pages of 8
         # to 64 keys); the others: rows of (token, group member) on mma.sync, 64 rows a tile or the split-key shape
         tc_min = 0
         if head_dim == _TC_ATTENTION_HEAD_DIM and pool.shape[3] in _TC_ATTENTION_PAGE_SIZES and _TC_ATTENTION_ENABLED:
             tc_min = _TC_ATTENTION_MIN_TOKENS
-        tc_longest = max((x for x in lens if tc_min and x >= tc_min), default=0)
+        num_requests, tc_longest, small, max_rows_large, other_rows = _attention_route(ctx, group, tc_min)
         if tc_longest:
             code = _launch(
                 "llm_attention_tcgen05", _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), pool.shape[0],
-                _ptr(page_table), page_table.shape[1], _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), len(lens), n, num_heads,
+                _ptr(page_table), page_table.shape[1], _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), num_requests, n, num_heads,
                 num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), tc_min, tc_longest, _error_flag_ptr(),
                 _stream(),
             )
             if code == 10002:  # the kernel does not take this layout: all requests go the other way
                 add_launches(-1)
-                tc_min = tc_longest = 0
+                tc_min = 0
+                num_requests, tc_longest, small, max_rows_large, other_rows = _attention_route(ctx, group, 0)
             else:
                 _check(code, "paged_attention (tcgen05)")
-        rows = [x * group for x in lens if not (tc_longest and x >= tc_min)]
-        small = sum(1 for x in rows if x <= _SMALL_ROWS)
-        max_rows_large = max((x for x in rows if x > _SMALL_ROWS), default=0)
-        if not rows:
+        if not other_rows:
             return out
         splits = 1
         if small:
@@ -626,12 +620,12 @@ def paged_attention(
             splits = max(1, min(useful, _SM_COUNT // (small * num_kv_heads), 32))  # one CTA per SM at most: all run at once
         scratch_o = scratch_ml = counters = None
         if splits > 1:
-            counters = _split_counters(qkv.device, len(lens) * num_kv_heads)
+            counters = _split_counters(qkv.device, num_requests * num_kv_heads)
             scratch_o = torch.empty((n * num_heads * splits * head_dim,), dtype=torch.float32, device=qkv.device)
             scratch_ml = torch.empty((n * num_heads * splits * 2,), dtype=torch.float32, device=qkv.device)
         code = _launch(
             "llm_attention_mma_routed", _ptr(qkv), qkv.stride(0), _ptr(out), out.stride(0), _ptr(pool), _ptr(page_table),
-            page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), len(lens), n,
+            page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), num_requests, n,
             num_heads, num_kv_heads, head_dim, pool.shape[3], int(window or 0), float(scale), max_rows_large,
             int(small > 0), splits, 1, _ptr(scratch_o), _ptr(scratch_ml), _ptr(counters), tc_min if tc_longest else 0, _stream(),
         )
@@ -645,6 +639,26 @@ def paged_attention(
     )
     _check(code, "paged_attention")
     return out
+
+
+def _attention_route(ctx, group: int, tc_min: int) -> tuple[int, int, int, int, bool]:
+    """Which kernels a step's requests go to, from how many tokens each brings: (requests, most tokens of a request
+    that the tcgen05 kernel takes (0: none), requests of the split-key shape, most rows of a request of the 64-row
+    shape (0: none), any request for the mma.sync kernels at all).  The same for every layer of a step, so it is
+    worked out once and kept on the step's context."""
+    kept = ctx.__dict__.setdefault("_attention_routes", {}) if hasattr(ctx, "__dict__") else {}
+    route = kept.get((group, tc_min))
+    if route is None:
+        cu = getattr(ctx, "host_cu_tokens", None)
+        if cu is None:
+            cu = ctx.cu_tokens.tolist()
+        lens = [b - a for a, b in zip(cu, cu[1:])]
+        tc_longest = max((x for x in lens if tc_min and x >= tc_min), default=0)
+        rows = [x * group for x in lens if not (tc_longest and x >= tc_min)]
+        small = sum(1 for x in rows if x <= _SMALL_ROWS)
+        max_rows_large = max((x for x in rows if x > _SMALL_ROWS), default=0)
+        route = kept[(group, tc_min)] = (len(lens), tc_longest, small, max_rows_large, bool(rows))
+    return route
 
 
 _counters: dict = {}
