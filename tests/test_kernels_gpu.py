@@ -109,9 +109,7 @@ def test_linear_swiglu_fused_for_few_rows(m, inter, k):
 
 
 @pytest.mark.parametrize("m,hidden,k,n_next", [(1, 2048, 5632, 2560), (8, 2048, 2048, 11264), (16, 96, 256, 40), (3, 72, 24, 172),
-                                              (128, 96, 256, 40), (300, 2048, 5632, 2560), (2048, 2048, 2048, 11264), (131, 72, 24, 172),
-                                              (17, 2048, 5632, 2560), (64, 2048, 2048, 11264), (100, 96, 256, 40), (33, 72, 24, 172),
-                                              (127, 1028, 72, 16)])
+                                              (128, 96, 256, 40), (300, 2048, 5632, 2560), (2048, 2048, 2048, 11264), (131, 72, 24, 172)])
 def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
     """A product that adds into the residual stream and hands it on in factored normalised form,
     and the next product that consumes that form: together they must equal
@@ -144,9 +142,7 @@ def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
 
 @pytest.mark.parametrize("m,H,KV,D,hidden,page_size,rotate", [(1, 32, 4, 64, 2048, 16, True), (8, 4, 2, 16, 64, 8, True),
                                                             (16, 3, 1, 32, 96, 4, True), (5, 6, 3, 128, 72, 16, False),
-                                                            (2, 5, 0, 48, 40, 1, True), (64, 32, 4, 64, 2048, 16, True),
-                                                            (17, 3, 1, 32, 96, 4, True), (127, 6, 3, 128, 72, 16, False),
-                                                            (40, 5, 0, 48, 40, 1, True)])
+                                                            (2, 5, 0, 48, 40, 1, True)])
 def test_linear_qkv_rope_fused_for_few_rows(m, H, KV, D, hidden, page_size, rotate):
     """Projection, rotation and cache write in one kernel against the three done plainly."""
     o = ops()
