@@ -1,5 +1,5 @@
 // Next-token choice on the device: argmax, and temperature sampling with optional top-k and
-// top-p, one block per row of 32-bit logits.
+// top-p, a thread-block cluster per row of 32-bit logits.
 //
 // The reference's sampler (src/llmserve/sampling/sampler.py:16-39) divides by the temperature,
 // keeps the k largest (ties kept), drops a token when the probability mass before it in
@@ -18,9 +18,9 @@ namespace cg = cooperative_groups;
 namespace {
 
 // A row is shared out over a thread-block cluster of up to eight blocks (fewer when there are many
-// rows): one block alone takes some 8 us to pull a row of 32,000 logits out of L2, and a search pass
-// is bound by the instructions one SM can issue.  Block `rank` of a cluster owns the tokens of
-// `runs_per_block` runs of 32 consecutive tokens; what the blocks have to agree on (the largest
+// rows): one block alone takes some 4 us to pull a row of 32,000 logits out of L2, and a search pass
+// is bound by the instructions one SM can issue.  Block `rank` of a cluster owns a share of the row's
+// runs of 32 consecutive tokens (`slice_of`); what the blocks have to agree on (the largest
 // logit, the weight in the bins of a search pass, their share of the probability mass) every block
 // writes into every block's shared memory and then adds up in the same order.
 constexpr int THREADS = 1024;
