@@ -17,32 +17,48 @@ from .. import ops
 from .params import SamplingParams
 
 
+class _ParameterBuffers:
+    """Where the parameters of one batch size travel: four pinned host buffers used in turn (each taken again only
+    after the kernel that fetched it last has ended) and their one place on the device."""
+
+    TURNS = 4
+
+    def __init__(self, rows: int, device: torch.device):
+        self.on_device = torch.zeros(8 * rows, dtype=torch.int32, device=device)
+        self.rows, self.pinned, self.turn = rows, [], 0
+
+    def take(self):
+        """(array to fill, the same as a pinned tensor, event to record once its fetch has been launched)."""
+        if len(self.pinned) < self.TURNS:
+            tensor = torch.zeros(8 * self.rows, dtype=torch.int32, pin_memory=True)
+            self.pinned.append((tensor.numpy(), tensor, torch.cuda.Event()))
+            return self.pinned[-1]
+        array, tensor, fetched = self.pinned[self.turn % self.TURNS]
+        self.turn += 1
+        fetched.synchronize()
+        return array, tensor, fetched
+
+
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
         self.d2h_bytes = 0
         self.h2d_bytes = 0
-        self._buffers: dict[int, list] = {}  # rows -> [next, [(array, pinned tensor, event after its last use), ...], device tensor]
+        self._buffers: dict[int, _ParameterBuffers] = {}  # by number of rows
 
     def _parameters(self, rows: int):
         """Buffers for the rows' parameters: (array to fill, the same as a pinned tensor, its place on the device,
-        event).  On a CUDA device four pinned buffers per batch size are used in turn, each taken again only after
-        the kernel that fetched it last has ended; a kernel brings the buffer to the device (no hand-over to the copy
-        engine; the sampling kernel itself does not read host memory: every small read is a trip over the bus of its
-        own, and they queue up)."""
+        event).  On a CUDA device a kernel brings the pinned buffer to the device (no hand-over to the copy engine; the
+        sampling kernel itself does not read host memory: every small read is a trip over the bus of its own, and
+        they queue up)."""
         if self.device.type != "cuda":
             packed = np.zeros(8 * rows, dtype=np.int32)
             return packed, None, torch.from_numpy(packed), None
-        ring = self._buffers.setdefault(rows, [0, [], torch.zeros(8 * rows, dtype=torch.int32, device=self.device)])
-        if len(ring[1]) < 4:
-            tensor = torch.zeros(8 * rows, dtype=torch.int32, pin_memory=True)
-            ring[1].append((tensor.numpy(), tensor, torch.cuda.Event()))
-            packed, tensor, used = ring[1][-1]
-        else:
-            packed, tensor, used = ring[1][ring[0] % 4]
-            ring[0] += 1
-            used.synchronize()
-        return packed, tensor, ring[2], used
+        buffers = self._buffers.get(rows)
+        if buffers is None:
+            buffers = self._buffers[rows] = _ParameterBuffers(rows, self.device)
+        packed, tensor, fetched = buffers.take()
+        return packed, tensor, buffers.on_device, fetched
 
     def __call__(self, logits: torch.Tensor, params: list[SamplingParams], seeds: list[int], counters: list[int]) -> list[int]:
         """``logits [rows, vocab]`` float32 on the device -> one token id per row, on the host."""
@@ -62,7 +78,7 @@ class Sampler:
             tokens = ops.argmax(logits, **extra)
         else:
             # one buffer: [temperature | top_k | top_p | - | seeds (64-bit) | counters (64-bit)]
-            packed, host, dev, used = self._parameters(rows)
+            packed, host, dev, fetched = self._parameters(rows)
             packed[0:rows] = np.asarray([p.temperature for p in params], dtype=np.float32).view(np.int32)
             packed[rows : 2 * rows] = np.asarray([p.top_k for p in params], dtype=np.int32)
             packed[2 * rows : 3 * rows] = np.asarray([p.top_p for p in params], dtype=np.float32).view(np.int32)
@@ -71,7 +87,7 @@ class Sampler:
             self.h2d_bytes = packed.nbytes
             if host is not None:
                 ops.fetch_words(host, dev)
-                used.record()
+                fetched.record()
             tokens = ops.sample(
                 logits,
                 dev[0:rows].view(torch.float32),
