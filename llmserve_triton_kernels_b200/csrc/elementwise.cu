@@ -271,7 +271,8 @@ LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int 
     const size_t total = (size_t)n * inter;
     const int threads = 256;
     const size_t want = (total / 4 + threads - 1) / threads + 1;
-    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    const size_t most = 148 * 16;  // sixteen blocks an SM of a B200; the kernel's loop strides over what is left
+    const int blocks = (int)(want < most ? want : most);
     if (dtype == LLM_F32)
         return launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total);
     if (dtype == LLM_BF16)

@@ -356,7 +356,7 @@ LLM_EXPORT int llm_gemm_tcgen05_fused(const void* x, int ldx, const void* w, voi
     if (mode != MODE_PLAIN) return LLM_ERR_BAD_ARGUMENT;
     // the tile width that wastes the fewest SM-rounds: wide tiles re-read x less often, but the last round of
     // CTAs should not be nearly empty
-    const int row_tiles = (M + BM - 1) / BM, sms = 148;
+    const int row_tiles = (M + BM - 1) / BM, sms = sm_count();
     int best = 128;
     double best_cost = 1e30;
     for (int bn : {256, 192, 160, 128}) {

@@ -76,7 +76,6 @@ _launches = 0
 _MMA_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention; others take the general kernel
 _SMALL_ROWS = 16  # requests with at most this many (token, group member) rows take the split-key shape
 _SMALL_TILE_KEYS = 128  # keys one CTA of that shape covers per tile
-_SM_COUNT = 148
 _TC_ATTENTION_ENABLED = True
 _TC_ATTENTION_HEAD_DIM = 64
 _TC_ATTENTION_PAGE_SIZES = (8, 16, 32, 64)
@@ -85,6 +84,18 @@ _TCGEN05_RESIDUAL_SINK = False  # see ResidualSink.usable
 _TCGEN05_MIN_ROWS = 128  # from this many rows a bfloat16 product runs on tcgen05 with TMA-fed tiles (own kernel)
 _DECODE_LINEAR_MAX_ROWS = 16  # up to this many rows a bfloat16 matrix product streams the weights once (own kernel)
 _FORCE_GENERIC_ATTENTION = False  # tests switch the tensor-core attention off to reach the general kernel in bfloat16
+
+
+_sm_counts: dict[int, int] = {}
+
+
+def _sm_count() -> int:
+    """SMs of the current device (asked once per device)."""
+    device = torch.cuda.current_device()
+    count = _sm_counts.get(device)
+    if count is None:
+        count = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return count
 
 
 def launch_count() -> int:
@@ -468,7 +479,7 @@ def fused_decode_plan(*, ctx, hidden, num_heads, num_kv_heads, head_dim, inter, 
     dbase = (-device_records.data_ptr()) % 64
     device_records[dbase : dbase + len(layers) * record].copy_(host[base : base + len(layers) * record])
     longest = ctx.max_context_len
-    splits = max(1, min(-(-longest // _SMALL_TILE_KEYS), _SM_COUNT // (m * num_kv_heads), 32))  # an item per CTA at most
+    splits = max(1, min(-(-longest // _SMALL_TILE_KEYS), _sm_count() // (m * num_kv_heads), 32))  # an item per CTA at most
     f32 = dict(dtype=torch.float32, device=dev)
     bf16 = dict(dtype=torch.bfloat16, device=dev)
     plan = FusedDecodePlan(
@@ -617,7 +628,7 @@ def paged_attention(
         if small:
             longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
             useful = -(-longest // _SMALL_TILE_KEYS)
-            splits = max(1, min(useful, _SM_COUNT // (small * num_kv_heads), 32))  # one CTA per SM at most: all run at once
+            splits = max(1, min(useful, _sm_count() // (small * num_kv_heads), 32))  # one CTA per SM at most: all run at once
         scratch_o = scratch_ml = counters = None
         if splits > 1:
             counters = _split_counters(qkv.device, num_requests * num_kv_heads)
