@@ -21,6 +21,7 @@ context lengths, and prefills over prompt lengths, timed the same way.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -273,6 +274,7 @@ def main() -> int:
                 tokens = ahead[1].tolist()
             ahead = (chosen, host, copied)
 
+        gc.collect()  # the prefill left garbage behind; a full collection (tens of ms) must not fall into the timed steps
         for _ in range(w):
             one_step()
         torch.cuda.synchronize()

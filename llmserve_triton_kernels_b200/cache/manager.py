@@ -62,6 +62,33 @@ class PageGroup:
         )
         self.allocator = IdAllocator(self.num_pages, "page")
         self.tables: dict[object, list[int]] = {}
+        # the same tables as int32 arrays with room to grow (released pages as 0), so that a step's table is put
+        # together from slices, not from Python lists
+        self._rows: dict[object, np.ndarray] = {}
+
+    def new_table(self, req) -> None:
+        self.tables[req] = []
+        self._rows[req] = np.zeros(16, dtype=np.int32)
+
+    def drop_table(self, req) -> list[int]:
+        del self._rows[req]
+        return self.tables.pop(req)
+
+    def append_page(self, req, page: int) -> None:
+        table = self.tables[req]
+        row = self._rows[req]
+        if len(table) == row.shape[0]:
+            row = self._rows[req] = np.concatenate((row, np.zeros_like(row)))
+        row[len(table)] = page
+        table.append(page)
+
+    def release_page(self, req, index: int) -> None:
+        self.tables[req][index] = RELEASED
+        self._rows[req][index] = 0
+
+    def row(self, req) -> np.ndarray:
+        """The request's table as int32 (released pages read 0); a view, not to be written."""
+        return self._rows[req][: len(self.tables[req])]
 
     def first_needed_page(self, length: int) -> int:
         """Logical index of the first page that a query at position ``length`` or later reads."""
@@ -167,7 +194,7 @@ class CacheManager:
         self.lengths[req] = 0
         self.slot_of[req] = slot
         for g in self.groups:
-            g.tables[req] = []
+            g.new_table(req)
         for states in self._state_entries.values():
             states[slot].zero_()
 
@@ -175,7 +202,7 @@ class CacheManager:
         if req not in self.lengths:
             raise KeyError(f"request {req!r} is not held")
         for g in self.groups:
-            g.allocator.free([p for p in g.tables.pop(req) if p != RELEASED])
+            g.allocator.free([p for p in g.drop_table(req) if p != RELEASED])
         self.slots.free([self.slot_of.pop(req)])
         del self.lengths[req]
 
@@ -202,9 +229,8 @@ class CacheManager:
                 raise OutOfPages(f"step needs {need} pages, {g.allocator.num_free} free of {g.num_pages}")
         for g in self.groups:
             for req, n in entries:
-                table = g.tables[req]
                 for _ in range(g.extra_pages(req, self.lengths[req], n)):
-                    table.append(g.allocator.allocate())
+                    g.append_page(req, g.allocator.allocate())
 
     def commit(self, entries: list[tuple[object, int]]) -> None:
         """The step ran: advance lengths and give back the pages that windows have passed."""
@@ -218,7 +244,7 @@ class CacheManager:
                 stale = [i for i in range(min(g.first_needed_page(length), len(table))) if table[i] != RELEASED]
                 g.allocator.free([table[i] for i in stale])
                 for i in stale:
-                    table[i] = RELEASED
+                    g.release_page(req, i)
 
     def reset(self) -> None:
         for req in list(self.lengths):
@@ -231,6 +257,9 @@ class CacheManager:
             held = [p for t in g.tables.values() for p in t if p != RELEASED]
             assert len(held) == len(set(held)), "a page is in two tables"
             assert set(held) == g.allocator._used, "tables and allocator disagree"
+            assert g.tables.keys() == g._rows.keys()
+            for req, t in g.tables.items():
+                assert g.row(req).tolist() == [max(p, 0) for p in t], "a table and its array disagree"
         self.slots.check()
         assert set(self.slot_of.values()) == self.slots._used
 
@@ -239,16 +268,20 @@ class CacheManager:
         """Host arrays for a reserved step: per group a page table ``[R, width]`` and the slot of
         every new token; and the state slot of every request."""
         out = []
+        starts = np.asarray([self.lengths[req] for req, _ in entries], dtype=np.int64)
+        counts = np.asarray([n for _, n in entries], dtype=np.int64)
+        # position of every new token, request by request, and the row of `table` it belongs to
+        owner = np.repeat(np.arange(len(entries)), counts)
+        first = np.cumsum(counts) - counts
+        pos = np.arange(int(counts.sum())) - np.repeat(first, counts) + np.repeat(starts, counts)
         for g in self.groups:
-            width = max(1, max(len(g.tables[req]) for req, _ in entries))
+            rows = [g.row(req) for req, _ in entries]
+            width = max(1, max(r.shape[0] for r in rows))
             table = np.zeros((len(entries), width), dtype=np.int32)
-            slots = []
-            for r, (req, n) in enumerate(entries):
-                t = np.asarray(g.tables[req], dtype=np.int32)
-                table[r, : len(t)] = np.maximum(t, 0)
-                pos = np.arange(self.lengths[req], self.lengths[req] + n)
-                slots.append(t[pos // g.page_size] * g.page_size + pos % g.page_size)
-            out.append((table, np.concatenate(slots).astype(np.int32)))
+            for r, row in enumerate(rows):
+                table[r, : row.shape[0]] = row
+            slots = table[owner, pos // g.page_size].astype(np.int64) * g.page_size + pos % g.page_size
+            out.append((table, slots.astype(np.int32)))
         state_slots = np.asarray([self.slot_of[req] for req, _ in entries], dtype=np.int32)
         return out, state_slots
 
