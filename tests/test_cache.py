@@ -176,3 +176,39 @@ def test_budget_to_pages():
     per_page = 2 * 22 * 4 * 16 * 64 * 2
     assert num_pages_for_budget(specs, 16, 2, 10 * per_page + 5) == 10  # src/llmserve/kvcache/paged.py:221-227
     assert num_pages_for_budget(specs, 16, 2, 1) == 1
+
+
+def test_a_steps_tables_and_slots_for_portions_and_single_tokens():
+    """`step_tables` for a mixed step: every request's table padded to the widest, released pages as 0, and the slot
+    of every new token, token by token."""
+    m = manager([PagedKVSpec(1, 8, 6)], page_size=4, num_pages=12)  # a window of 6 keys: early pages are given back
+    m.add_request("a")
+    m.add_request("b")
+    m.reserve([("a", 11)])
+    m.commit([("a", 11)])  # a holds positions 0..10; its first page has passed out of the window
+    assert m.groups[0].tables["a"][0] == -1
+    entries = [("a", 1), ("b", 6)]
+    m.reserve(entries)
+    (table, slots), = m.step_tables(entries)[0]
+    ta, tb = m.groups[0].tables["a"], m.groups[0].tables["b"]
+    assert table.shape == (2, 3)
+    assert table[0].tolist() == [max(p, 0) for p in ta] and table[1].tolist()[:2] == tb
+    want = [ta[11 // 4] * 4 + 11 % 4] + [tb[p // 4] * 4 + p % 4 for p in range(6)]
+    assert slots.tolist() == want
+    m.commit(entries)
+    m.check()
+
+
+def test_attention_routes_are_worked_out_once_per_step():
+    from types import SimpleNamespace
+
+    from llmserve_triton_kernels_b200 import ops
+
+    ctx = SimpleNamespace(host_cu_tokens=[0, 1, 2, 300, 303, 343])  # 1, 1, 298, 3 and 40 tokens
+    # groups of 4 heads: 1 and 3 tokens are at most 16 rows (split-key shape), 40 tokens are 160 rows, 298 go to tcgen05
+    assert ops._attention_route(ctx, 4, 128) == (5, 298, 3, 160, True)
+    assert ops._attention_route(ctx, 4, 0) == (5, 0, 3, 298 * 4, True)
+    ctx.host_cu_tokens = None  # kept on the context: not worked out again
+    assert ops._attention_route(ctx, 4, 128) == (5, 298, 3, 160, True)
+    only_long = SimpleNamespace(host_cu_tokens=[0, 200])
+    assert ops._attention_route(only_long, 8, 128) == (1, 200, 0, 0, False)
