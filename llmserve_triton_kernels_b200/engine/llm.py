@@ -68,9 +68,8 @@ class LLM:
         config.json dictionary, for random weights drawn from ``seed``.
 
         ``freeze_gc``: once the engine stands, collect garbage and move everything that is alive to the collector's
-        permanent generation (``gc.freeze()``).  A full collection otherwise walks the several hundred thousand
-        objects that the imported libraries keep, tens of milliseconds in which no step is launched: 6 % of the
-        time of a decode loop of 64 requests."""
+        permanent generation (``gc.freeze()``).  A full collection otherwise walks the some 170,000 objects that the
+        imported libraries keep, about 50 ms in which no step is launched; afterwards it walks a thousand."""
         self.device = torch.device(device)
         self.dtype = resolve_dtype(dtype)
         if self.device.type == "cuda":
