@@ -330,6 +330,48 @@ def test_paged_attention_finds_one_far_key(dtype, far_key, n):
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("H,KV,D", [(8, 4, 64), (4, 4, 32), (8, 4, 128)])
+def test_paged_attention_many_requests_each_finds_its_far_key(H, KV, D, monkeypatch):
+    """Forty decoding requests with four key/value heads: more (request, head) pairs than the GPU has SMs, which takes
+    the split-key kernel's eight-warp shape with 128-key tiles, two CTAs to an SM.  Contexts run from 1 to 2,100 keys;
+    in every request one key — the first, the last, one at a tile's or a split's edge — is made to match the query, and
+    the output must be that key's value.  The general kernel is run on the same inputs."""
+    page_size, R = 16, 40
+    g = torch.Generator().manual_seed(9)
+    ctx_lens = [1, 2, 15, 16, 17, 127, 128, 129, 255, 256, 257, 383, 384, 385, 511, 512, 513, 1023, 1024, 1025, 2047, 2048, 2100]
+    ctx_lens += torch.randint(1, 2101, (R - len(ctx_lens),), generator=g).tolist()
+    far = []
+    for i, n in enumerate(ctx_lens):
+        choices = [0, n - 1, n // 2, min(n - 1, 127), min(n - 1, 128), max(0, n - 129), max(0, n - 128)]
+        far.append(choices[i % len(choices)])
+    pool, table, keys, values = make_cache(ctx_lens, KV, D, page_size, torch.bfloat16, seed=13)
+    direction = torch.nn.functional.normalize(rnd(D, seed=6), dim=0)
+    for r in range(R):
+        keys[r][:] = keys[r] * 0.05
+        keys[r][far[r]] = direction * 24
+    filled = torch.zeros_like(pool)
+    for r, (k, v) in enumerate(zip(keys, values)):
+        j = torch.arange(k.shape[0], device=DEV)
+        page = table[r].long()[j // page_size]
+        filled[page, 0, :, j % page_size] = k.to(torch.bfloat16)
+        filled[page, 1, :, j % page_size] = v.to(torch.bfloat16)
+    q = (direction * 24).to(torch.bfloat16).repeat(R, H).contiguous()
+    ctx = step_ctx(ctx_lens, [1] * R)
+    kw = dict(num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5)
+    want = torch.stack([values[r][far[r]].to(torch.bfloat16).float().repeat_interleave(H // KV, dim=0).reshape(H * D) for r in range(R)])
+    for general in (False, True):
+        monkeypatch.setattr(ops(), "_FORCE_GENERIC_ATTENTION", general)
+        got = ops().paged_attention(q, filled, table, ctx, **kw).float()
+        bad = (got - want).abs().amax(dim=1) > 2e-2 + 2e-2 * want.abs().amax(dim=1)
+        assert not bad.any(), f"general={general}: requests {bad.nonzero().flatten().tolist()} with contexts {[ctx_lens[i] for i in bad.nonzero().flatten().tolist()]}"
+    # and with ordinary inputs against the plain statement
+    monkeypatch.setattr(ops(), "_FORCE_GENERIC_ATTENTION", False)
+    q2 = rnd(R, H * D, dtype=torch.bfloat16, seed=77)
+    pool2, table2, _, _ = _filled(ctx_lens, KV, D, page_size, seed=14)
+    torch.testing.assert_close(ops().paged_attention(q2, pool2, table2, ctx, **kw).float(),
+                               plain_ops.paged_attention(q2, pool2, table2, ctx, **kw).float(), **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 16, 17, 40])
 def test_paged_attention_window_edge(dtype, window):

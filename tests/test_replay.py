@@ -86,3 +86,39 @@ def test_replay_on_gpu(name, dtype, model_folder, tmp_path):
     assert len(got) == sum(len(v) for v in trace.rows.values())
     worst = trace_tools.compare(got, expected_logits(folder, flat), tolerance(dtype))
     print(f"worst row (fraction of tolerance, (request, position, diff)): {worst}")
+
+
+def _edges(pos: int) -> bool:
+    """Every fifth position, and the edges of pages, key tiles and query tiles."""
+    return pos % 5 == 0 or pos % 16 in (0, 15) or pos % 64 in (0, 1, 63)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("preset", ["tinyllama-1.1b", "llama2-7b", "llama3-8b"])
+def test_replay_at_real_layer_sizes(preset, dtype, model_folder, tmp_path):
+    """Two layers of the sizes of TinyLlama 1.1B, Llama-2 7B (32 key/value heads of 128, feed-forward 11008) and
+    Llama-3 8B (8 key/value heads, feed-forward 14336, vocabulary 128256) in the four ways of cutting: a request of 300
+    tokens whole (on the tensor-core prefill kernels in bfloat16), with its last 32 tokens one by one, and in portions
+    of 2 to 16 tokens; and shorter requests mixed, portions of some beside decoded tokens of others, over a pool in
+    which pages are used again.  Rows are compared at every fifth position and at the edges of pages and tiles."""
+    from llmserve_triton_kernels_b200.config.presets import PRESETS
+
+    cfg = {**PRESETS[preset], "num_hidden_layers": 2, "max_position_embeddings": 512}
+    folder = model_folder(cfg, 0, torch.bfloat16)
+    long, short_a, short_b = tiny_configs.seeded_tokens(cfg["vocab_size"], [300, 97, 70], 77)
+    late = lambda n: (lambda pos: _edges(pos) or pos >= n - 34)  # noqa: E731
+    trace = trace_tools.Trace()
+    flat = {}
+    for tag, make in (("w", trace_tools.whole), ("d", trace_tools.decode_tail), ("p", trace_tools.portions)):
+        trace.extend(make(f"{tag}.long", long, keep=late(len(long))))
+        flat[f"{tag}.long"] = long
+    trace.extend(trace_tools.whole("w.a", short_a, keep=late(len(short_a))))
+    flat["w.a"] = short_a
+    both = {"m.a": short_a, "m.b": short_b, "m.a'": short_a, "m.b'": short_b, "m.a''": short_a}
+    trace.extend(trace_tools.mixed(both, {k: len(v) - 34 for k, v in both.items()}, chunk=16, live=4, keep=_edges))
+    flat.update(both)
+    got = trace_tools.run_trace(folder, dtype, trace, tmp_path)
+    assert len(got) == sum(len(v) for v in trace.rows.values())
+    worst = trace_tools.compare(got, expected_logits(folder, flat), tolerance(dtype))
+    print(f"worst row (fraction of tolerance, (request, position, diff)): {worst}")

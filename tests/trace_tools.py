@@ -23,7 +23,10 @@ def round_up(n: int, m: int) -> int:
 class Trace:
     """Steps of a trace plus, for every wanted row, which (request, position) it is."""
 
-    def __init__(self):
+    def __init__(self, keep=None):
+        """``keep``: of the places that "all" names, only those whose absolute position it accepts are wanted (large
+        vocabularies: a row of logits is half a megabyte)."""
+        self.keep = keep
         self.steps: list[dict] = []
         self.rows: dict[int, list[tuple[str, int]]] = {}
         self._fed: dict[str, int] = {}
@@ -35,13 +38,13 @@ class Trace:
         step = len(self.steps)
         rec_entries, rows = [], []
         for req, tokens, want in entries:
+            start = self._fed.get(req, 0)
             if want == "all":
-                want = list(range(len(tokens)))
+                want = [i for i in range(len(tokens)) if self.keep is None or self.keep(start + i)]
             elif want == "last":
                 want = [len(tokens) - 1]
             elif want == "none":
                 want = []
-            start = self._fed.get(req, 0)
             rec_entries.append({"id": req, "tokens": list(tokens), "want": list(want)})
             rows += [(req, start + w) for w in want]
             self._fed[req] = start + len(tokens)
@@ -64,15 +67,15 @@ class Trace:
         self.peak_tokens = max(self.peak_tokens, other.peak_tokens)
 
 
-def whole(name: str, tokens: list[int]) -> Trace:
-    t = Trace()
+def whole(name: str, tokens: list[int], keep=None) -> Trace:
+    t = Trace(keep)
     t.add_step([(name, tokens, "all")], end=[name])
     return t
 
 
-def decode_tail(name: str, tokens: list[int], tail: int = 32) -> Trace:
+def decode_tail(name: str, tokens: list[int], tail: int = 32, keep=None) -> Trace:
     """Most of it in one step, the last ``tail`` tokens one by one."""
-    t = Trace()
+    t = Trace(keep)
     head = max(1, len(tokens) - tail)
     t.add_step([(name, tokens[:head], "all")])
     for i in range(head, len(tokens)):
@@ -82,9 +85,9 @@ def decode_tail(name: str, tokens: list[int], tail: int = 32) -> Trace:
     return t
 
 
-def portions(name: str, tokens: list[int], sizes=(7, 2, 16, 3, 5, 2, 1, 9)) -> Trace:
+def portions(name: str, tokens: list[int], sizes=(7, 2, 16, 3, 5, 2, 1, 9), keep=None) -> Trace:
     """Portions of changing size, down to two tokens (and one)."""
-    t = Trace()
+    t = Trace(keep)
     i, k = 0, 0
     while i < len(tokens):
         n = min(sizes[k % len(sizes)], len(tokens) - i)
@@ -94,11 +97,11 @@ def portions(name: str, tokens: list[int], sizes=(7, 2, 16, 3, 5, 2, 1, 9)) -> T
     return t
 
 
-def mixed(requests: dict[str, list[int]], prefill: dict[str, int], chunk: int = 16, live: int = 4, stagger: int = 2) -> Trace:
+def mixed(requests: dict[str, list[int]], prefill: dict[str, int], chunk: int = 16, live: int = 4, stagger: int = 2, keep=None) -> Trace:
     """Up to ``live`` requests at a time: each is first fed ``prefill[name]`` tokens in portions
     of at most ``chunk`` and then its remaining tokens one by one, beside the others; a request
     starts ``stagger`` steps after the one before it, or when a place becomes free."""
-    t = Trace()
+    t = Trace(keep)
     waiting = list(requests)
     active: dict[str, int] = {}
     steps_since_start = stagger
