@@ -66,6 +66,11 @@ class LlamaConfig:
             )
         if self.head_dim % 2:
             raise ConfigError(f"head_dim {self.head_dim} must be even for rotary positions")
+        if self.head_dim > 256:
+            raise ConfigError(
+                f"hidden_size {self.hidden_size} / num_attention_heads {self.num_attention_heads} gives head_dim "
+                f"{self.head_dim}; the attention kernels take head sizes up to 256"
+            )
         if not self.rms_norm_eps > 0 or not self.rope_theta > 0:
             raise ConfigError("rms_norm_eps and rope_theta must be positive")
 

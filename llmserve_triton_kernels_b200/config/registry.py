@@ -19,13 +19,16 @@ class Architecture:
     name: str
     config_class: Any  # has from_dict(dict) and to_dict()
     plan: Callable[[Any], Any]  # config -> ModelPlan
+    model_class: Any = None  # a subclass of models.model.Model (None: Model itself)
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, config_class, plan) -> Architecture:
-    arch = Architecture(name, config_class, plan)
+def register_architecture(name: str, config_class, plan, model_class=None) -> Architecture:
+    """``model_class``: a subclass of ``Model`` for an architecture that prepares its embeddings or treats its
+    logits in a way of its own (``Model.embed_tokens``, ``Model.project_logits``); most need none."""
+    arch = Architecture(name, config_class, plan, model_class)
     _ARCHITECTURES[name] = arch
     return arch
 

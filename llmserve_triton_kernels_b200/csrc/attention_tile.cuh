@@ -1,6 +1,6 @@
 // The tensor-core attention over the paged cache as a device function: one CTA of 4 warps computes
-// one (request, key/value head, row tile, split of the keys).  Shared by the attention kernel
-// (attention_mma.cu) and the kernel that runs a whole decode step (decode_fused.cu).
+// one (request, key/value head, row tile, split of the keys).  Used by the attention kernels of
+// attention_mma.cu.
 #pragma once
 
 #include "common.cuh"

@@ -1,5 +1,5 @@
 // Row-wise kernels: token embedding, RMS norm fused with the residual sum, rotary encoding fused
-// with the write of keys and values into their pages, and the gated activation.
+// with the write of keys and values into their pages, the gated activation, and a projection's bias.
 //
 // All of them are bound by memory traffic; each row is read once and written once.  Statistics,
 // angles and the residual sum are 32-bit whatever the element type.
@@ -278,6 +278,38 @@ LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int 
     if (dtype == LLM_BF16)
         return launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up,
                           (__nv_bfloat16*)out, inter, total);
+    return LLM_ERR_BAD_ARGUMENT;
+}
+
+// ---------------------------------------------------------------------------------------------
+// bias of a projection: x[t, j] += bias[j], summed in 32-bit and rounded once.  The products of layers
+// without a bias never come here; a layer with one runs its product, then this.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, int ld, const T* __restrict__ bias, int cols, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t t = i / cols;
+        const int j = (int)(i - t * cols);
+        T* p = x + t * ld + j;
+        *p = from_float<T>(to_float(*p) + to_float(bias[j]));
+    }
+}
+
+LLM_EXPORT int llm_add_bias(void* x, int dtype, int rows, int cols, int ld, const void* bias, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (ld < cols) return LLM_ERR_BAD_ARGUMENT;
+    const size_t total = (size_t)rows * cols;
+    const int threads = 256;
+    const size_t want = (total + threads - 1) / threads, most = 148 * 16;
+    const int blocks = (int)(want < most ? want : most);
+    if (dtype == LLM_F32)
+        return launch_pdl(add_bias_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)x, ld, (const float*)bias, cols, total);
+    if (dtype == LLM_BF16)
+        return launch_pdl(add_bias_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)x, ld,
+                          (const __nv_bfloat16*)bias, cols, total);
     return LLM_ERR_BAD_ARGUMENT;
 }
 

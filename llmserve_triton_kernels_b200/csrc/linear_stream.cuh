@@ -1,5 +1,5 @@
-// The weight-streaming matrix product for few rows as device functions, shared by the kernel that runs
-// one product (linear_decode.cu) and the kernel that runs a whole decode step (decode_fused.cu).
+// The weight-streaming matrix product for few rows as device functions, used by the kernels of
+// linear_decode.cu.
 //
 // A CTA of 8 warps; each warp streams tiles of 16 output features of its own through a private ring
 // of TMA boxes (16 rows x 128 k, completion counted by the warp's own mbarriers).  The caller owns

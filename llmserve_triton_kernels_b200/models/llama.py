@@ -57,6 +57,9 @@ def llama_plan(cfg: LlamaConfig) -> ModelPlan:
         schedule=tuple(LayerRun(i) for i in range(cfg.num_hidden_layers)),
         final_norm=PartSpec("rms_norm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, "model.norm."),
         head=None if cfg.tie_word_embeddings else "lm_head.weight",
+        # a tied checkpoint may still store the output matrix; the reference overrides it with the token table
+        # (src/llmserve/weights.py:49-52)
+        ignored=("lm_head.weight",) if cfg.tie_word_embeddings else (),
     )
 
 

@@ -27,7 +27,7 @@ def resolve_dtype(dtype) -> torch.dtype:
 def load_model(model_dir: str | Path, dtype="bfloat16", device="cuda:0"):
     """``(model, configuration)`` of the folder; the model class follows config.json's ``architectures``."""
     arch, config = read_config(model_dir)
-    model = Model(arch.plan(config), resolve_dtype(dtype), device)
+    model = (arch.model_class or Model)(arch.plan(config), resolve_dtype(dtype), device)
     tensors = read_safetensors(model_dir)
     check_tensors(tensors, model.tensor_specs(), model.ignored_tensor_names(), where=str(model_dir))
     model.bind(tensors)
@@ -37,6 +37,6 @@ def load_model(model_dir: str | Path, dtype="bfloat16", device="cuda:0"):
 def random_model(config, seed: int, dtype="bfloat16", device="cuda:0", std: float = 0.02, storage=torch.bfloat16):
     """The model that :func:`write_random_model` would write and :func:`load_model` read back, without the disk."""
     arch = get_architecture(config.architecture)
-    model = Model(arch.plan(config), resolve_dtype(dtype), device)
+    model = (arch.model_class or Model)(arch.plan(config), resolve_dtype(dtype), device)
     model.bind(random_tensors(model.tensor_specs(), seed, std, storage))
     return model

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..parts.base import Block, PagedKVSpec, StateSpec, TensorSpec, build_part
+from ..parts.base import Block, PagedKVSpec, StateSpec, TensorSpec, build_part, part_factory
 from .plan import ModelPlan
 
 
@@ -24,18 +24,20 @@ class Model:
         self.device = torch.device(device)
         self.blocks: list[Block] = []
         self._named_parts: list[tuple[str, object]] = []  # (prefix, part) of every tensor-owning part
-        for spec in plan.layers:
+        for i, spec in enumerate(plan.layers):
+            factory = part_factory("block", spec.block.kind)
+            roles = getattr(factory, "roles", None)
+            if not roles:
+                raise ValueError(f"block kind {spec.block.kind!r} declares no roles (Block.roles: role -> part category)")
+            if set(roles) != set(spec.parts):
+                raise ValueError(
+                    f"layer {i}: block kind {spec.block.kind!r} is built from {sorted(roles)}, the plan gives {sorted(spec.parts)}"
+                )
             parts = {}
-            for role, category in (
-                ("mixer_norm", "norm"),
-                ("mixer", "mixer"),
-                ("ff_norm", "norm"),
-                ("feed_forward", "feed_forward"),
-            ):
-                part_spec = getattr(spec, role)
-                parts[role] = build_part(category, part_spec)
-                self._named_parts.append((part_spec.prefix, parts[role]))
-            block = build_part("block", type(spec.block)(spec.block.kind, {**spec.block.params, **parts}, spec.block.prefix))
+            for role, category in roles.items():
+                parts[role] = build_part(category, spec.parts[role])
+                self._named_parts.append((spec.parts[role].prefix, parts[role]))
+            block = build_part("block", spec.block, **parts)
             self._named_parts.append((spec.block.prefix, block))
             self.blocks.append(block)
         self.final_norm = build_part("norm", plan.final_norm)
@@ -59,8 +61,8 @@ class Model:
         return specs
 
     def ignored_tensor_names(self) -> set[str]:
-        """Names a checkpoint may carry that the model does not read (a copy of a tied output matrix)."""
-        return {"lm_head.weight"} if self.plan.head is None else set()
+        """Names a checkpoint may carry that the model does not read; the plan lists them."""
+        return set(self.plan.ignored)
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         plan = self.plan
@@ -77,7 +79,7 @@ class Model:
             order = []
             for run in self.plan.schedule:
                 block = self.blocks[run.layer]
-                for part in (getattr(block, "mixer", None), getattr(block, "feed_forward", None)):
+                for part in block.owned_parts():
                     order += list(getattr(part, "streamed_weights", lambda: [])())
             ops.set_weight_order(order + [self.head])
 
@@ -104,64 +106,38 @@ class Model:
             getattr(b, "graph_safe", False) for b in self.blocks
         ) and getattr(self.final_norm, "graph_safe", False)
 
-    def _fused_decode(self, ctx, caches):
-        """A captured decode step of few tokens through the one-kernel path, when every layer of the
-        order is of the kind that kernel runs and all agree in their sizes; else None."""
-        plan = getattr(ctx, "_fused_plan", None)
-        if plan is None:
-            plan = self._make_fused_plan(ctx, caches) or False
-            ctx._fused_plan = plan
-        return ops.fused_decode_run(plan) if plan else None
-
-    def _make_fused_plan(self, ctx, caches):
-        order = self.plan.schedule
-        if any(run.cache_of is not None for run in order) or getattr(self.final_norm, "fused_params", None) is None:
-            return None
-        specs = []
-        for i, run in enumerate(order):
-            spec = getattr(self.blocks[run.layer], "fused_decode_spec", lambda c: None)(caches[i])
-            if spec is None:
-                return None
-            specs.append(spec)
-        first = specs[0]
-        if any(s["dims"] != first["dims"] or s["rotary_table"] is not first["rotary_table"] or s["page_size"] != first["page_size"] for s in specs):
-            return None
-        layers = []
-        for i, s in enumerate(specs):
-            nxt = specs[i + 1]["mixer_norm"] if i + 1 < len(specs) else self.final_norm.fused_params()
-            layers.append({**s, "next_norm": nxt})
-        hidden, heads, kv_heads, head_dim, inter = first["dims"]
-        return ops.fused_decode_plan(
-            ctx=ctx, hidden=hidden, num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, inter=inter,
-            vocab=self.plan.vocab_size, page_size=first["page_size"], embedding=self.embedding, first_norm=first["mixer_norm"],
-            rotary_table=first["rotary_table"], layers=layers, head=self.head,
-        )
-
     # ------------------------------------------------------------------ caches
     def cache_specs(self) -> list[PagedKVSpec | StateSpec | None]:
         """For each entry of the order: what its mixer keeps, or None if it keeps nothing of its
         own (no cache, or it reads an earlier entry's)."""
         out = []
         for run in self.plan.schedule:
-            out.append(None if run.cache_of is not None else self.blocks[run.layer].mixer.cache_spec())
+            out.append(None if run.cache_of is not None else self.blocks[run.layer].cache_spec())
         return out
 
     # ------------------------------------------------------------------ step
     def forward(self, ctx, caches) -> torch.Tensor:
         """Run the tokens of ``ctx`` through every entry of the order; ``caches[i]`` is the view
         of entry i's cache.  Returns 32-bit logits ``[len(ctx.logit_rows), vocab]``."""
-        if getattr(ctx, "static_decode", False) and self.dtype == torch.bfloat16:
-            logits = self._fused_decode(ctx, caches)
-            if logits is not None:
-                return logits
-        resid = ops.embed(ctx.token_ids, self.embedding)
+        resid = self.embed_tokens(ctx)
         pending = None
         order = self.plan.schedule
         for i, run in enumerate(order):
             # the norm that meets the stream next, so that a block's last product may prepare for it
-            next_norm = self.blocks[order[i + 1].layer].mixer_norm if i + 1 < len(order) else None
+            next_norm = self.blocks[order[i + 1].layer].first_norm() if i + 1 < len(order) else None
             pending = self.blocks[run.layer].forward(resid, pending, ctx, caches[i], next_norm=next_norm)
         if ctx.num_logits == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
         x = self.final_norm.add_forward(resid, pending, rows=ctx.logit_rows)
+        return self.project_logits(x)
+
+    def embed_tokens(self, ctx) -> torch.Tensor:
+        """The residual stream that the first layer meets: the tokens' rows of the table, in 32-bit ``[N, hidden]``.
+        An architecture that scales or otherwise prepares its embeddings overrides this in a subclass that it names
+        when it registers (``register_architecture(..., model_class=...)``)."""
+        return ops.embed(ctx.token_ids, self.embedding)
+
+    def project_logits(self, x) -> torch.Tensor:
+        """32-bit logits ``[rows, vocab]`` of the normalised rows ``x`` (a tensor, or the factored form that the
+        last block handed on).  The place for an architecture's cap or scale of its logits, in a subclass."""
         return ops.linear(x, self.head, out_dtype=torch.float32)

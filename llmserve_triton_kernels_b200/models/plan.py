@@ -3,19 +3,46 @@
 from __future__ import annotations
 
 from dataclasses import dataclass
+from types import MappingProxyType
+from typing import Mapping
 
 from ..parts.base import PartSpec
 
 
-@dataclass(frozen=True)
 class LayerSpec:
-    """One layer's parts.  ``block`` arranges the other four around the residual stream."""
+    """One layer: the kind of block that arranges it, and the parts that block asks for, by role.
 
-    block: PartSpec
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ff_norm: PartSpec
-    feed_forward: PartSpec
+    Which roles there are is the block kind's business (``Block.roles``: role -> part category): the pre-norm block
+    has ``mixer_norm, mixer, ff_norm, feed_forward``; a block with norms after its parts as well, or with one norm and
+    two parallel parts, names other roles and is built from the same ``LayerSpec(block, role=spec, ...)``."""
+
+    __slots__ = ("block", "parts")
+
+    def __init__(self, block: PartSpec, parts: Mapping[str, PartSpec] | None = None, **roles: PartSpec):
+        object.__setattr__(self, "block", block)
+        object.__setattr__(self, "parts", MappingProxyType({**(parts or {}), **roles}))
+
+    def __setattr__(self, name, value):
+        raise AttributeError("a LayerSpec is not changed after it is made")
+
+    def __getattr__(self, role: str) -> PartSpec:  # spec.mixer, spec.ff_norm, ...
+        try:
+            return self.parts[role]
+        except KeyError:
+            raise AttributeError(role) from None
+
+    def replace(self, block: PartSpec | None = None, **roles: PartSpec) -> "LayerSpec":
+        """A copy with another block or other parts in the named roles."""
+        return LayerSpec(block or self.block, {**self.parts, **roles})
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, LayerSpec) and self.block == other.block and dict(self.parts) == dict(other.parts)
+
+    def __hash__(self) -> int:
+        return hash((self.block.kind, tuple(self.parts)))
+
+    def __repr__(self) -> str:
+        return f"LayerSpec({self.block!r}, {dict(self.parts)!r})"
 
 
 @dataclass(frozen=True)
@@ -41,6 +68,7 @@ class ModelPlan:
     schedule: tuple[LayerRun, ...]
     final_norm: PartSpec
     head: str | None  # tensor name of the output matrix [vocab, hidden]; None: the token table
+    ignored: tuple[str, ...] = ()  # names a checkpoint may carry that the model does not read (e.g. a copy of a tied head)
 
     def __post_init__(self) -> None:
         for i, run in enumerate(self.schedule):

@@ -25,13 +25,11 @@ _SIGNATURES = {
     "llm_rmsnorm": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
     "llm_rope_kv_write": [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "llm_add_bias": [_vp, _i, _i, _i, _i, _vp, _vp],
     "llm_fetch_words": [_vp, _vp, _vp, _i, _i, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_ulonglong, _vp],
     "llm_linear_decode_qkv": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
-    "llm_fused_layer_fill": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _f, _vp, _vp, _i, _vp, _i, _f],
-    "llm_decode_fused": [_i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _f, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                         _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_gemm_tcgen05": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_tcgen05_fused": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_gemm_tcgen05_parts": [_i],
@@ -65,7 +63,6 @@ def library():
                 fn = getattr(lib, name)
                 fn.argtypes = args
                 fn.restype = ctypes.c_int
-            lib.llm_fused_layer_bytes.restype = ctypes.c_int
             lib.llm_error_string.argtypes = [ctypes.c_int]
             lib.llm_error_string.restype = ctypes.c_char_p
             _lib = lib
@@ -431,90 +428,6 @@ def linear_qkv_rope(
     return q
 
 
-# The whole decode step in one cooperative kernel (csrc/decode_fused.cu).  Correct and tested, but measured slower
-# than the step kernel by kernel with programmatic dependent launch (1.50 ms against 1.22 ms per step of 8 requests
-# on a 1.1B model): each of its 111 phases pays a grid barrier and a chain of dependent trips to L2.  Off by default.
-_FUSED_DECODE_ENABLED = False
-_FUSED_DECODE_MAX_TOKENS = 8
-_FUSED_DECODE_HEAD_DIMS = (64, 128)
-
-
-class FusedDecodePlan:
-    """Everything the one-kernel decode step needs, made once per captured decode shape: the
-    layers' records (tensor maps of the four matrices, norm weights, cache plane, page table and
-    slot map of the step's static buffers) on the device, and the scratch tensors."""
-
-    def __init__(self, **kw):
-        self.__dict__.update(kw)
-
-
-def fused_decode_plan(*, ctx, hidden, num_heads, num_kv_heads, head_dim, inter, vocab, page_size, embedding, first_norm,
-                      rotary_table, layers: list[dict], head) -> "FusedDecodePlan | None":
-    """A plan for :func:`fused_decode_run`, or None when the kernel does not take these sizes.
-    ``layers``: per layer ``w_in, w_out, w_gate_up, w_down`` (bfloat16), ``ff_norm`` and
-    ``next_norm`` as ``(weight, eps)``, ``pool``, ``page_table``, ``slot_map``, ``window``, ``scale``."""
-    m = ctx.num_tokens
-    if not _FUSED_DECODE_ENABLED:
-        return None
-    if m > _FUSED_DECODE_MAX_TOKENS or head_dim not in _FUSED_DECODE_HEAD_DIMS or embedding.dtype != torch.bfloat16:
-        return None
-    if hidden % 8 or inter % 8 or num_heads % num_kv_heads or num_heads // num_kv_heads > 16:
-        return None
-    lib = library()
-    dev = embedding.device
-    record = lib.llm_fused_layer_bytes()
-    host = torch.zeros(len(layers) * record + 64, dtype=torch.uint8).pin_memory()
-    base = (-host.data_ptr()) % 64
-    for i, L in enumerate(layers):
-        pt = L["page_table"]
-        code = lib.llm_fused_layer_fill(
-            host.data_ptr() + base + i * record, _ptr(L["w_in"]), _ptr(L["w_out"]), _ptr(L["w_gate_up"]), _ptr(L["w_down"]),
-            hidden, num_heads, num_kv_heads, head_dim, inter, _ptr(L["ff_norm"][0]), float(L["ff_norm"][1]),
-            _ptr(L["next_norm"][0]), float(L["next_norm"][1]), _ptr(L["pool"]), _ptr(pt), pt.shape[1], _ptr(L["slot_map"]),
-            int(L["window"] or 0), float(L["scale"]),
-        )
-        if code != 0:
-            return None
-    device_records = torch.empty(len(layers) * record + 64, dtype=torch.uint8, device=dev)
-    dbase = (-device_records.data_ptr()) % 64
-    device_records[dbase : dbase + len(layers) * record].copy_(host[base : base + len(layers) * record])
-    longest = ctx.max_context_len
-    splits = max(1, min(-(-longest // _SMALL_TILE_KEYS), _sm_count() // (m * num_kv_heads), 32))  # an item per CTA at most
-    f32 = dict(dtype=torch.float32, device=dev)
-    bf16 = dict(dtype=torch.bfloat16, device=dev)
-    plan = FusedDecodePlan(
-        ctx=ctx, m=m, hidden=hidden, H=num_heads, KV=num_kv_heads, D=head_dim, inter=inter, vocab=vocab, page_size=page_size,
-        n_layers=len(layers), embedding=embedding, first_norm=first_norm, rotary_table=rotary_table, head=head,
-        records=device_records, records_ptr=device_records.data_ptr() + dbase, keep=layers, splits=splits,
-        resid=torch.empty((m, hidden), **f32), xw=torch.empty((m, hidden), **bf16),
-        ss=torch.empty((-(-hidden // 16), m), **f32), q=torch.empty((m, num_heads * head_dim), **bf16),
-        attn=torch.empty((m, num_heads * head_dim), **bf16), act=torch.empty((m, inter), **bf16),
-        part_o=torch.empty((m * num_heads * splits * head_dim,), **f32), part_ml=torch.empty((m * num_heads * splits * 2,), **f32),
-        counters=torch.zeros((m * num_kv_heads,), dtype=torch.int32, device=dev),
-        barrier=torch.zeros((1,), dtype=torch.int32, device=dev), logits=torch.empty((m, vocab), **f32),
-    )
-    torch.cuda.synchronize(dev)  # the records are on the device before the pinned buffer goes away
-    return plan
-
-
-def fused_decode_run(plan: "FusedDecodePlan") -> torch.Tensor | None:
-    """One decode step in one kernel; returns the plan's logits tensor ``[tokens, vocab]``
-    (overwritten by the next run), or None if the kernel refused."""
-    p, ctx = plan, plan.ctx
-    code = _launch(
-        "llm_decode_fused", p.m, p.hidden, p.H, p.KV, p.D, p.inter, p.vocab, p.page_size, p.n_layers, _ptr(ctx.token_ids),
-        _ptr(p.embedding), _ptr(p.first_norm[0]), float(p.first_norm[1]), _ptr(ctx.positions), _ptr(p.rotary_table),
-        p.rotary_table.shape[0], _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), _ptr(p.resid), _ptr(p.xw), _ptr(p.ss), _ptr(p.q),
-        _ptr(p.attn), _ptr(p.act), p.splits, _ptr(p.part_o), _ptr(p.part_ml), _ptr(p.counters), p.records_ptr, _ptr(p.head),
-        _ptr(p.logits), _ptr(p.barrier), _error_flag_ptr(), _stream(),
-    )
-    if code == 10002:
-        add_launches(-1)
-        return None
-    _check(code, "fused decode step")
-    return p.logits
-
-
 def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
     """``silu(x @ gate^T) * (x @ up^T)`` for ``w_gate_up = [gate rows | up rows]``: one kernel for
     few bfloat16 rows, else a product followed by the activation kernel."""
@@ -598,7 +511,7 @@ def paged_attention(
     _need(qkv.stride(1) == 1 and qkv.shape[1] >= num_heads * head_dim, "qkv rows must start with the query heads")
     _need(pool.dtype == qkv.dtype and pool.is_contiguous() and pool.dim() == 5, "the pool plane must be contiguous and of the query type")
     _need(tuple(pool.shape[1:3]) == (2, num_kv_heads) and pool.shape[4] == head_dim, "the pool plane does not match the heads")
-    _need(head_dim % 16 == 0 and head_dim <= 256, f"head_dim {head_dim} is not supported (multiples of 16 up to 256)")
+    _need(1 <= head_dim <= 256, f"head_dim {head_dim} is not supported (up to 256)")
     _i32(page_table, "page_table")
     out = torch.empty((n, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     if qkv.dtype == torch.bfloat16 and head_dim in _MMA_HEAD_DIMS and not _FORCE_GENERIC_ATTENTION:
@@ -692,6 +605,15 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
     _check(_launch("llm_swiglu", _ptr(gate_up), _ptr(out), _code(gate_up.dtype), n, inter, _stream()), "swiglu")
     return out
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``x [N, C] += bias [C]`` in place (summed in 32-bit, rounded once); returns ``x``."""
+    _need(x.dim() == 2 and x.stride(1) == 1 and bias.dim() == 1 and bias.numel() == x.shape[1] and bias.is_contiguous(),
+          "add_bias: x [N, C] with unit inner stride and bias [C]")
+    _need(bias.dtype == x.dtype, f"add_bias: the bias is {bias.dtype}, the rows are {x.dtype}")
+    _check(_launch("llm_add_bias", _ptr(x), _code(x.dtype), x.shape[0], x.shape[1], x.stride(0), _ptr(bias), _stream()), "add_bias")
+    return x
 
 
 def fetch_words(host: torch.Tensor, dev: torch.Tensor, head: torch.Tensor | None = None) -> None:

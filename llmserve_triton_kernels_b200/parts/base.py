@@ -14,7 +14,8 @@ Interfaces (what a new part must provide):
 * ``Mixer``: ``cache_spec()`` saying what it keeps per request (pages of keys and values, a
   slot of fixed-size state, or nothing) and ``forward(x, ctx, cache) -> delta``;
 * ``FeedForward``: ``forward(x, ctx) -> delta``;
-* ``Block``: ``forward(resid, pending, ctx, cache) -> pending`` arranging the four.
+* ``Block``: ``roles`` (which parts it is built from) and ``forward(resid, pending, ctx, cache) -> pending``
+  arranging them.
 
 The reference hard-wires these choices into classes that read one config object
 (src/llmserve/model/llama.py:57-135); here they are parameters.
@@ -100,6 +101,10 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     category = "position"
+    # How a tabulated rotation pairs the lanes of a head, for mixers whose kernels can apply it while they store keys
+    # and values: "half" = lanes (j, j + head_dim/2) over the whole head, with ``rotary_table [positions, head_dim]`` =
+    # cos | sin halves.  None (or a layout a mixer does not know): the mixer calls ``apply``.
+    rotary_layout: str | None = None
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
         """Encode absolute ``positions [N]`` into ``q [N, H, D]`` and ``k [N, KV, D]`` in place."""
@@ -127,9 +132,27 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """The arrangement of norms, mixer and feed-forward around the residual stream."""
+    """The arrangement of norms, mixer and feed-forward around the residual stream.
+
+    ``roles`` names the parts a block kind is built from and the category of each, in the order of its
+    constructor's arguments: the model builds one part per role from the layer's ``LayerSpec`` and hands them over by
+    these names.  A block kind with more norms, or with parts side by side, declares other roles."""
 
     category = "block"
+    roles: dict[str, str] = {}
+
+    def owned_parts(self) -> list[Part]:
+        """The parts of this block, in the order of ``roles``."""
+        return [getattr(self, role) for role in self.roles]
+
+    def first_norm(self):
+        """The norm that the residual stream meets first in this block (None: it meets none first), so that the
+        block in front may fold it into its last product."""
+        return getattr(self, "mixer_norm", None)
+
+    def cache_spec(self):
+        """What this block keeps per request: its mixer's ``cache_spec()``."""
+        return self.mixer.cache_spec()
 
     def forward(self, resid: torch.Tensor, pending, ctx, cache, next_norm=None):
         """``resid [N, hidden]`` is the 32-bit residual stream, updated in place; ``pending`` a
@@ -161,8 +184,12 @@ def register_part(category: str, kind: str, factory: Callable[..., Part] | None 
     return _add(factory) if factory is not None else _add
 
 
-def build_part(category: str, spec: PartSpec) -> Part:
+def part_factory(category: str, kind: str) -> Callable[..., Part]:
     kinds = _REGISTRY[category]
-    if spec.kind not in kinds:
-        raise KeyError(f"no {category} of kind {spec.kind!r} is registered; known: {sorted(kinds)}")
-    return kinds[spec.kind](**spec.params)
+    if kind not in kinds:
+        raise KeyError(f"no {category} of kind {kind!r} is registered; known: {sorted(kinds)}")
+    return kinds[kind]
+
+
+def build_part(category: str, spec: PartSpec, **more) -> Part:
+    return part_factory(category, spec.kind)(**spec.params, **more)

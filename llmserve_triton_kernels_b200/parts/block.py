@@ -15,6 +15,8 @@ from .base import Block, FeedForward, Mixer, Norm, register_part
 
 
 class PreNormBlock(Block):
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "ff_norm": "norm", "feed_forward": "feed_forward"}
+
     def __init__(self, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm, feed_forward: FeedForward):
         self.mixer_norm = mixer_norm
         self.mixer = mixer
@@ -32,28 +34,6 @@ class PreNormBlock(Block):
         x = self._normed(self.ff_norm, resid, pending, self.feed_forward)
         sink = self._sink(self.feed_forward, next_norm, resid, ctx)
         return self.feed_forward.forward(x, ctx, sink=sink) if sink else self.feed_forward.forward(x, ctx)
-
-    def fused_decode_spec(self, cache):
-        """What the one-kernel decode step needs of this layer, if the layer is of the kind that kernel runs
-        (RMS norms, rotary paged attention with keys and values of its own, gated feed-forward); else None."""
-        from ..cache.manager import PagedKVView
-        from .attention import PagedAttention
-        from .feed_forward import GatedMLP
-
-        a, f = self.mixer, self.feed_forward
-        if not (isinstance(a, PagedAttention) and isinstance(f, GatedMLP) and isinstance(cache, PagedKVView)):
-            return None
-        if not a.own_kv or getattr(a.position, "rotary_table", None) is None:
-            return None
-        if getattr(self.mixer_norm, "fused_params", None) is None or getattr(self.ff_norm, "fused_params", None) is None:
-            return None
-        return {
-            "mixer_norm": self.mixer_norm.fused_params(), "ff_norm": self.ff_norm.fused_params(),
-            "w_in": a.w_in, "w_out": a.w_out, "w_gate_up": f.w_gate_up, "w_down": f.w_down,
-            "pool": cache.pool, "page_table": cache.page_table, "slot_map": cache.slot_map, "window": a.window,
-            "scale": a.scale, "rotary_table": a.position.rotary_table, "page_size": cache.page_size,
-            "dims": (a.hidden_size, a.num_heads, a.num_kv_heads, a.head_dim, f.intermediate_size),
-        }
 
     @staticmethod
     def _normed(norm, resid, pending, consumer):

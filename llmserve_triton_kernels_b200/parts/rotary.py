@@ -20,6 +20,7 @@ _TABLES: dict = {}
 
 class RotaryEmbedding(PositionEncoding):
     graph_safe = True
+    rotary_layout = "half"  # lanes j and j + head_dim/2 form a pair, over the whole head
 
     def __init__(self, head_dim: int, theta: float, max_positions: int):
         if head_dim % 2:

@@ -54,7 +54,7 @@ def write_random_model(
     from ..models.model import Model
 
     arch = get_architecture(config.architecture)
-    model = Model(arch.plan(config), torch.float32, "cpu")
+    model = (arch.model_class or Model)(arch.plan(config), torch.float32, "cpu")
     tensors = random_tensors(model.tensor_specs(), seed, std, dtype)
     path = Path(model_dir)
     path.mkdir(parents=True, exist_ok=True)

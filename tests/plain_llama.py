@@ -85,30 +85,40 @@ def attention_scores(q, k, v, scale: float, window: int | None = None) -> torch.
 def attention_layer(x, w, prefix, cfg, window=None, shared_kv=None):
     """src/llmserve/model/llama.py:78-88: projections, rotary on q and k, attention, output
     projection.  Returns the layer's contribution and its (rotated k, v) so that another layer
-    can share them."""
+    can share them.  Bias vectors are added where ``w`` holds them: the reference's q, k and v
+    projections take one as an option (src/llmserve/model/llama.py:64-66), its output projection
+    never does (an ``o_proj.bias`` here serves the engine's general part only)."""
     T = x.shape[0]
     H, KV = cfg["num_attention_heads"], cfg.get("num_key_value_heads") or cfg["num_attention_heads"]
     D = cfg["hidden_size"] // H
     theta = float(cfg.get("rope_theta", 10000.0))
     cos, sin = rope_cos_sin(torch.arange(T), D, theta)
-    q = (x @ w[prefix + "q_proj.weight"].T).view(T, H, D).transpose(0, 1)
+    def project(name):
+        y = x @ w[prefix + name + ".weight"].T
+        return y + w[prefix + name + ".bias"] if prefix + name + ".bias" in w else y
+
+    q = project("q_proj").view(T, H, D).transpose(0, 1)
     q = apply_rope(q, cos, sin)
     if shared_kv is None:
-        k = (x @ w[prefix + "k_proj.weight"].T).view(T, KV, D).transpose(0, 1)
-        v = (x @ w[prefix + "v_proj.weight"].T).view(T, KV, D).transpose(0, 1)
+        k = project("k_proj").view(T, KV, D).transpose(0, 1)
+        v = project("v_proj").view(T, KV, D).transpose(0, 1)
         k = apply_rope(k, cos, sin)
     else:
         k, v = shared_kv
     o = attention_scores(q, k, v, 1.0 / math.sqrt(D), window)
-    o = o.transpose(0, 1).reshape(T, H * D)
-    return o @ w[prefix + "o_proj.weight"].T, (k, v)
+    x = o.transpose(0, 1).reshape(T, H * D)
+    return project("o_proj"), (k, v)
 
 
 def swiglu_mlp(x, w, prefix):
-    """src/llmserve/model/llama.py:119-120: down(silu(gate(x)) * up(x)), silu(z) = z * sigmoid(z)."""
-    g = x @ w[prefix + "gate_proj.weight"].T
-    u = x @ w[prefix + "up_proj.weight"].T
-    return ((g * torch.sigmoid(g)) * u) @ w[prefix + "down_proj.weight"].T
+    """src/llmserve/model/llama.py:119-120: down(silu(gate(x)) * up(x)), silu(z) = z * sigmoid(z).  The reference's
+    three products carry no bias; vectors ``*_proj.bias`` in ``w`` are added for the engine's general part."""
+    def project(x, name):
+        y = x @ w[prefix + name + ".weight"].T
+        return y + w[prefix + name + ".bias"] if prefix + name + ".bias" in w else y
+
+    g, u = project(x, "gate_proj"), project(x, "up_proj")
+    return project((g * torch.sigmoid(g)) * u, "down_proj")
 
 
 def forward(cfg: dict, w: dict[str, torch.Tensor], tokens, windows=None, schedule=None) -> torch.Tensor:

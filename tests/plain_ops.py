@@ -99,6 +99,11 @@ def swiglu(gate_up):
     return (g * torch.sigmoid(g) * u).to(gate_up.dtype)
 
 
+def add_bias(x, bias):
+    x.copy_((x.float() + bias.float()).to(x.dtype))
+    return x
+
+
 def linear_swiglu(x, w_gate_up):
     return swiglu(linear(x, w_gate_up))
 
@@ -129,6 +134,7 @@ ALL = (
     "rope_inplace",
     "paged_attention",
     "swiglu",
+    "add_bias",
     "linear_swiglu",
     "linear_qkv_rope",
     "argmax",

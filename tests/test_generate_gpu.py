@@ -174,46 +174,6 @@ def test_requests_that_come_go_and_are_put_back_at_random(name, stream_seed, mod
     llm.cache.check()
 
 
-@pytest.mark.parametrize("name", ["c", "d"])
-def test_one_kernel_decode_step_equals_the_step_kernel_by_kernel(name, model_folder, monkeypatch):
-    """Head sizes 64 and 128 with up to 8 requests can decode through one cooperative kernel (an
-    option, off by default: it measured slower); the same step kernel by kernel (graphs off) must
-    give the same logits up to rounding."""
-    from llmserve_triton_kernels_b200 import ops
-    from llmserve_triton_kernels_b200.engine.batch import StepEntry
-
-    monkeypatch.setattr(ops, "_FUSED_DECODE_ENABLED", True)
-
-    cfg, seed, _, _ = tiny_configs.TINY[name]
-    folder = model_folder(cfg, seed, torch.bfloat16)
-    plain_cfg, w = plain_llama.read_model(folder)
-    prompts = tiny_configs.seeded_tokens(cfg["vocab_size"], [5, 33, 1, 17, 64, 2, 9], 71)
-    fused = engine(folder, "bfloat16", max_batch_size=8, num_blocks=96)
-    plain = engine(folder, "bfloat16", max_batch_size=8, num_blocks=96)
-    plain.step_function.use_graphs = False
-    for llm in (fused, plain):
-        llm.step_function([StepEntry(f"r{i}", p, []) for i, p in enumerate(prompts)])
-    seqs = [list(p) for p in prompts]
-    nxt = [p[-1] for p in prompts]
-    for step in range(12):
-        entries = [StepEntry(f"r{i}", [t], [0]) for i, t in enumerate(nxt)]
-        a = fused.step_function(entries).float().cpu()
-        b = plain.step_function(entries).float().cpu()
-        for i, t in enumerate(nxt):
-            seqs[i].append(t)
-        scale = float(b.abs().max())
-        assert float((a - b).abs().max()) <= 2e-2 * scale, f"step {step}"
-        if step in (0, 11):  # and both follow the plain implementation
-            for i in (0, 4):
-                ref = plain_llama.forward(plain_cfg, w, seqs[i])[-1]
-                assert float((a[i] - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
-        nxt = [int(t) for t in torch.argmax(b, dim=-1)]
-    graph = fused.step_function.graphs[len(prompts)]
-    assert getattr(graph.ctx, "_fused_plan", None), "the one-kernel path was not taken"
-    assert graph.launches <= 3  # the step itself and little else
-    ops.check_device_errors()
-
-
 def test_long_decoding_to_the_last_position(model_folder):
     """One token at a time from position 1 to the model's limit, in both dtypes."""
     from llmserve_triton_kernels_b200.engine.batch import StepEntry

@@ -205,7 +205,7 @@ def step_ctx(ctx_lens, q_lens):
 @pytest.mark.parametrize(
     "H,KV,D,page_size,window",
     [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 2, 48, 4, None), (8, 8, 64, 16, 9), (5, 5, 80, 32, None),
-     (12, 4, 128, 64, 33), (2, 1, 256, 16, None), (7, 7, 112, 16, 1)],
+     (12, 4, 128, 64, 33), (2, 1, 256, 16, None), (7, 7, 112, 16, 1), (5, 5, 20, 8, None), (4, 2, 100, 16, 7), (3, 1, 6, 4, None)],
 )
 def test_paged_attention_mixed_batch(dtype, H, KV, D, page_size, window):
     ctx_lens, q_lens = [70, 1, 33, 129, 17], [5, 1, 33, 1, 2]  # a portion, a first token, a whole prompt, decodes
@@ -425,6 +425,20 @@ def test_swiglu(dtype, n, inter):
     torch.testing.assert_close(ops().swiglu(gate_up).float(), plain_ops.swiglu(gate_up).float(), **tol(dtype, 3.0))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,cols,pad", [(3, 172, 0), (17, 2560, 8), (1, 5, 3), (300, 100, 0)])
+def test_add_bias(dtype, n, cols, pad):
+    wide = rnd(n, cols + pad, dtype=dtype, seed=17)
+    x = wide[:, :cols]  # rows wider than the columns that take the bias
+    bias = rnd(cols, dtype=dtype, seed=18)
+    want = (x.float() + bias.float()).to(dtype)
+    before = wide.clone()
+    got = ops().add_bias(x, bias)
+    assert got.data_ptr() == x.data_ptr()
+    torch.testing.assert_close(x.float(), want.float(), atol=0, rtol=0)
+    torch.testing.assert_close(wide[:, cols:], before[:, cols:], atol=0, rtol=0)
+
+
 @pytest.mark.parametrize("rows,vocab", [(1, 256), (5, 32000), (3, 50257), (2, 7)])
 def test_argmax_lowest_index_among_equals(rows, vocab):
     logits = rnd(rows, vocab, seed=13)
@@ -498,23 +512,3 @@ def test_sample_follows_the_distribution():
     freq = torch.bincount(got, minlength=vocab).double() / draws
     assert freq[probs == 0].sum() == 0  # nothing outside the top 10
     assert (freq - probs.double()).abs().max() < 0.03
-
-
-def test_grid_barrier_of_the_one_kernel_decode_step():
-    """The grid-wide barrier that the one-kernel decode step is built on (one CTA per SM, launched
-    cooperatively; its wait is bounded): 200 barriers in a row complete, the counter holds every arrival and
-    no CTA gave up."""
-    import ctypes
-
-    o = ops()
-    lib = o.library()
-    lib.llm_grid_barrier_probe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
-    lib.llm_grid_barrier_probe.restype = ctypes.c_int
-    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
-    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
-    rounds = 200
-    code = lib.llm_grid_barrier_probe(counter.data_ptr(), rounds, flag.data_ptr(), torch.cuda.current_stream().cuda_stream)
-    assert code == 0
-    torch.cuda.synchronize()
-    sms = torch.cuda.get_device_properties(0).multi_processor_count
-    assert int(flag) == 0 and int(counter) == rounds * sms

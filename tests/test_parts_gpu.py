@@ -59,14 +59,18 @@ def test_rotary_part(dtype):
         torch.testing.assert_close(got.float().cpu(), want, atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("bias", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_feed_forward_part(dtype):
+def test_feed_forward_part(dtype, bias):
     from llmserve_triton_kernels_b200.parts import PartSpec, build_part
 
-    ff = build_part("feed_forward", PartSpec("gated_mlp", {"hidden_size": 40, "intermediate_size": 104}))
+    ff = build_part("feed_forward", PartSpec("gated_mlp", {"hidden_size": 40, "intermediate_size": 104, "bias": bias}))
     w = {"gate_proj.weight": rnd(104, 40, seed=6, std=0.2), "up_proj.weight": rnd(104, 40, seed=7, std=0.2),
          "down_proj.weight": rnd(40, 104, seed=8, std=0.2)}
+    if bias:
+        w.update({"gate_proj.bias": rnd(104, seed=60), "up_proj.bias": rnd(104, seed=61), "down_proj.bias": rnd(40, seed=62)})
     w = {k: v.to(dtype) for k, v in w.items()}
+    assert {k: v.shape for k, v in ff.tensors().items()} == {k: tuple(v.shape) for k, v in w.items()}
     ff.bind(w, dtype, DEV)
     for n in (3, 70):  # few rows: the fused decode kernels in bfloat16; many: the library product
         x = rnd(n, 40, seed=9).to(dtype)
@@ -78,21 +82,24 @@ def test_feed_forward_part(dtype):
         build_part("feed_forward", PartSpec("gated_mlp", {"hidden_size": 8, "intermediate_size": 8, "activation": "relu"}))
 
 
-def _attention_alone(dtype, window, page_size):
+def _attention_alone(dtype, window, page_size, D=32, bias=False, position_kind="rotary"):
     """The attention part over a cache of its own, fed in three portions, against the plain layer."""
     from llmserve_triton_kernels_b200.cache import CacheManager
     from llmserve_triton_kernels_b200.engine.batch import StepEntry, pack_step
     from llmserve_triton_kernels_b200.models.plan import LayerRun
     from llmserve_triton_kernels_b200.parts import PartSpec, build_part
 
-    H, KV, D, hidden, T = 6, 2, 32, 80, 37
+    H, KV, hidden, T = 6, 2, 80, 37
     cfg = {"num_attention_heads": H, "num_key_value_heads": KV, "hidden_size": H * D, "rope_theta": 3000.0}
-    rotary = PartSpec("rotary", {"head_dim": D, "theta": 3000.0, "max_positions": 64})
+    rotary = PartSpec(position_kind, {"head_dim": D, "theta": 3000.0, "max_positions": 64})
     attn = build_part("mixer", PartSpec("attention", {
         "hidden_size": hidden, "num_heads": H, "num_kv_heads": KV, "head_dim": D, "scale": D**-0.5, "window": window,
-        "position": rotary}))
+        "position": rotary, "qkv_bias": bias, "out_bias": bias}))
     w = {"q_proj.weight": rnd(H * D, hidden, seed=10, std=0.1), "k_proj.weight": rnd(KV * D, hidden, seed=11, std=0.1),
          "v_proj.weight": rnd(KV * D, hidden, seed=12, std=0.1), "o_proj.weight": rnd(hidden, H * D, seed=13, std=0.1)}
+    if bias:
+        w.update({"q_proj.bias": rnd(H * D, seed=70), "k_proj.bias": rnd(KV * D, seed=71), "v_proj.bias": rnd(KV * D, seed=72),
+                  "o_proj.bias": rnd(hidden, seed=73)})
     w = {k: v.to(dtype) for k, v in w.items()}
     assert {k: v.shape for k, v in attn.tensors().items()} == {k: tuple(v.shape) for k, v in w.items()}
     attn.bind(w, dtype, DEV)
@@ -123,6 +130,39 @@ def _attention_alone(dtype, window, page_size):
 @pytest.mark.parametrize("window,page_size", [(None, 8), (5, 4), (16, 16)])
 def test_attention_part(dtype, window, page_size):
     _attention_alone(dtype, window, page_size)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D", [20, 100, 64])
+def test_attention_part_at_head_sizes_that_are_no_multiple_of_16_and_with_biases(dtype, D):
+    """Head sizes 20 and 100 (a hidden size of 3200 over 32 heads) take the general attention kernel in both
+    precisions; with ``qkv_bias`` and ``out_bias`` the projections carry bias vectors, and the fused decode kernels
+    (which have no place for one) stand aside for the product and a bias kernel."""
+    _attention_alone(dtype, None, 8, D=D)
+    _attention_alone(dtype, 9, 16, D=D, bias=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_rotary_table_of_another_layout_is_not_taken_for_the_half_rotation(dtype):
+    """A position encoding that tabulates its angles like the rotary one but says nothing of how lanes pair
+    (``rotary_layout`` None) must be asked to ``apply`` itself: the kernels that rotate while they store keys know the
+    half-rotation layout only.  Here the encoding's own ``apply`` IS the half rotation, so the plain layer stays the
+    oracle; a call counter shows which way was taken."""
+    from llmserve_triton_kernels_b200.parts import register_part
+    from llmserve_triton_kernels_b200.parts.rotary import RotaryEmbedding
+
+    calls = []
+
+    class OtherLayout(RotaryEmbedding):
+        rotary_layout = None
+
+        def apply(self, q, k, positions):
+            calls.append(q.shape[0])
+            super().apply(q, k, positions)
+
+    register_part("position", "other_layout_rotary", OtherLayout)
+    _attention_alone(dtype, None, 8, position_kind="other_layout_rotary")
+    assert calls == [20, 1, 16]
 
 
 # ------------------------------------------------------------------ a toy architecture, defined here
@@ -194,9 +234,9 @@ def register_toy():
 
         def layer(i, mixer):
             p = f"model.layers.{i}."
-            return LayerSpec(PartSpec("pre_norm"), PartSpec("rms_norm", norm, p + "input_layernorm."), mixer,
-                             PartSpec("rms_norm", norm, p + "post_attention_layernorm."),
-                             PartSpec("gated_mlp", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size}, p + "mlp."))
+            return LayerSpec(PartSpec("pre_norm"), mixer_norm=PartSpec("rms_norm", norm, p + "input_layernorm."), mixer=mixer,
+                             ff_norm=PartSpec("rms_norm", norm, p + "post_attention_layernorm."),
+                             feed_forward=PartSpec("gated_mlp", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size}, p + "mlp."))
 
         layers = (layer(0, attention(0)), layer(1, PartSpec("running_mean", {"hidden_size": cfg.hidden_size, "decay": cfg.decay}, "model.layers.1.toy.")),
                   layer(2, attention(2, window=cfg.window)), layer(3, attention(3, own_kv=False)))
@@ -388,7 +428,8 @@ def register_routed_toy():
             attention = PartSpec("attention", {"hidden_size": cfg.hidden_size, "num_heads": cfg.num_heads, "num_kv_heads": cfg.num_kv_heads,
                                                "head_dim": D, "scale": D**-0.5, "position": positions[i]}, p + "self_attn.")
             ff_norm = PartSpec("rms_norm", rms, p + "post_attention_layernorm.") if i == 0 else PartSpec("centred_norm", rms, p + "ff_norm.")
-            layers.append(LayerSpec(PartSpec("pre_norm"), PartSpec("rms_norm", rms, p + "input_layernorm."), attention, ff_norm, feed_forwards[i]))
+            layers.append(LayerSpec(PartSpec("pre_norm"), mixer_norm=PartSpec("rms_norm", rms, p + "input_layernorm."), mixer=attention,
+                                    ff_norm=ff_norm, feed_forward=feed_forwards[i]))
         return ModelPlan(cfg.hidden_size, cfg.vocab_size, cfg.max_positions, "model.embed_tokens.weight", tuple(layers),
                          (LayerRun(0), LayerRun(1)), PartSpec("rms_norm", rms, "model.norm."), "lm_head.weight")
 
@@ -502,7 +543,7 @@ def test_llama_parts_in_another_order_windows_repeats_and_shared_caches(dtype, s
     layers = []
     for spec, window in zip(base.layers, windows):
         mixer = PartSpec(spec.mixer.kind, {**spec.mixer.params, "window": window}, spec.mixer.prefix)
-        layers.append(replace(spec, mixer=mixer))
+        layers.append(spec.replace(mixer=mixer))
     schedule = (LayerRun(0), LayerRun(1), LayerRun(1), LayerRun(2), LayerRun(0))  # layer 1 twice, layer 0 again at the end
     plan = replace(base, layers=tuple(layers), schedule=schedule)
     model = Model(plan, torch.float32 if dtype == "float32" else torch.bfloat16, DEV)
