@@ -134,6 +134,8 @@ LLM_EXPORT int llm_attention_mma_routed(const void* q, int q_stride, void* out, 
     if ((splits_small > 1 || splits_large > 1) && (!scratch_o || !scratch_ml)) return LLM_ERR_BAD_ARGUMENT;
     if (splits_small > 1 && !counters) return LLM_ERR_BAD_ARGUMENT;
     if (splits_small > 32) return LLM_ERR_BAD_ARGUMENT;
+    // the merge of the 64-row shape's splits walks every token of the step, also those that another kernel serves
+    if (splits_large > 1 && skip_tokens_from > 0) return LLM_ERR_BAD_ARGUMENT;
     AttnParams p;
     p.q = (const __nv_bfloat16*)q;
     p.q_stride = q_stride;

@@ -86,20 +86,23 @@ class DecodeGraph:
         self.copied.record()
 
     def run(self) -> torch.Tensor:
-        """Logits ``[R, vocab]`` of the step whose arrays were filled last.  The tensor is
-        the graph's own: the next replay overwrites it."""
+        """Logits ``[R, vocab]`` of the step whose arrays were filled last.  The tensor is the graph's own from the
+        second call on: the next replay overwrites it.  The first call runs the step once, kernel by kernel (which
+        also sets up libraries and kernel attributes, as must happen outside a capture), hands out that pass's
+        logits and then only records the graph, which executes nothing: no step runs twice, so a part that keeps
+        state of its own need not be idempotent to be captured."""
         if self.graph is None:
-            self._capture()
+            return self._first_run_and_capture()
         self.graph.replay()
         ops.add_launches(self.launches)
         return self.logits
 
-    def _capture(self) -> None:
+    def _first_run_and_capture(self) -> torch.Tensor:
         current = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(current)
-        with torch.cuda.stream(side):  # once outside a capture: lazy set-up of libraries and kernels
-            self.model.forward(self.ctx, self.views)
+        with torch.cuda.stream(side):
+            first = self.model.forward(self.ctx, self.views)
         current.wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -109,3 +112,4 @@ class DecodeGraph:
         self.launches = ops.launch_count() - before
         ops.add_launches(-self.launches)  # a capture launches nothing
         self.graph = graph
+        return first

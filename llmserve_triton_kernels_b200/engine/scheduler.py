@@ -26,9 +26,10 @@ from dataclasses import dataclass, field
 from enum import Enum
 from time import perf_counter
 
-from ..cache import CacheManager, OutOfPages
 import torch
 
+from .. import ops
+from ..cache import CacheManager, OutOfPages
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 
@@ -148,70 +149,72 @@ class Scheduler:
         # steps.  The host sees a step's tokens one call of step() later.
         self.run_ahead = bool(getattr(step_function, "use_graphs", False)) if run_ahead is None else bool(run_ahead)
         self._ahead: _Ahead | None = None
+        self._pinned: dict[int, dict] = {}
 
-    # ------------------------------------------------------------------ public
-    def validate_request(self, prompt_len: int, max_new_tokens: int) -> None:
-        """Raise ValueError for a request that could never be served (src/llmserve/scheduler/engine.py:111-125)."""
+    # ------------------------------------------------------------------ requests in and out
+    def _unservable(self, prompt_len: int, max_new_tokens: int) -> str | None:
+        """Why a request of these lengths could never run here, or None.  The page need is the cache manager's: the
+        most pages any group of layers holds for it at once, a windowed group giving pages back as it goes."""
         if prompt_len < 1:
-            raise ValueError("prompt must contain at least one token")
+            return "prompt must contain at least one token"
         if max_new_tokens < 1:
-            raise ValueError("max_new_tokens must be >= 1")
-        total = prompt_len + max_new_tokens
-        if total > self.max_position:
-            raise ValueError(f"prompt + max_new_tokens = {total} exceeds model limit {self.max_position}")
-        need = self.cache.peak_pages_for(total, min(self.chunk_size, self.max_num_batched_tokens))
-        if need > self.cache.num_pages:
-            raise ValueError(f"request needs {need} pages but the pool has only {self.cache.num_pages}")
+            return "max_new_tokens must be >= 1"
+        longest = prompt_len + max_new_tokens
+        if longest > self.max_position:
+            return f"prompt + max_new_tokens = {longest} exceeds model limit {self.max_position}"
+        portion = min(self.chunk_size, self.max_num_batched_tokens)
+        peak = self.cache.peak_pages_for(longest, portion)
+        if peak > self.cache.num_pages:
+            return f"request needs {peak} pages but the pool has only {self.cache.num_pages}"
+        return None
+
+    def validate_request(self, prompt_len: int, max_new_tokens: int) -> None:
+        """ValueError for a request that no amount of waiting would serve (the reference refuses the same four cases
+        up front: src/llmserve/scheduler/engine.py:111-125)."""
+        why = self._unservable(prompt_len, max_new_tokens)
+        if why:
+            raise ValueError(why)
 
     def add_request(self, prompt_ids, params: SamplingParams, *, req_id: int | None = None, arrival_time: float | None = None) -> int:
         self.validate_request(len(prompt_ids), params.max_new_tokens)
-        if req_id is None:
-            req_id = self._next_id
-        self._next_id = max(self._next_id, req_id + 1)
-        seed = params.seed if params.seed is not None else random.getrandbits(63)
-        self.waiting.append(
-            Request(
-                req_id=req_id,
-                prompt_ids=[int(t) for t in prompt_ids],
-                params=params,
-                arrival_time=perf_counter() if arrival_time is None else arrival_time,
-                seed=int(seed) & ((1 << 63) - 1),
-            )
-        )
-        return req_id
+        rid = self._next_id if req_id is None else req_id
+        self._next_id = max(self._next_id, rid + 1)
+        drawn = random.getrandbits(63) if params.seed is None else int(params.seed)
+        self.waiting.append(Request(
+            req_id=rid, prompt_ids=[int(t) for t in prompt_ids], params=params, seed=drawn & ((1 << 63) - 1),
+            arrival_time=perf_counter() if arrival_time is None else arrival_time,
+        ))
+        return rid
 
     def abort(self, req_id: int) -> None:
-        """Cancel a request at the start of the next step.  Thread-safe."""
+        """Cancel a request; it leaves at the start of the next step.  May be called from another thread."""
         with self._lock:
             self._aborts.add(req_id)
 
     def reset(self) -> None:
-        """Drop every request in flight and free all pages (error recovery)."""
-        for r in self.running:
-            if self.cache.has_request(r.req_id):
-                self.cache.free_request(r.req_id)
-        self.running.clear()
-        self.waiting.clear()
+        """Error recovery: every request in flight is dropped (none is reported finished) and its pages come back."""
         self._ahead = None
+        for req in list(self.running):
+            self._leave(req, None)
+        self.waiting.clear()
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting) or bool(self.running)
 
     def snapshot(self) -> dict:
+        """Counters under the names the reference's engine reports them by (src/llmserve/scheduler/engine.py:164-173)."""
+        cache, stats = self.cache, self.stats
         return {
-            "running": len(self.running),
-            "waiting": len(self.waiting),
-            "free_blocks": self.cache.num_free_pages,
-            "total_blocks": self.cache.num_pages,
-            "kv_utilization": round(self.cache.utilization(), 4),
-            "preemptions": self.stats.preemptions,
-            "tokens_generated": self.stats.tokens_generated,
+            "running": len(self.running), "waiting": len(self.waiting),
+            "free_blocks": cache.num_free_pages, "total_blocks": cache.num_pages,
+            "kv_utilization": round(cache.utilization(), 4),
+            "preemptions": stats.preemptions, "tokens_generated": stats.tokens_generated,
         }
 
     def run_until_complete(self) -> dict[int, Request]:
         while self.has_unfinished():
             self.step()
-        self._ahead = None  # a step too many of requests that ended by their end-of-sequence token: nobody reads it
+        self._drop_ahead()  # a step too many of requests that ended by their end-of-sequence token: nobody reads it
         return self.finished
 
     # ------------------------------------------------------------------ one step
@@ -254,8 +257,19 @@ class Scheduler:
                 # a decode step of every running request: its tokens stay on the device for now
                 self._ahead = self._sample_ahead(sampled, logits, params, seeds, counters)
             else:
-                self._append(sampled, self.sampler(logits, params, seeds, counters), events)
+                tokens = self.sampler(logits, params, seeds, counters)  # ends in a read by the host
+                self._check_device()
+                self._append(sampled, tokens, events)
         return events
+
+    def _check_device(self) -> None:
+        """Called where the host has just waited for the device: if a kernel reported that one of its bounded waits
+        gave up, the step's results are not valid; everything in flight is dropped and the error raised."""
+        try:
+            ops.check_device_errors()
+        except ops.KernelError:
+            self.reset()
+            raise
 
     # ------------------------------------------------------------------ one step ahead of the host
     def _sample_ahead(self, reqs: list[Request], logits, params, seeds, counters) -> _Ahead:
@@ -264,11 +278,27 @@ class Scheduler:
         if not logits.is_cuda:
             tokens = self.sampler.on_device(logits, params, seeds, counters)
             return _Ahead(reqs, tokens, tokens.clone(), None)
-        host = torch.empty((logits.shape[0],), dtype=torch.int32, pin_memory=True)
+        host, written = self._pinned_tokens(logits.shape[0])
         tokens = self.sampler.on_device(logits, params, seeds, counters, host_out=host)
-        written = torch.cuda.Event()
         written.record()
         return _Ahead(reqs, tokens, host, written)
+
+    def _pinned_tokens(self, rows: int):
+        """A pinned buffer for a step's tokens and the event that follows the kernel that writes it.  The sampling
+        kernel writes the buffer itself, which torch's allocator of pinned memory knows nothing of, so the buffers
+        are the scheduler's own: a ring of four per row count, each taken again only after its last kernel has run
+        (at most two steps are in flight; a step that nobody collects leaves its buffer to come round)."""
+        ring = self._pinned.setdefault(rows, {"at": 0, "slots": []})
+        if len(ring["slots"]) < 4:
+            ring["slots"].append((torch.empty((rows,), dtype=torch.int32, pin_memory=True), torch.cuda.Event()))
+            return ring["slots"][-1]
+        ring["at"] = (ring["at"] + 1) % 4
+        host, event = ring["slots"][ring["at"]]
+        event.synchronize()
+        return host, event
+
+    def _drop_ahead(self) -> None:
+        self._ahead = None
 
     def _can_run_ahead(self, ahead: _Ahead) -> bool:
         """The step after ``ahead`` can be launched before ``ahead``'s tokens are known: the same requests decode on
@@ -298,25 +328,45 @@ class Scheduler:
         end-of-sequence token came with the step before, or it was aborted) drops its token."""
         if ahead.copied is not None:
             ahead.copied.synchronize()
+        self._check_device()
         tokens = ahead.host_tokens.tolist()
         live = [(r, t) for r, t in zip(ahead.reqs, tokens) if r.status is Status.RUNNING and r in self.running]
         self._append([r for r, _ in live], [t for _, t in live], events)
 
     # ------------------------------------------------------------------ internals
+    def _leave(self, req: Request, how: str | None, events: list[TokenEvent] | None = None, token: int | None = None) -> None:
+        """Every way out of the running set goes through here, so that pages and state slot come back in one place.
+        ``how``: "stop", "length" or "abort" end the request (an event says so, with the last token where there is
+        one); "preempt" frees what it holds and puts it at the head of the queue, to be computed again from its
+        first token; None drops it without a trace."""
+        if any(r is req for r in self.running):
+            self.running.remove(req)
+        if self.cache.has_request(req.req_id):
+            self.cache.free_request(req.req_id)
+        if how is None:
+            return
+        if how == "preempt":
+            req.status, req.num_computed = Status.WAITING, 0
+            req.num_preemptions += 1
+            self.stats.preemptions += 1
+            self.waiting.appendleft(req)
+            return
+        req.status, req.finish_reason, req.finish_time = Status.FINISHED, how, perf_counter()
+        self.finished[req.req_id] = req
+        if events is not None:
+            events.append(TokenEvent(req.req_id, token, True, how))
+
     def _process_aborts(self, events: list[TokenEvent]) -> None:
         with self._lock:
-            aborts, self._aborts = self._aborts, set()
-        for rid in sorted(aborts):
-            req = next((r for r in self.waiting if r.req_id == rid), None)
-            if req is not None:
+            wanted, self._aborts = self._aborts, set()
+        if not wanted:
+            return
+        leaving = [r for r in list(self.waiting) + self.running if r.req_id in wanted]
+        for req in sorted(leaving, key=lambda r: r.req_id):
+            if req.status is Status.WAITING:
                 self.waiting.remove(req)
-            else:
-                req = next((r for r in self.running if r.req_id == rid), None)
-                if req is None:
-                    continue  # already finished
-                self.running.remove(req)
-                self.cache.free_request(rid)
-            self._finish(req, "abort", events, emit_token=None)
+            self._leave(req, "abort", events)
+        # an id that is neither waiting nor running has ended already: nothing to do
 
     def _portion(self, req: Request, budget: int) -> int:
         remaining = req.num_ids - req.num_computed
@@ -368,35 +418,21 @@ class Scheduler:
         return plan
 
     def _preempt(self, req: Request) -> None:
-        self.running.remove(req)
-        self.cache.free_request(req.req_id)
-        req.status = Status.WAITING
-        req.num_computed = 0
-        req.num_preemptions += 1
-        self.stats.preemptions += 1
-        self.waiting.appendleft(req)
+        self._leave(req, "preempt")
 
     def _append(self, reqs: list[Request], tokens: list[int], events: list[TokenEvent]) -> None:
+        """The tokens a step chose, one per request: each is recorded, and ends its request if it is the request's
+        end-of-sequence token (which is emitted) or its last by length."""
         now = perf_counter()
-        for r, tok in zip(reqs, tokens):
-            r.append(int(tok))
-            r.token_times.append(now)
-            self.stats.tokens_generated += 1
-            reason = None
-            if r.params.eos_token_id is not None and tok == r.params.eos_token_id:
-                reason = "stop"
-            elif len(r.generated) >= r.params.max_new_tokens:
-                reason = "length"
-            if reason:
-                self.running.remove(r)
-                self.cache.free_request(r.req_id)
-                self._finish(r, reason, events, emit_token=int(tok))
+        self.stats.tokens_generated += len(reqs)
+        for req, token in zip(reqs, tokens):
+            token = int(token)
+            req.append(token)
+            req.token_times.append(now)
+            params = req.params
+            if params.eos_token_id is not None and token == params.eos_token_id:
+                self._leave(req, "stop", events, token)
+            elif len(req.generated) >= params.max_new_tokens:
+                self._leave(req, "length", events, token)
             else:
-                events.append(TokenEvent(r.req_id, int(tok), False))
-
-    def _finish(self, req: Request, reason: str, events: list[TokenEvent], emit_token: int | None) -> None:
-        req.status = Status.FINISHED
-        req.finish_reason = reason
-        req.finish_time = perf_counter()
-        self.finished[req.req_id] = req
-        events.append(TokenEvent(req.req_id, emit_token, True, reason))
+                events.append(TokenEvent(req.req_id, token, False))

@@ -73,6 +73,7 @@ _launches = 0
 _MMA_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention; others take the general kernel
 _SMALL_ROWS = 16  # requests with at most this many (token, group member) rows take the split-key shape
 _SMALL_TILE_KEYS = 128  # keys one CTA of that shape covers per tile
+_SPLIT_SCRATCH_BYTES = 16 << 20  # most scratch memory the split-key attention's partial results may take per call
 _TC_ATTENTION_ENABLED = True
 _TC_ATTENTION_HEAD_DIM = 64
 _TC_ATTENTION_PAGE_SIZES = (8, 16, 32, 64)
@@ -542,6 +543,9 @@ def paged_attention(
             longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
             useful = -(-longest // _SMALL_TILE_KEYS)
             splits = max(1, min(useful, _sm_count() // (small * num_kv_heads), 32))  # one CTA per SM at most: all run at once
+            # the partial results are indexed by token over the whole step: beside a long portion of a prompt the
+            # decode tokens are not split so finely that the scratch memory grows past a few megabytes
+            splits = min(splits, max(1, _SPLIT_SCRATCH_BYTES // (n * num_heads * head_dim * 4)))
         scratch_o = scratch_ml = counters = None
         if splits > 1:
             counters = _split_counters(qkv.device, num_requests * num_kv_heads)

@@ -69,7 +69,8 @@ class Part:
     category = "part"
     # True if forward() launches the same device work for the same shapes whatever the step's
     # contents (no reads of device data on the host, no host loops over lengths): then a decode
-    # step through this part can be captured in a CUDA graph.
+    # step through this part can be captured in a CUDA graph.  A captured step's first run is an
+    # ordinary pass and every later one a replay, so each step runs exactly once.
     graph_safe = False
 
     def tensors(self) -> dict[str, TensorSpec]:

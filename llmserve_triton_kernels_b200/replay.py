@@ -42,6 +42,7 @@ def parse_args(argv=None):
 def main(argv=None) -> int:
     args = parse_args(argv)
     from . import models as _models  # noqa: F401
+    from . import ops
     from .cache import CacheManager
     from .engine.batch import StepEntry
     from .engine.step import StepFunction
@@ -77,6 +78,7 @@ def main(argv=None) -> int:
                 host.astype("<f4", copy=False).tofile(out_dir / f"{step}.f32")
             elif device.type == "cuda":
                 torch.cuda.synchronize(device)
+            ops.check_device_errors()  # the host has just waited for the device: a kernel whose wait gave up has said so
         for req in record.get("end", []):
             if cache.has_request(req):
                 cache.free_request(req)

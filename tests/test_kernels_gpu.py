@@ -372,6 +372,38 @@ def test_paged_attention_many_requests_each_finds_its_far_key(H, KV, D, monkeypa
                                plain_ops.paged_attention(q2, pool2, table2, ctx, **kw).float(), **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("splits", [2, 5])
+def test_paged_attention_64_row_shape_with_split_keys_and_merge(splits):
+    """The library's C interface lets the 64-row shape split its keys over CTAs too, merged by a kernel of its own
+    (the Python side never asks for it).  Called directly: portions of 40 and 9 tokens behind a thousand keys, beside a
+    decode token of the split-key shape."""
+    import ctypes
+
+    o = ops()
+    lib = o.library()
+    H, KV, D, page_size = 8, 2, 64, 16
+    ctx_lens, q_lens = [1100, 700, 900], [40, 9, 1]
+    pool, table, _, _ = _filled(ctx_lens, KV, D, page_size, seed=41)
+    ctx = step_ctx(ctx_lens, q_lens)
+    n = sum(q_lens)
+    q = rnd(n, H * D, dtype=torch.bfloat16, seed=42)
+    out = torch.zeros((n, H * D), dtype=torch.bfloat16, device=DEV)
+    scratch_o = torch.empty(n * H * splits * D, dtype=torch.float32, device=DEV)
+    scratch_ml = torch.empty(n * H * splits * 2, dtype=torch.float32, device=DEV)
+    counters = torch.zeros(len(q_lens) * KV, dtype=torch.int32, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    args = [q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), pool.data_ptr(), table.data_ptr(), table.shape[1],
+            ctx.token_request.data_ptr(), ctx.cu_tokens.data_ptr(), ctx.context_lens.data_ptr(), len(q_lens), n, H, KV, D, page_size, 0,
+            float(D**-0.5), max(q_lens) * (H // KV), 1, splits, splits, scratch_o.data_ptr(), scratch_ml.data_ptr(), counters.data_ptr()]
+    assert lib.llm_attention_mma(*args, stream) == 0
+    torch.cuda.synchronize()
+    want = plain_ops.paged_attention(q, pool, table, ctx, num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5)
+    torch.testing.assert_close(out.float(), want.float(), **tol(torch.bfloat16))
+    assert int(counters.abs().sum()) == 0  # left zeroed for the next call
+    # requests left to another kernel and split keys of the 64-row shape do not go together: refused, nothing launched
+    assert lib.llm_attention_mma_routed(*args, 128, stream) == 10001
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 16, 17, 40])
 def test_paged_attention_window_edge(dtype, window):

@@ -240,3 +240,39 @@ def test_running_ahead_with_few_pages_and_an_abort(model_folder, plain_ops_engin
     assert got == plain_tokens(plain, prompts[0], 30)[: len(got)]
     assert llm.cache.num_free_pages == llm.cache.num_pages
     llm.cache.check()
+
+
+def test_a_kernel_that_reports_a_failed_wait_stops_the_engine(model_folder, plain_ops_engine, monkeypatch):
+    """Kernels whose bounded waits give up set a word in pinned host memory and run to their end with invalid
+    results.  The scheduler reads the word wherever it has just waited for the device: the step's tokens are not
+    handed out, everything in flight is dropped with its pages, and the error is raised.  The word is set from the
+    host here; no kernel is made to fail."""
+    from llmserve_triton_kernels_b200 import ops
+
+    llm, plain = make(model_folder)
+    sched = llm.scheduler
+    prompts = tiny_configs.seeded_tokens(256, [6, 9], 19)
+    ids = [sched.add_request(p, SamplingParams(max_new_tokens=8)) for p in prompts]
+    sched.step()
+    sched.step()
+    flag = torch.zeros(1, dtype=torch.int32)
+    monkeypatch.setattr(ops, "_error_flag", flag)
+    flag[0] = 1
+    with pytest.raises(ops.KernelError, match="wait"):
+        sched.step()
+    assert int(flag[0]) == 0  # read and cleared
+    assert not sched.has_unfinished() and not sched.finished
+    assert llm.cache.num_free_pages == llm.cache.num_pages
+    llm.cache.check()
+    # the engine serves again afterwards
+    outs = llm.generate(prompts, SamplingParams(max_new_tokens=8))
+    assert [o.token_ids for o in outs] == [plain_tokens(plain, p, 8) for p in prompts]
+    # and the same with steps running ahead of the host
+    ahead(llm)
+    ids = [sched.add_request(p, SamplingParams(max_new_tokens=8)) for p in prompts]
+    while sched._ahead is None:
+        sched.step()
+    flag[0] = 1
+    with pytest.raises(ops.KernelError):
+        sched.step()
+    assert not sched.has_unfinished() and llm.cache.num_free_pages == llm.cache.num_pages

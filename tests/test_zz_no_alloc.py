@@ -22,6 +22,8 @@ from types import SimpleNamespace
 import pytest
 import torch
 
+import plain_ops
+
 pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
@@ -77,6 +79,9 @@ def test_static_scratch_entry_point_matches_the_usual_one_twice_in_a_row():
         # the same kernel and the same split arithmetic: equal up to the order in which splits are merged
         torch.testing.assert_close(got.float(), want.float(), atol=1.6e-2, rtol=1.6e-2)
         assert got.float().abs().max() > 0
+        # and both stand against the plain statement of the attention
+        plain = plain_ops.paged_attention(q, pool, table, ctx, num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5)
+        torch.testing.assert_close(got.float(), plain.float(), atol=1.6e-2, rtol=1.6e-2)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
