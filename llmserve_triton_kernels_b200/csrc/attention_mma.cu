@@ -16,6 +16,7 @@
 // finishes last (a counter per request and key/value head tells) merges them.  A split's share of the keys is worked out on the device from the request's
 // length, so the grid does not depend on the lengths (a CUDA graph replays it as captured).
 #include "attention_tile.cuh"
+#include "timeline.cuh"
 
 namespace {
 
@@ -25,9 +26,14 @@ using namespace attn;
 // head, request * tiles_per_request + row tile).
 template <int D, int ROW_WARPS, int KEY_WARPS, int BN, int STAGES>
 __global__ void __launch_bounds__(32 * ROW_WARPS * KEY_WARPS) attention_mma_kernel(const AttnParams p) {
+    TL(tl::Marks marks;)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     attention_tile<D, ROW_WARPS, KEY_WARPS, BN, STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z / p.tiles_per_request,
                                                 blockIdx.z % p.tiles_per_request, smem_raw, true);
+    TL(__syncthreads(); if (threadIdx.x == 0) {
+        marks.mark(4);
+        marks.write(100 + KEY_WARPS, 0, blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z), p.splits, 0);
+    })
 }
 
 // Merges the splits of every (token, head) whose request went through a launch with splits > 1.
@@ -114,6 +120,8 @@ int launch_all(AttnParams p, int requests, int n_tokens, const int* token_reques
 }
 
 }  // namespace
+
+TL_DEFINE_READER(llm_timeline_read_attention)
 
 // One step's attention in bfloat16.  max_rows_large: the most rows (tokens x group) of any request
 // with more than 16 rows, 0 if there is none; have_small: some request has at most 16 rows.

@@ -23,6 +23,7 @@
 //     next factored normalised form (v * next_norm_weight in bfloat16, partial sums of v^2 per CTA)
 //     is written for the next product.
 #include "linear_stream.cuh"
+#include "timeline.cuh"
 
 #include <mutex>
 #include <unordered_map>
@@ -35,6 +36,7 @@ using namespace lin;
 template <int MT, int MODE, typename TO>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
+    TL(tl::Marks marks;)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [WARPS][SLOTS][SLOT_ELEMS]
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)WARPS * SLOTS * SLOT_ELEMS * 2);  // [tiles of a team][WARPS][MT * 4][32]
@@ -66,11 +68,16 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
         }
     }
     pdl_trigger();
+    TL(marks.mark(1);)
     pdl_wait();
+    TL(marks.mark(2);)
+    if constexpr (MODE == MODE_RESIDUAL) stream_fetch_resid<MT>(st, p);
     stream_stage_x<MT>(p, x_s, row_scale);
     __syncthreads();  // the only CTA-wide barrier
+    TL(marks.mark(3);)
     if (!stream_run<MT, MODE, TO>(st, p, &wmap, my_ring, full[warp], red, x_s, row_scale) && lane == 0 && p.error_flag)
         atomicExch(p.error_flag, 1);
+    TL(__syncthreads(); if (threadIdx.x == 0) { marks.mark(4); marks.write(MODE, p.tl_launch, blockIdx.x, p.N, p.K); })
 }
 
 int sm_count() {
@@ -113,6 +120,7 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     const int tiles = (p.N + FEATURES - 1) / FEATURES;
     const int grid = tiles < sm_count() ? tiles : sm_count();
     LinearParams q = p;
+    TL(static int tl_launches = 0; q.tl_launch = tl_launches++;)
     const size_t fixed = (size_t)WARPS * SLOTS * SLOT_ELEMS * 2 + (size_t)8 * MT * (p.K + X_PAD) * 2;
     if (fixed > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;  // x does not fit beside the rings
     // as many tiles of a team may be shared as their partial sums find room for
@@ -145,6 +153,8 @@ LLM_EXPORT int llm_linear_decode_qkv(const void* x, const void* w, void* q_out, 
                                      int in_parts, float in_eps, const int* positions, const float* rotary, int rotary_rows,
                                      const int* slot_map, void* pool, int H, int KV, int D, int page_size, int* error_flag,
                                      cudaStream_t stream);
+
+TL_DEFINE_READER(llm_timeline_read_linear)
 
 // The most rows this kernel takes; more go to another matrix product.
 LLM_EXPORT int llm_linear_decode_max_rows() { return 16; }

@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "tma.cuh"
+#include "timeline.cuh"
 
 namespace lin {
 
@@ -48,8 +49,7 @@ struct LinearParams {
     const int* slot_map;    // [M] page * page_size + offset of each token
     __nv_bfloat16* pool;    // [pages, 2, KV, page_size, D]
     int H, KV, D, page_size;
-    int resid_early;        // MODE_RESIDUAL: resid may be read before the product's input is ready (it was written
-                            // before the previous grid-wide barrier); a kernel of its own must leave this 0
+    int tl_launch;          // profiling builds: which launch this is
     const void* prefetch;   // weights that a later product will stream: pulled into L2 meanwhile (or null)
     unsigned long long prefetch_bytes;
 };
@@ -102,7 +102,8 @@ struct StreamState {
     bool early;                                  // the values below are there
     float e_cos[MT_MAX][2], e_sin[MT_MAX][2];    // MODE_QKV: the rotation of this thread's pair, per token
     int e_slot[MT_MAX][2];                       // MODE_QKV: the tokens' cache slots
-    float e_resid[MT_MAX][4];                    // MODE_RESIDUAL: the stream's values (only with resid_early)
+    bool have_resid;                             // MODE_RESIDUAL: e_resid holds the stream's values of the first tile
+    float e_resid[MT_MAX][4];                    // MODE_RESIDUAL: fetched by stream_fetch_resid once the kernel in front has ended
     float e_norm[2];                             // MODE_RESIDUAL: the next norm's weights of this thread's features
 };
 
@@ -155,6 +156,7 @@ __device__ __forceinline__ void stream_plan(StreamState& st, const LinearParams&
     st.up_offset = p.up_offset;
     st.D = p.D;
     st.early = false;
+    st.have_resid = false;
     if (st.member == 0 && st.my_tiles > 0) {
         const int qr = lane >> 2, qc = lane & 3, tile = st.first;
         if constexpr (MODE == MODE_QKV) {
@@ -182,16 +184,26 @@ __device__ __forceinline__ void stream_plan(StreamState& st, const LinearParams&
             const int n0 = tile * 16;
 #pragma unroll
             for (int h = 0; h < 2; ++h) st.e_norm[h] = n0 + qr + 8 * h < p.N ? p.norm_w[n0 + qr + 8 * h] : 0.f;
-#pragma unroll
-            for (int t = 0; t < MT; ++t)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int n = n0 + qr + 8 * (e >> 1), m = 8 * t + 2 * qc + (e & 1);
-                    st.e_resid[t][e] = p.resid_early && m < p.M && n < p.N ? p.resid[(size_t)m * p.N + n] : 0.f;
-                }
             st.early = true;
         }
     }
+}
+
+// MODE_RESIDUAL: the residual stream's values that the end of this warp's first tile adds to, asked for as soon as
+// the kernel in front has ended (its writes, and those of every kernel before it, are visible then) instead of at the
+// end of the tile, where the trip to memory would stand between the last product and the kernel's end.
+template <int MT>
+__device__ __forceinline__ void stream_fetch_resid(StreamState& st, const LinearParams& p) {
+    if (st.member != 0 || st.my_tiles <= 0) return;
+    const int lane = threadIdx.x & 31, qr = lane >> 2, qc = lane & 3, n0 = st.first * 16;
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int n = n0 + qr + 8 * (e >> 1), m = 8 * t + 2 * qc + (e & 1);
+            st.e_resid[t][e] = m < p.M && n < p.N ? p.resid[(size_t)m * p.N + n] : 0.f;
+        }
+    st.have_resid = true;
 }
 
 // Fills the free slots of the ring with the product's next boxes; `consumed`: how many of its boxes have been used.
@@ -341,7 +353,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 if constexpr (MODE == MODE_RESIDUAL) {
                     if (live) {
                         const bool have = ti == 0 && st.early;
-                        const float before = have && p.resid_early ? st.e_resid[t][e] : p.resid[(size_t)m * N + n];
+                        const float before = ti == 0 && st.have_resid ? st.e_resid[t][e] : p.resid[(size_t)m * N + n];
                         const float v = before + s;
                         p.resid[(size_t)m * N + n] = v;
                         p.xw_out[(size_t)m * N + n] = __float2bfloat16_rn(v * (have ? st.e_norm[e >> 1] : p.norm_w[n]));
