@@ -56,17 +56,6 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
     // the weights do not depend on what ran before: their first boxes are asked for at once, while the
     // kernel before this one may still be running; everything else waits for it
     stream_begin<MODE, MT>(st, p, &wmap, my_ring, full[warp], 0u);
-    // and the weights of a later product start their way into L2, a slice per CTA, 4 KB per instruction
-    if (p.prefetch && warp == WARPS - 1) {
-        const unsigned long long per_cta = ((p.prefetch_bytes / gridDim.x) + 4095) & ~4095ull;
-        const unsigned long long begin = per_cta * blockIdx.x;
-        const unsigned long long end = begin + per_cta < p.prefetch_bytes ? begin + per_cta : p.prefetch_bytes;
-        for (unsigned long long off = begin + (unsigned long long)lane * 4096; off < end; off += 32ull * 4096) {
-            const unsigned bytes = (unsigned)((end - off < 4096 ? end - off : 4096) & ~15ull);
-            if (bytes)
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"((const char*)p.prefetch + off), "r"(bytes) : "memory");
-        }
-    }
     pdl_trigger();
     TL(marks.mark(1);)
     pdl_wait();
@@ -170,12 +159,11 @@ LLM_EXPORT int llm_linear_decode_parts(int N) { return (N + 15) / 16; }
 // in_ss (or null): [in_parts, M] partial sums of squares; the product is scaled by
 // rsqrt(sum / K + in_eps) per row.  Needs M <= 16, K a multiple of 8, 16-byte aligned rows;
 // otherwise it returns LLM_ERR_UNSUPPORTED and the caller takes another route.  error_flag (host-visible
-// int, or null) is set to 1 if a bounded wait inside the kernel ever gives up.  prefetch (or null): 16-byte
-// aligned weights of a later product, pulled into L2 while this one runs.
+// int, or null) is set to 1 if a bounded wait inside the kernel ever gives up.
 LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldx,
                                  int ldo, const float* in_ss, int in_parts, float in_eps, int mode, int up_offset,
                                  float* resid, const float* norm_w, void* xw_out, float* ss_out, int* error_flag,
-                                 const void* prefetch, unsigned long long prefetch_bytes, cudaStream_t stream) {
+                                 cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return LLM_ERR_UNSUPPORTED;
     LinearParams p = {};
@@ -196,8 +184,6 @@ LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int ou
     p.xw_out = (__nv_bfloat16*)xw_out;
     p.ss_out = ss_out;
     p.error_flag = error_flag;
-    p.prefetch = prefetch;
-    p.prefetch_bytes = prefetch ? prefetch_bytes : 0;
     if (mode == MODE_RESIDUAL) {
         if (!resid || !norm_w || !xw_out || !ss_out) return LLM_ERR_BAD_ARGUMENT;
         return dispatch<MODE_RESIDUAL, __nv_bfloat16>(p, stream);

@@ -50,8 +50,6 @@ struct LinearParams {
     __nv_bfloat16* pool;    // [pages, 2, KV, page_size, D]
     int H, KV, D, page_size;
     int tl_launch;          // profiling builds: which launch this is
-    const void* prefetch;   // weights that a later product will stream: pulled into L2 meanwhile (or null)
-    unsigned long long prefetch_bytes;
 };
 
 constexpr int SLOTS = 4;   // boxes per warp, all in flight but for the moment in which one is read into registers
@@ -268,12 +266,10 @@ __device__ __forceinline__ void stream_stage_x(const LinearParams& p, __nv_bfloa
 }
 
 // The products of every box of this warp's tiles and the tiles' epilogues.  Returns false if a wait gave up.
-// `next` (or null): the planned product that follows on the same ring (its base is this one's base plus units); once
-// all of this product's boxes are on their way, the slots it frees take the next product's boxes.
 template <int MT, int MODE, typename TO>
 __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& p, const CUtensorMap* wmap, __nv_bfloat16* my_ring,
                                            unsigned long long* my_full, float* red, const __nv_bfloat16* x_s,
-                                           const float* row_scale, StreamState* next = nullptr, const CUtensorMap* next_map = nullptr) {
+                                           const float* row_scale) {
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
     constexpr int CHAINS = MT == 1 ? 4 : 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -409,10 +405,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     b[i][t] = have ? *reinterpret_cast<const uint4*>(xrow[t] + k0 + i * 32) : make_uint4(0, 0, 0, 0);
             }
             __syncwarp();  // every lane holds its pieces of the slot in registers: the slot takes the next box
-            if (lane == 0) {
-                if (st.armed < units) arm_next(st, wmap, my_ring, my_full);
-                else if (next && next->armed < next->units) arm_next(*next, next_map, my_ring, my_full);
-            }
+            if (lane == 0 && st.armed < units) arm_next(st, wmap, my_ring, my_full);
 #pragma unroll
             for (int i = 0; i < PIECES; ++i)
 #pragma unroll

@@ -74,14 +74,6 @@ class Model:
         for prefix, part in self._named_parts:
             local = {name: tensors[prefix + name] for name in part.tensors()}
             part.bind(local, self.dtype, self.device)
-        if self.dtype == torch.bfloat16:
-            # the order in which a step streams its matrices, for the decode products' L2 prefetch
-            order = []
-            for run in self.plan.schedule:
-                block = self.blocks[run.layer]
-                for part in block.owned_parts():
-                    order += list(getattr(part, "streamed_weights", lambda: [])())
-            ops.set_weight_order(order + [self.head])
 
     def weight_bytes(self) -> int:
         """Bytes of every distinct weight tensor a step reads (the token table only if it is also the head)."""

@@ -28,7 +28,7 @@ _SIGNATURES = {
     "llm_add_bias": [_vp, _i, _i, _i, _i, _vp, _vp],
     "llm_fetch_words": [_vp, _vp, _vp, _i, _i, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_ulonglong, _vp],
+    "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_linear_decode_qkv": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_tcgen05": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_tcgen05_fused": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -211,32 +211,6 @@ def check_device_errors() -> None:
         raise KernelError("a kernel's wait for an asynchronous copy gave up; its results are not valid")
 
 
-_PREFETCH_AHEAD = 2  # a product pulls the weights of the product two places later into L2
-_PREFETCH_MAX_BYTES = 64 << 20  # at most this much of a matrix (the whole L2 holds 126 MB)
-
-
-def set_weight_order(weights: list[torch.Tensor]) -> None:
-    """Tell the decode products in which order a step streams its weight matrices, so that each
-    can pull a later one into L2 while it runs (HBM then stays busy through the short kernels
-    in between).  A model calls this once its weights are bound; the order wraps around.  The
-    hint hangs on the weight tensor itself and keeps the later matrix alive."""
-    n = len(weights)
-    if n <= _PREFETCH_AHEAD:
-        return
-    for i, w in enumerate(weights):
-        w._llm_prefetch_next = weights[(i + _PREFETCH_AHEAD) % n]
-
-
-_PREFETCH_ENABLED = False  # measured on a 1.1B model: the prefetches queue ahead of the product's own loads and cost more than they save
-
-
-def _prefetch_hint(w: torch.Tensor) -> tuple[int | None, int]:
-    later = getattr(w, "_llm_prefetch_next", None) if _PREFETCH_ENABLED else None
-    if later is None:
-        return None, 0
-    return later.data_ptr(), min(later.numel() * later.element_size(), _PREFETCH_MAX_BYTES)
-
-
 class NormedInput:
     """A normalised activation in factored form, as the fused decode kernels hand it on:
     ``xw [M, hidden]`` holds ``v * norm_weight`` (``v`` the residual stream after the last sum) and
@@ -300,7 +274,7 @@ class ResidualSink:
         ss = torch.empty((parts, m), dtype=torch.float32, device=x.device)
         code = _launch(
             "llm_linear_decode", _ptr(x), _ptr(w), None, _BF16, m, n, k, x.stride(0), n, None, 0, 0.0, 2, 0,
-            _ptr(self.resid), _ptr(self.weight), _ptr(xw), _ptr(ss), _error_flag_ptr(), *_prefetch_hint(w), _stream(),
+            _ptr(self.resid), _ptr(self.weight), _ptr(xw), _ptr(ss), _error_flag_ptr(), _stream(),
         )
         if code == 10002:
             add_launches(-1)
@@ -320,7 +294,7 @@ def _decode_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):
     code = _launch(
         "llm_linear_decode", _ptr(xt), _ptr(w), _ptr(out), _code(out_dtype), m, n_out, k, xt.stride(0), n_out,
         _ptr(x.ss) if scaled else None, x.ss.shape[0] if scaled else 0, x.eps if scaled else 0.0, mode, up_offset,
-        None, None, None, None, _error_flag_ptr(), *_prefetch_hint(w), _stream(),
+        None, None, None, None, _error_flag_ptr(), _stream(),
     )
     if code == 10002:  # a shape the kernel refuses
         add_launches(-1)

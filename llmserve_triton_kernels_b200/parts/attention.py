@@ -88,10 +88,6 @@ class PagedAttention(Mixer):
         if self.position is not None:
             self.position.bind({}, dtype, device)
 
-    def streamed_weights(self):
-        """The matrices a step reads, in the order it reads them."""
-        return [self.w_in, self.w_out]
-
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 

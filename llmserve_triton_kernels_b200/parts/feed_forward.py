@@ -51,10 +51,6 @@ class GatedMLP(FeedForward):
 
     accepts_sink = True
 
-    def streamed_weights(self):
-        """The matrices a step reads, in the order it reads them."""
-        return [self.w_gate_up, self.w_down]
-
     def forward(self, x, ctx, sink=None):
         if self.bias:
             act = ops.swiglu(ops.add_bias(ops.linear(x, self.w_gate_up), self.b_gate_up))
