@@ -16,6 +16,8 @@
 // finishes last (a counter per request and key/value head tells) merges them.  A split's share of the keys is worked out on the device from the request's
 // length, so the grid does not depend on the lengths (a CUDA graph replays it as captured).
 #include "attention_tile.cuh"
+
+#include <cstdlib>
 #include "timeline.cuh"
 
 namespace {
@@ -29,7 +31,7 @@ __global__ void __launch_bounds__(32 * ROW_WARPS * KEY_WARPS) attention_mma_kern
     TL(tl::Marks marks;)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     attention_tile<D, ROW_WARPS, KEY_WARPS, BN, STAGES>(p, blockIdx.x, blockIdx.y, blockIdx.z / p.tiles_per_request,
-                                                blockIdx.z % p.tiles_per_request, smem_raw, true);
+                                                blockIdx.z % p.tiles_per_request, smem_raw, true TL(, &marks));
     TL(__syncthreads(); if (threadIdx.x == 0) {
         marks.mark(4);
         marks.write(100 + KEY_WARPS, 0, blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z), p.splits, 0);
@@ -73,6 +75,11 @@ int launch_shape(const AttnParams& p, int requests, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
+    static bool carved = false;  // per instantiation: all of the SM's memory as shared memory, so that this kernel's CTAs
+    if (!carved) {               // may join those of the kernel in front on an SM, and the next kernel's may join them
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        carved = true;
+    }
     const long long z = (long long)requests * p.tiles_per_request;
     if (z > 65535 || p.KV > 65535) return LLM_ERR_UNSUPPORTED;
     dim3 grid(p.splits, p.KV, (unsigned)z);
@@ -99,7 +106,8 @@ int launch_all(AttnParams p, int requests, int n_tokens, const int* token_reques
         int sms = 0, dev = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-        const bool many = (long long)requests * p.KV > sms;
+        static const int forced = [] { const char* e = getenv("LLMSERVE_B200_ATTN_KEY_WARPS"); return e ? atoi(e) : 0; }();
+        const bool many = forced ? forced == 8 : (long long)requests * p.KV > sms;
         if constexpr (D <= 64) code = many ? launch_shape<D, 1, 8, 16, 3>(p, requests, stream) : launch_shape<D, 1, 16, 16, 3>(p, requests, stream);
         else code = launch_shape<D, 1, 8, 16, 3>(p, requests, stream);
         if (code) return code;

@@ -4,12 +4,13 @@
 #pragma once
 
 #include "common.cuh"
+#include "timeline.cuh"
 
 namespace attn {
 
 
 constexpr int SMALL_ROWS = 16;  // requests with at most this many rows go to the KEYS shape
-constexpr int SMALL_MIN_TILES = 3;  // tiles (256 keys at head sizes up to 64) a split of that shape takes at least: measured best of 2, 3, 4, 8
+constexpr int SMALL_MIN_KEYS = 768;  // keys a split of that shape takes at least (three tiles of 256): measured best of 512, 768, 1024, 2048
 
 // The threads that compute a tile meet here.  A named barrier, not __syncthreads: inside the fused decode
 // kernel the tile is computed by four of the CTA's eight warps.
@@ -76,7 +77,7 @@ __host__ __device__ constexpr int stages_of(int D, int key_warps) { return D <= 
 // D: head size.  ROW_WARPS x KEY_WARPS warps.  BN: keys per warp and tile.
 template <int D, int ROW_WARPS, int KEY_WARPS, int BN, int STAGES = stages_of(D, KEY_WARPS)>
 __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, int kvh, int r, int tile, unsigned char* smem_raw,
-                                               bool use_pdl) {
+                                               bool use_pdl TL(, tl::Marks* marks = nullptr)) {
     constexpr int THREADS = 32 * ROW_WARPS * KEY_WARPS;
     constexpr int BM = 16 * ROW_WARPS;   // rows of the CTA
     constexpr int BNC = BN * KEY_WARPS;  // keys of one CTA tile
@@ -122,11 +123,11 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     const int tile_pos_min = pos0 + tok_first;
     const int tile_lo_max = p.window > 0 ? max(0, pos0 + tok_last - p.window + 1) : 0;
     const int tile_first = key_lo / BNC, tile_last = key_hi / BNC;
-    // a split of the small shape takes at least SMALL_MIN_TILES tiles, so contexts up to that many tiles are not
+    // a split of the small shape takes at least SMALL_MIN_KEYS keys, so contexts up to that many keys are not
     // split however many splits the grid has (merging splits costs more than a few more tiles in a row); splits
     // beyond the last active one do nothing
     const int n_tiles = tile_last - tile_first + 1;
-    const int per_split = max(SMALL ? SMALL_MIN_TILES : 1, (n_tiles + p.splits - 1) / p.splits);
+    const int per_split = max(SMALL ? (SMALL_MIN_KEYS + BNC - 1) / BNC : 1, (n_tiles + p.splits - 1) / p.splits);
     const int active_splits = (n_tiles + per_split - 1) / per_split;
     const int t_begin = tile_first + split * per_split;
     const int t_end = min(tile_last + 1, t_begin + per_split);
@@ -184,7 +185,9 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     // writes; the queries and the step's own keys come from the kernels before this one
     if (use_pdl) {
         pdl_trigger();
+        TL(if (marks) marks->mark(1);)
         pdl_wait();
+        TL(if (marks) marks->mark(2);)
     }
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
@@ -312,6 +315,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     }
     cp_async_wait<0>();
     cta_sync<THREADS>();  // the ring is free (the small shape merges its warps through it)
+    TL(if (marks) marks->mark(3);)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);

@@ -38,8 +38,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
     TL(tl::Marks marks;)
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [WARPS][SLOTS][SLOT_ELEMS]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)WARPS * SLOTS * SLOT_ELEMS * 2);  // [tiles of a team][WARPS][MT * 4][32]
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [warps that have tiles][slots][SLOT_ELEMS]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)p.ring_warps * p.slots * SLOT_ELEMS * 2);  // [tiles of a team][WARPS][MT * 4][32]
     __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(red + p.red_floats);  // [8 MT][K + X_PAD]
     __shared__ float row_scale[8 * MT];
     __shared__ __align__(8) unsigned long long full[WARPS][SLOTS];
@@ -51,7 +51,7 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
         if (warp == 0) tma::prefetch_map(&wmap);
     }
     __syncwarp();
-    __nv_bfloat16* my_ring = ring + (size_t)warp * SLOTS * SLOT_ELEMS;
+    __nv_bfloat16* my_ring = ring + (size_t)warp * p.slots * SLOT_ELEMS;
     StreamState st;
     // the weights do not depend on what ran before: their first boxes are asked for at once, while the
     // kernel before this one may still be running; everything else waits for it
@@ -106,22 +106,45 @@ constexpr size_t SMEM_LIMIT = 227 * 1024;
 template <int MT, int MODE, typename TO>
 int launch(const LinearParams& p, cudaStream_t stream) {
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
-    const int tiles = (p.N + FEATURES - 1) / FEATURES;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
+    const int tiles = (p.N + FEATURES - 1) / FEATURES, kblocks = (p.K + BOXK - 1) / BOXK, sms = sm_count();
+    int grid = tiles < sms ? tiles : sms;
     LinearParams q = p;
     TL(static int tl_launches = 0; q.tl_launch = tl_launches++;)
-    const size_t fixed = (size_t)WARPS * SLOTS * SLOT_ELEMS * 2 + (size_t)8 * MT * (p.K + X_PAD) * 2;
-    if (fixed > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;  // x does not fit beside the rings
-    // as many tiles of a team may be shared as their partial sums find room for
-    const int room = (int)((SMEM_LIMIT - fixed) / ((size_t)WARPS * MT * 4 * 32 * sizeof(float)));
-    q.group = choose_group(tiles, (p.K + BOXK - 1) / BOXK, grid, room);
+    const size_t x_bytes = (size_t)8 * MT * (p.K + X_PAD) * 2;
+    auto ring_bytes = [](int slots, int warps = WARPS) { return (size_t)warps * slots * SLOT_ELEMS * 2; };
+    // A product of a few more tiles than SMs whose k is short (the stacked projection of a small model): one tile per
+    // CTA, shared by its eight warps, on as many CTAs as tiles.  Each CTA then needs two boxes per warp, two such
+    // CTAs fit an SM, and none has twice the work of the others.
+    const size_t pair_limit = (SMEM_LIMIT + 1024) / 2 - 1024;
+    const bool one_each = MT == 1 && tiles > sms && tiles <= 2 * sms && (kblocks + WARPS - 1) / WARPS <= 2 &&
+                          ring_bytes(2) + x_bytes + (size_t)WARPS * MT * 4 * 32 * sizeof(float) <= pair_limit;
+    if (one_each) {
+        grid = tiles;
+        q.group = WARPS;
+    } else {
+        if (ring_bytes(SLOTS) + x_bytes > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;  // x does not fit beside the rings
+        // as many tiles of a team may be shared as their partial sums find room for
+        const int room = (int)((SMEM_LIMIT - ring_bytes(SLOTS) - x_bytes) / ((size_t)WARPS * MT * 4 * 32 * sizeof(float)));
+        q.group = choose_group(tiles, kblocks, grid, room);
+    }
+    // a warp that never has more than two boxes needs no more than two slots: the CTA is then small enough for the
+    // CTA of the kernel behind it (launched early) to sit beside it and do what it can before its turn
+    const int teams = grid * (WARPS / q.group);
+    const int boxes_each = ((tiles + teams - 1) / teams) * ((kblocks + q.group - 1) / q.group);
+    q.slots = boxes_each <= 2 ? 2 : SLOTS;
     q.red_floats = (int)red_floats(tiles, grid, q.group, MT);
-    const size_t smem = fixed + (size_t)q.red_floats * sizeof(float);
+    // rings only for the warps that have tiles (those of the teams j with j grid < tiles: the first warps of a CTA)
+    const int busy_teams = (tiles + grid - 1) / grid < WARPS / q.group ? (tiles + grid - 1) / grid : WARPS / q.group;
+    q.ring_warps = busy_teams * q.group;
+    const size_t smem = ring_bytes(q.slots, q.ring_warps) + x_bytes + (size_t)q.red_floats * sizeof(float);
+    if (smem > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;
     auto kernel = linear_decode_kernel<MT, MODE, TO>;
     static size_t configured = 0;  // per instantiation: the most dynamic shared memory asked for so far
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        // all of the SM's memory as shared memory whatever this launch needs, so that a CTA of the next kernel can join
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = smem;
     }
     const CUtensorMap* map = weight_map(p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, MODE == MODE_QKV ? 8 : FEATURES);

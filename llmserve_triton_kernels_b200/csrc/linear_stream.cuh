@@ -41,6 +41,8 @@ struct LinearParams {
     float* ss_out;          // MODE_RESIDUAL: [tiles of 16 features, M]
     int* error_flag;        // set to 1 if a wait for a copy gave up (host-visible memory), or null
     int group;              // warps that share a tile: 1, 2, 4 or 8
+    int slots;              // boxes of a warp's ring: 2 or 4 (a power of two)
+    int ring_warps;         // warps that have a ring: the first ones of the CTA, those whose teams have tiles
     int red_floats;         // floats of shared memory for the teams' partial sums (red_floats() below)
     // MODE_QKV: w rows are [H query heads | KV key heads | KV value heads] x D; out is [M, H * D]
     const int* positions;   // [M]
@@ -52,7 +54,8 @@ struct LinearParams {
     int tl_launch;          // profiling builds: which launch this is
 };
 
-constexpr int SLOTS = 4;   // boxes per warp, all in flight but for the moment in which one is read into registers
+constexpr int SLOTS = 4;   // most boxes per warp, all in flight but for the moment in which one is read into registers;
+                           // a product whose warps never have more than two boxes is given two (LinearParams::slots)
 constexpr int BOXK = 128;  // k per box: a slot is 16 rows x 128 k = 4 KB
 constexpr int SLOT_ELEMS = 16 * BOXK;
 constexpr int PIECES = BOXK / 32;
@@ -92,6 +95,7 @@ inline size_t red_floats(int tiles, int grid, int group, int MT) {
 
 struct StreamState {
     int group, member, tiles, kblocks, first, stride, my_tiles, units;
+    int slots, slots_log2;  // boxes of this warp's ring
     int a_ti, a_kb, armed;
     int mode, up_offset, D;  // what arm_next needs of the product: which rows a box takes
     unsigned base;  // boxes this warp's ring carried before this product
@@ -109,7 +113,7 @@ struct StreamState {
 // from the number of boxes the ring has carried, so a product's boxes may be asked for while the product before
 // it is still being computed.
 __device__ __forceinline__ void arm_next(StreamState& st, const CUtensorMap* wmap, __nv_bfloat16* my_ring, unsigned long long* my_full) {
-    const int tile = st.first + st.a_ti * st.stride, sl = (st.base + st.armed) % SLOTS;
+    const int tile = st.first + st.a_ti * st.stride, sl = (st.base + st.armed) & (st.slots - 1);
     __nv_bfloat16* dst = my_ring + (size_t)sl * SLOT_ELEMS;
     tma::mbar_expect_tx(&my_full[sl], (unsigned)(SLOT_ELEMS * 2));
     if (st.mode == MODE_SWIGLU) {  // the map's box is 8 rows: gate rows, then up rows
@@ -138,6 +142,8 @@ __device__ __forceinline__ void stream_plan(StreamState& st, const LinearParams&
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     st.group = p.group;
+    st.slots = p.slots;
+    st.slots_log2 = p.slots == 2 ? 1 : 2;
     st.member = warp % st.group;
     st.tiles = (p.N + FEATURES - 1) / FEATURES;
     st.kblocks = (p.K + BOXK - 1) / BOXK;
@@ -208,7 +214,7 @@ __device__ __forceinline__ void stream_fetch_resid(StreamState& st, const Linear
 __device__ __forceinline__ void stream_arm(StreamState& st, const CUtensorMap* wmap, __nv_bfloat16* my_ring, unsigned long long* my_full,
                                            int consumed) {
     if ((threadIdx.x & 31) == 0)
-        while (st.armed < st.units && st.armed < consumed + SLOTS) arm_next(st, wmap, my_ring, my_full);
+        while (st.armed < st.units && st.armed < consumed + st.slots) arm_next(st, wmap, my_ring, my_full);
 }
 
 template <int MODE, int MT = 1>
@@ -387,11 +393,12 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
 #pragma unroll
                 for (int e = 0; e < 4; ++e) part[t][c][e] = 0.f;
         for (int kb = member; kb < kblocks; kb += group, ++unit) {
-            if (!gave_up && !tma::mbar_wait(&my_full[(st.base + unit) % SLOTS], ((st.base + unit) / SLOTS) & 1)) {
+            const unsigned at = st.base + unit, sl = at & (unsigned)(st.slots - 1);
+            if (!gave_up && !tma::mbar_wait(&my_full[sl], (at >> st.slots_log2) & 1)) {
                 gave_up = true;
                 if (p.error_flag) atomicExch(p.error_flag, 1);
             }
-            const __nv_bfloat16* slot = my_ring + (size_t)((st.base + unit) % SLOTS) * SLOT_ELEMS + qc * 8;
+            const __nv_bfloat16* slot = my_ring + (size_t)sl * SLOT_ELEMS + qc * 8;
             const int k0 = kb * BOXK;
             uint4 a[PIECES][2], b[PIECES][MT];
 #pragma unroll
@@ -456,7 +463,8 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
     // nothing of this warp's is in flight: every armed unit was waited for above (after a failed wait, once
     // more here, bounded, so that no copy lands in shared memory after the CTA has left)
     if (gave_up && lane == 0)
-        for (unit = max(0, units - SLOTS); unit < units; ++unit) tma::mbar_wait(&my_full[(st.base + unit) % SLOTS], ((st.base + unit) / SLOTS) & 1);
+        for (unit = max(0, units - st.slots); unit < units; ++unit)
+            tma::mbar_wait(&my_full[(st.base + unit) & (unsigned)(st.slots - 1)], ((st.base + unit) >> st.slots_log2) & 1);
     return !gave_up;
 }
 
