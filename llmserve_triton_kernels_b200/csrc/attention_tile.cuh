@@ -365,17 +365,27 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
             }
         }
         cta_sync<THREADS>();
-        for (int idx = tid; idx < 16 * D; idx += THREADS) {
-            const int row = idx / D, d = idx - row * D;
-            if (row >= rows_total) continue;
+        // each row's weights of the warps' shares first (one thread per (row, warp): a few exponentials in all, not one per
+        // element), then the weighted sums, an element per thread, over the rows that exist only
+        float* f_sm = ml_sm + KEY_WARPS * 16 * 2;  // [16][KEY_WARPS] weight of a warp's share; then [16] max, [16] sum
+        float* row_m = f_sm + 16 * KEY_WARPS;
+        float* row_l = row_m + 16;
+        for (int idx = tid; idx < rows_total * KEY_WARPS; idx += THREADS) {
+            const int row = idx / KEY_WARPS, w = idx - row * KEY_WARPS;
             float m = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < KEY_WARPS; ++w) m = fmaxf(m, ml_sm[(w * 16 + row) * 2]);
+            for (int w2 = 0; w2 < KEY_WARPS; ++w2) m = fmaxf(m, ml_sm[(w2 * 16 + row) * 2]);
             const float m_use = m == -INFINITY ? 0.f : m;
+            f_sm[row * KEY_WARPS + w] = exp2f(ml_sm[(w * 16 + row) * 2] - m_use);
+            if (w == 0) row_m[row] = m;
+        }
+        cta_sync<THREADS>();
+        for (int idx = tid; idx < rows_total * D; idx += THREADS) {
+            const int row = idx / D, d = idx - row * D;
             float o = 0.f, l = 0.f;
 #pragma unroll
-            for (int w = 0; w < KEY_WARPS; ++w) {
-                const float f = exp2f(ml_sm[(w * 16 + row) * 2] - m_use);
+            for (int w = 0; w < KEY_WARPS; ++w) {  // a fixed order
+                const float f = f_sm[row * KEY_WARPS + w];
                 o += o_sm[(w * 16 + row) * D + d] * f;
                 l += ml_sm[(w * 16 + row) * 2 + 1] * f;
             }
@@ -386,7 +396,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
                 const size_t slot = ((size_t)(q_begin + tok) * p.H + head) * p.splits + split;
                 p.part_o[slot * D + d] = o;
                 if (d == 0) {
-                    p.part_ml[slot * 2] = m;
+                    p.part_ml[slot * 2] = row_m[row];
                     p.part_ml[slot * 2 + 1] = l;
                 }
             }

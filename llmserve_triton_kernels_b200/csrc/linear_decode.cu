@@ -66,7 +66,7 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
     TL(marks.mark(3);)
     if (!stream_run<MT, MODE, TO>(st, p, &wmap, my_ring, full[warp], red, x_s, row_scale) && lane == 0 && p.error_flag)
         atomicExch(p.error_flag, 1);
-    TL(__syncthreads(); if (threadIdx.x == 0) { marks.mark(4); marks.write(MODE, p.tl_launch, blockIdx.x, p.N, p.K); })
+    TL(__syncthreads(); if (threadIdx.x == 0) { marks.mark(4); marks.t[1] = ((unsigned long long)(unsigned)st.tl_sec[0] << 48) | ((unsigned long long)(unsigned)(st.tl_sec[1] & 0xffff) << 32) | ((unsigned long long)(unsigned)(st.tl_sec[2] & 0xffff) << 16) | (unsigned)(st.tl_sec[3] & 0xffff); marks.t[3] = (marks.t[3] & ~0xffull) | (unsigned)st.tl_sec[4]; marks.t[5] = ((unsigned long long)(unsigned)st.tl_loop << 40) | ((unsigned long long)(unsigned)st.tl_sync << 20) | (unsigned)st.tl_all; marks.write(MODE, p.tl_launch, blockIdx.x, p.N, p.K); })
 }
 
 int sm_count() {

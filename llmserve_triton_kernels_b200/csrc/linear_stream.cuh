@@ -96,6 +96,8 @@ inline size_t red_floats(int tiles, int grid, int group, int MT) {
 struct StreamState {
     int group, member, tiles, kblocks, first, stride, my_tiles, units;
     int slots, slots_log2;  // boxes of this warp's ring
+    int tl_sec[5];
+    int tl_loop, tl_sync, tl_all;  // profiling builds: cycles from the start of stream_run to the end of the boxes, of the team's meeting, of all
     int a_ti, a_kb, armed;
     int mode, up_offset, D;  // what arm_next needs of the product: which rows a box takes
     unsigned base;  // boxes this warp's ring carried before this product
@@ -382,6 +384,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
     };
 
     int unit = 0;
+    TL(const long long tl0 = clock64(); long long tl_loop = 0, tl_sync = 0, tl_w = 0, tl_l = 0, tl_a = 0, tl_m = 0; int tl_n = 0, tl_dummy = 0;)
     for (int ti = 0; ti < my_tiles; ++ti) {
         // CHAINS independent sums per token tile, joined when the tile is complete: an MMA waits for the one before it
         // on the same accumulator, and one chain of eight per box would leave the tensor pipe idle most of the time
@@ -394,10 +397,12 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 for (int e = 0; e < 4; ++e) part[t][c][e] = 0.f;
         for (int kb = member; kb < kblocks; kb += group, ++unit) {
             const unsigned at = st.base + unit, sl = at & (unsigned)(st.slots - 1);
+            TL(const long long c0 = clock64();)
             if (!gave_up && !tma::mbar_wait(&my_full[sl], (at >> st.slots_log2) & 1)) {
                 gave_up = true;
                 if (p.error_flag) atomicExch(p.error_flag, 1);
             }
+            TL(const long long c1 = clock64(); tl_w += c1 - c0;)
             const __nv_bfloat16* slot = my_ring + (size_t)sl * SLOT_ELEMS + qc * 8;
             const int k0 = kb * BOXK;
             uint4 a[PIECES][2], b[PIECES][MT];
@@ -412,7 +417,9 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     b[i][t] = have ? *reinterpret_cast<const uint4*>(xrow[t] + k0 + i * 32) : make_uint4(0, 0, 0, 0);
             }
             __syncwarp();  // every lane holds its pieces of the slot in registers: the slot takes the next box
+            TL(if (a[PIECES - 1][1].w == 0x7fc12345u && b[PIECES - 1][0].w == 0x7fc12345u) ++tl_dummy; const long long c2 = clock64(); tl_l += c2 - c1;)
             if (lane == 0 && st.armed < units) arm_next(st, wmap, my_ring, my_full);
+            TL(__syncwarp(); const long long c3 = clock64(); tl_a += c3 - c2;)
 #pragma unroll
             for (int i = 0; i < PIECES; ++i)
 #pragma unroll
@@ -420,6 +427,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     mma_bf16(part[t][(2 * i) % CHAINS], a[i][0].x, a[i][1].x, a[i][0].y, a[i][1].y, b[i][t].x, b[i][t].y);
                     mma_bf16(part[t][(2 * i + 1) % CHAINS], a[i][0].z, a[i][1].z, a[i][0].w, a[i][1].w, b[i][t].z, b[i][t].w);
                 }
+            TL(if (part[0][0][0] + part[0][1][0] + part[0][CHAINS - 1][0] == -1.2345e30f) ++tl_dummy; tl_m += clock64() - c3; ++tl_n;)
         }
         float acc[MT][4];
 #pragma unroll
@@ -442,8 +450,10 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 for (int e = 0; e < 4; ++e) red[(((size_t)ti * WARPS + warp) * (MT * 4) + t * 4 + e) * 32 + lane] = acc[t][e];
         }
     }
+    TL(tl_loop = clock64() - tl0;)
     if (group > 1) {
         asm volatile("bar.sync %0, %1;\n" ::"r"(1 + warp / group), "r"(group * 32) : "memory");
+        TL(tl_sync = clock64() - tl0;)
         if (member == 0) {
             for (int ti = 0; ti < my_tiles; ++ti) {
                 float acc[MT][4];
@@ -465,6 +475,8 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
     if (gave_up && lane == 0)
         for (unit = max(0, units - st.slots); unit < units; ++unit)
             tma::mbar_wait(&my_full[(st.base + unit) & (unsigned)(st.slots - 1)], ((st.base + unit) >> st.slots_log2) & 1);
+    TL(if (threadIdx.x == 0) { st.tl_loop = (int)tl_loop; st.tl_sync = (int)tl_sync; st.tl_all = (int)(clock64() - tl0) + (tl_dummy & 1);
+       st.tl_sec[0] = (int)tl_w; st.tl_sec[1] = (int)tl_l; st.tl_sec[2] = (int)tl_a; st.tl_sec[3] = (int)tl_m; st.tl_sec[4] = tl_n; })
     return !gave_up;
 }
 
