@@ -1,15 +1,19 @@
-"""Decode steps as CUDA graphs.
+"""Steps as CUDA graphs.
 
-A step in which every request brings exactly one token and wants its logits has the same
-shapes every time, so the whole pass — some hundred and fifty launches for 22 layers — is
-captured once per batch size and replayed.  Only the step's integer arrays change: they are
-written into a pinned buffer of fixed layout and brought to the device in one piece before the
-replay.  The reference notes launch and host overhead as its next bottleneck and CUDA graphs as
-the cure (its docs/PROFILING.md:19-20 and the closing notes of its design document) but does not build them.
+A step whose shape has been seen before — how many tokens each request brings and which of them want
+logits — launches the same kernels with the same grids every time, so the whole pass (some hundred and
+fifty launches for 22 layers) is captured once per shape and replayed.  Only the step's integer arrays
+change: they are written into a pinned buffer of fixed layout and brought to the device in one piece
+before the replay.  Decode steps (one token per request) are captured at their first occurrence; other
+shapes (a prompt of 512 tokens, eight of them side by side, a portion beside decoded tokens) at their
+second, and the least recently used are dropped beyond a limit.  The reference notes launch and host
+overhead as its next bottleneck and CUDA graphs as the cure (its docs/PROFILING.md:19-20 and the closing
+notes of its design document) but does not build them.
 
 Page tables have the model's full width in a graph (``ceil(max_positions / page_size)``), and
-``StepContext.max_context_len`` is the model's limit, so no launch depends on how long the
-requests are at the time.
+``StepContext.max_context_len`` is the model's limit, so no launch depends on how long the requests
+are at the time.  The graphs of one step function share one memory pool: they never run at the same
+time, and what one keeps between replays (its logits) is never freed.
 """
 
 from __future__ import annotations
@@ -25,33 +29,49 @@ def _pad4(n: int) -> int:
     return -(-n // 4) * 4
 
 
-class DecodeGraph:
-    def __init__(self, model, cache, num_requests: int):
-        self.model, self.cache, self.R = model, cache, int(num_requests)
-        R = self.R
+class StepGraph:
+    def __init__(self, model, cache, counts: tuple[int, ...], wants: tuple[tuple[int, ...], ...], owner=None):
+        """``counts[r]``: tokens that request r of the step brings; ``wants[r]``: the places among them whose
+        logits are returned.  ``owner``: whoever keeps the graphs (an object with an attribute ``graph_pool``): the
+        graphs of one owner share one memory pool, that of the first one captured."""
+        self.model, self.cache, self.owner = model, cache, owner
+        self.counts, self.wants = tuple(counts), tuple(tuple(w) for w in wants)
+        R, N = len(self.counts), sum(self.counts)
+        self.R, self.N = R, N
+        cu = np.zeros(R + 1, dtype=np.int32)
+        cu[1:] = np.cumsum(self.counts)
+        rows = [int(cu[r]) + w for r, want in enumerate(self.wants) for w in want]
+        for r, want in enumerate(self.wants):
+            for w in want:
+                if not 0 <= w < self.counts[r]:
+                    raise ValueError(f"place {w} is wanted among {self.counts[r]} tokens")
+        P = len(rows)
         self.widths = [-(-model.plan.max_positions // g.page_size) for g in cache.groups]
-        sizes = [R, R, R, R + 1, R, R, R]  # ids, positions, token_request, cu, ctx_lens, logit_rows, state_slots
+        sizes = [N, N, N, R + 1, R, P, R]  # ids, positions, token_request, cu, ctx_lens, logit_rows, state_slots
         for w in self.widths:
-            sizes += [R * w, R]
+            sizes += [R * w, N]
         self.offsets = np.concatenate(([0], np.cumsum([_pad4(s) for s in sizes]))).tolist()
         self.sizes = sizes
         total = self.offsets[-1]
         self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(total, dtype=torch.int32, device=cache.device)
-        self._piece_np(2)[:] = np.arange(R)
-        self._piece_np(3)[:] = np.arange(R + 1)
-        self._piece_np(5)[:] = np.arange(R)
+        self._counts_np = np.asarray(self.counts, dtype=np.int64)
+        self._within = np.arange(N, dtype=np.int64) - np.repeat(cu[:-1].astype(np.int64), self._counts_np)
+        self._piece_np(2)[:] = np.repeat(np.arange(R, dtype=np.int32), self._counts_np)
+        self._piece_np(3)[:] = cu
+        self._piece_np(5)[:] = rows
         self.copied = torch.cuda.Event()
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
         self.launches = 0
+        self.decode_only = all(c == 1 for c in self.counts) and all(w == (0,) for w in self.wants)
         d = self._piece
         self.ctx = StepContext(
-            num_tokens=R, num_requests=R, num_logits=R,
+            num_tokens=N, num_requests=R, num_logits=P,
             token_ids=d(0), positions=d(1), token_request=d(2), cu_tokens=d(3), context_lens=d(4), logit_rows=d(5),
-            state_slots=d(6), host_cu_tokens=list(range(R + 1)), host_context_lens=None, host_state_slots=None,
-            max_query_len=1, max_context_len=model.plan.max_positions, static_decode=True,
+            state_slots=d(6), host_cu_tokens=cu.tolist(), host_context_lens=None, host_state_slots=None,
+            max_query_len=max(self.counts), max_context_len=model.plan.max_positions, static_decode=self.decode_only,
         )
         group_tensors = []
         for g, w in enumerate(self.widths):
@@ -66,15 +86,17 @@ class DecodeGraph:
         return self.host_np[self.offsets[i] : self.offsets[i] + self.sizes[i]]
 
     def fill(self, tokens, lengths: list[int], state_slots: np.ndarray, group_arrays) -> None:
-        """Write the step's arrays into the pinned buffer and start their copy to the device.  ``tokens``: a list
-        of ids on the host, or an int32 tensor ``[R]`` on the device (the step before has put its choices there and
-        the host has not seen them yet), which takes the place of the host's token ids on the way."""
+        """Write the step's arrays into the pinned buffer and start their way to the device.  ``tokens``: the ids
+        of all requests end to end on the host, or (decode steps) an int32 tensor ``[R]`` on the device (the step
+        before has put its choices there and the host has not seen them yet), which takes the place of the host's
+        token ids on the way.  ``lengths[r]``: what request r held before the step."""
         self.copied.synchronize()  # the previous copy has left the pinned buffer
         R = self.R
         on_device = isinstance(tokens, torch.Tensor)
+        starts = np.asarray(lengths, dtype=np.int64)
         self._piece_np(0)[:] = 0 if on_device else tokens
-        self._piece_np(1)[:] = lengths
-        self._piece_np(4)[:] = np.asarray(lengths, dtype=np.int32) + 1
+        self._piece_np(1)[:] = np.repeat(starts, self._counts_np) + self._within
+        self._piece_np(4)[:] = starts + self._counts_np
         self._piece_np(6)[:] = state_slots
         for g, (table, slot_map) in enumerate(group_arrays):
             dst = self._piece_np(7 + 2 * g).reshape(R, self.widths[g])
@@ -86,11 +108,11 @@ class DecodeGraph:
         self.copied.record()
 
     def run(self) -> torch.Tensor:
-        """Logits ``[R, vocab]`` of the step whose arrays were filled last.  The tensor is the graph's own from the
-        second call on: the next replay overwrites it.  The first call runs the step once, kernel by kernel (which
-        also sets up libraries and kernel attributes, as must happen outside a capture), hands out that pass's
-        logits and then only records the graph, which executes nothing: no step runs twice, so a part that keeps
-        state of its own need not be idempotent to be captured."""
+        """Logits ``[wanted places, vocab]`` of the step whose arrays were filled last.  The tensor is the graph's
+        own from the second call on: the next replay overwrites it.  The first call runs the step once, kernel by
+        kernel (which also sets up libraries and kernel attributes, as must happen outside a capture), hands out
+        that pass's logits and then only records the graph, which executes nothing: no step runs twice, so a part
+        that keeps state of its own need not be idempotent to be captured."""
         if self.graph is None:
             return self._first_run_and_capture()
         self.graph.replay()
@@ -107,9 +129,19 @@ class DecodeGraph:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(graph):
+        pool = getattr(self.owner, "graph_pool", None)
+        with torch.cuda.graph(graph, pool=pool):
             self.logits = self.model.forward(self.ctx, self.views)
+        if self.owner is not None and pool is None:
+            self.owner.graph_pool = graph.pool()
         self.launches = ops.launch_count() - before
         ops.add_launches(-self.launches)  # a capture launches nothing
         self.graph = graph
         return first
+
+
+class DecodeGraph(StepGraph):
+    """The graph of a decode step of ``num_requests`` requests: one token each, its logits wanted."""
+
+    def __init__(self, model, cache, num_requests: int, owner=None):
+        super().__init__(model, cache, (1,) * int(num_requests), ((0,),) * int(num_requests), owner)

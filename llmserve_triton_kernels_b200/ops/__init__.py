@@ -9,6 +9,7 @@ a CUDA device, or if the library cannot be built and loaded, the first call rais
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 
 import torch
@@ -305,9 +306,9 @@ def _decode_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):
 
 def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x [M, K] @ w [N, K]^T -> [M, N]``.  float32 operands run on the CUDA cores in true 32-bit
-    (fixed summation order); bfloat16 operands accumulate in 32-bit on the tensor cores: few rows
-    through the weight-streaming kernel, many through the vendor's library.  ``x`` may be a
-    :class:`NormedInput`."""
+    (fixed summation order); bfloat16 operands accumulate in 32-bit on the tensor cores: up to 16 rows
+    through the weight-streaming kernel, more through the vendor's library (or, where ``_GEMM_POLICY`` says so,
+    the own tcgen05 kernel from 128 rows on).  ``x`` may be a :class:`NormedInput`."""
     if isinstance(x, NormedInput):
         if x.shape[0] >= _TCGEN05_MIN_ROWS:
             out = _tcgen05_linear(x, w, out_dtype or x.dtype, 0, w.shape[0])
@@ -330,14 +331,36 @@ def linear(x, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Te
         out = _decode_linear(x, w, out_dtype, 0, n)
         if out is not None:
             return out
-    if m >= _TCGEN05_MIN_ROWS:
+    if m >= _TCGEN05_MIN_ROWS and not _library_is_faster("plain", m):
         out = _tcgen05_linear(x, w, out_dtype, 0, n)
         if out is not None:
             return out
+    return _library_linear(x, w, out_dtype)
+
+
+# Which of two ways a bfloat16 product of many rows takes: the own tcgen05 kernel or the vendor's library (as the
+# reference's F.linear).  Measured on a B200 in graphs of back-to-back products of one shape (hidden 2048, feed-forward
+# 5632; own / library in microseconds): 128 rows 13.9 / 5.3 (stacked projection), 30.8 / 9.5 (down); 2,048 rows 28.7 /
+# 17.6, 17.0 / 14.5 (output), 36.2 / 31.8; 8,192 rows 87.8 / 58.6, 189.6 / 129.9: the library's tiles of 256 rows over
+# two SMs need half the operand traffic per SM of the own kernel's 128-row tiles, and it splits small grids along k.
+# Gate and up with SwiGLU in the product's end, against the library's product and an activation kernel: 52 / 45 at 1,024
+# rows, 55 / 62 at 1,536, 72 / 85 at 2,048, 285 / 315 at 8,192.  So "auto" gives plain products to the library and the
+# gated one to the own kernel from _SWIGLU_OWN_MIN_ROWS rows on; "own" and "library" force one way (also through the
+# environment variable LLMSERVE_B200_GEMM; the tests run the own kernel at every shape).
+_GEMM_POLICY = os.environ.get("LLMSERVE_B200_GEMM", "auto")
+_SWIGLU_OWN_MIN_ROWS = 1536
+
+
+def _library_is_faster(kind: str, m: int) -> bool:
+    if _GEMM_POLICY != "auto":
+        return _GEMM_POLICY == "library"
+    return kind == "plain" or m < _SWIGLU_OWN_MIN_ROWS
+
+
+def _library_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     library()  # the engine never runs without its kernels, even where a matrix product is the vendor's
-    if out_dtype == torch.bfloat16:
-        return torch.matmul(x, w.t())
-    return torch.matmul(x, w.t()).to(out_dtype)
+    out = torch.matmul(x, w.t())
+    return out if out_dtype == torch.bfloat16 else out.to(out_dtype)
 
 
 def _tcgen05_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):
@@ -413,9 +436,13 @@ def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
         if out is not None:
             return out
     if xt.dtype == torch.bfloat16 and xt.shape[0] >= _TCGEN05_MIN_ROWS:
-        out = _tcgen05_linear(x, w_gate_up, torch.bfloat16, 1, inter, up_offset=inter)
-        if out is not None:
-            return out
+        scaled = isinstance(x, NormedInput)  # the factored form goes the own way: the library knows nothing of it
+        if scaled or not _library_is_faster("swiglu", xt.shape[0]):
+            out = _tcgen05_linear(x, w_gate_up, torch.bfloat16, 1, inter, up_offset=inter)
+            if out is not None:
+                return out
+        if not scaled:
+            return swiglu(_library_linear(x, w_gate_up, torch.bfloat16))
     return swiglu(linear(x, w_gate_up))
 
 

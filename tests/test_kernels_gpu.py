@@ -88,7 +88,11 @@ def test_linear_float32_is_true_32_bit_and_row_independent(m, n, k):
      (1000, 3000, 1096)],
 )
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_linear_bfloat16(m, n, k, out_dtype):
+@pytest.mark.parametrize("policy", ["own", "auto"])
+def test_linear_bfloat16(m, n, k, out_dtype, policy, monkeypatch):
+    """``own``: products of 128 rows and more on the tcgen05 kernel; ``auto``: as in serving (plain products of more
+    than 16 rows are the library's)."""
+    monkeypatch.setattr(ops(), "_GEMM_POLICY", policy)
     x, w = rnd(m, k, dtype=torch.bfloat16, seed=7), rnd(n, k, dtype=torch.bfloat16, seed=8, std=0.05)
     got = ops().linear(x, w, out_dtype=out_dtype)
     assert got.dtype == out_dtype
@@ -99,7 +103,9 @@ def test_linear_bfloat16(m, n, k, out_dtype):
 @pytest.mark.parametrize("m,inter,k", [(1, 5632, 2048), (8, 172 * 8, 64), (16, 100, 96), (5, 16, 8), (17, 100, 96), (300, 5632, 2048),
                                        (129, 200, 72), (2048, 1000, 256), (64, 5632, 2048), (127, 172 * 8, 64), (33, 100, 96),
                                        (50, 102, 104)])
-def test_linear_swiglu_fused_for_few_rows(m, inter, k):
+@pytest.mark.parametrize("policy", ["own", "auto"])
+def test_linear_swiglu_fused_for_few_rows(m, inter, k, policy, monkeypatch):
+    monkeypatch.setattr(ops(), "_GEMM_POLICY", policy)
     x = rnd(m, k, dtype=torch.bfloat16, seed=31)
     w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=32, std=0.05)
     got = ops().linear_swiglu(x, w)
