@@ -400,22 +400,30 @@ class Scheduler:
 
         if self.policy == "static" and self.running:
             return plan
-        reserved = sum(self.cache.extra_pages_needed(r.req_id, n) for r, n in plan)
+        # Admission counts pages as the reference does, for the whole of what a request has to feed (its engine runs
+        # whole prompts: src/llmserve/scheduler/engine.py:220-225), although here they are taken portion by portion:
+        # what the running requests still need for their known tokens is spoken for.  A request that was admitted when
+        # its first portion fitted would otherwise run out of pages halfway, be put back and computed again, over and over.
+        spoken_for = sum(self._pages_still_needed(r) for r in self.running)
         while self.waiting and len(self.running) < self.max_batch_size and budget > 0:
             req = self.waiting[0]
             n = self._portion(req, budget)
-            need = self.cache.pages_for(n)
+            need = min(self.cache.pages_for(req.num_ids), self.cache.peak_pages_for(req.num_ids, min(self.chunk_size, self.max_num_batched_tokens)))
             headroom = len(self.running)  # one spare page per live request, so the next decode cannot starve
-            if self.cache.num_free_pages - reserved - need < headroom:
+            if self.cache.num_free_pages - spoken_for - need < headroom:
                 break
             self.waiting.popleft()
             self.cache.add_request(req.req_id)
             req.status = Status.RUNNING
             self.running.append(req)
             plan.append((req, n))
-            reserved += need
+            spoken_for += need
             budget -= n
         return plan
+
+    def _pages_still_needed(self, req: Request) -> int:
+        """Pages that a running request has yet to take for the tokens it is known to hold (the rest of its prompt)."""
+        return self.cache.extra_pages_needed(req.req_id, req.num_ids - req.num_computed) if req.num_ids > req.num_computed else 0
 
     def _preempt(self, req: Request) -> None:
         self._leave(req, "preempt")

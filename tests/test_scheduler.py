@@ -276,3 +276,23 @@ def test_a_kernel_that_reports_a_failed_wait_stops_the_engine(model_folder, plai
     with pytest.raises(ops.KernelError):
         sched.step()
     assert not sched.has_unfinished() and llm.cache.num_free_pages == llm.cache.num_pages
+
+
+def test_admission_speaks_for_the_pages_of_the_whole_prompt(model_folder, plain_ops_engine):
+    """Prompts are fed in portions, but a request is admitted only if the pages of ALL it has to feed are there beside
+    what the running requests still need (the reference admits whole prompts: engine.py:220-225).  Three prompts of 40
+    tokens (10 pages each) over 24 pages: two run, the third waits for one of them to end; nobody is put back.  Admitted
+    by its first portion alone, the third would take pages that the others need and all three would be computed again
+    and again."""
+    llm, plain = make(model_folder, block_size=4, num_blocks=24, max_batch_size=3, max_num_batched_tokens=16, chunk_size=8)
+    sched = llm.scheduler
+    prompts = tiny_configs.seeded_tokens(256, [40, 40, 40], 21)
+    ids = [sched.add_request(p, SamplingParams(max_new_tokens=4)) for p in prompts]
+    most_running = 0
+    while sched.has_unfinished():
+        sched.step()
+        most_running = max(most_running, len(sched.running))
+    assert most_running == 2 and sched.stats.preemptions == 0
+    for rid, prompt in zip(ids, prompts):
+        assert sched.finished[rid].generated == plain_tokens(plain, prompt, 4)
+    assert llm.cache.num_free_pages == llm.cache.num_pages
