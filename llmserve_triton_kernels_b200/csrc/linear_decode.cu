@@ -37,7 +37,8 @@ template <int MT, int MODE, typename TO>
 __global__ void __launch_bounds__(THREADS, 1)
 linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
     TL(tl::Marks marks;)
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+    extern __shared__ __align__(1024) unsigned char smem_all[];
+    unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_all + 1023) & ~(uintptr_t)1023);  // the swizzle's period
     __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [warps that have tiles][slots][SLOT_ELEMS]
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)p.ring_warps * p.slots * SLOT_ELEMS * 2);  // [tiles of a team][WARPS][MT * 4][32]
     __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(red + p.red_floats);  // [8 MT][K + X_PAD]
@@ -97,7 +98,7 @@ const CUtensorMap* weight_map(const void* w, int rows, int K, int box_rows) {
     auto it = maps.find(Key{w, rows, K, box_rows});
     if (it != maps.end()) return &it->second;
     CUtensorMap map;
-    if (!tma::make_map_2d_bf16(&map, w, rows, K, K, box_rows, BOXK, CU_TENSOR_MAP_SWIZZLE_NONE)) return nullptr;
+    if (!tma::make_map_row_pieces_bf16(&map, w, rows, K, box_rows)) return nullptr;
     return &maps.emplace(Key{w, rows, K, box_rows}, map).first->second;
 }
 
@@ -136,7 +137,7 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     // rings only for the warps that have tiles (those of the teams j with j grid < tiles: the first warps of a CTA)
     const int busy_teams = (tiles + grid - 1) / grid < WARPS / q.group ? (tiles + grid - 1) / grid : WARPS / q.group;
     q.ring_warps = busy_teams * q.group;
-    const size_t smem = ring_bytes(q.slots, q.ring_warps) + x_bytes + (size_t)q.red_floats * sizeof(float);
+    const size_t smem = ring_bytes(q.slots, q.ring_warps) + x_bytes + (size_t)q.red_floats * sizeof(float) + 1024;  // and room to align
     if (smem > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;
     auto kernel = linear_decode_kernel<MT, MODE, TO>;
     static size_t configured = 0;  // per instantiation: the most dynamic shared memory asked for so far
@@ -180,7 +181,7 @@ LLM_EXPORT int llm_linear_decode_parts(int N) { return (N + 15) / 16; }
 //   mode 2: resid [M, N] += product; xw_out [M, N] = resid * norm_w; ss_out [parts(N), M] = partial sums
 //           of resid^2.  out is not used.
 // in_ss (or null): [in_parts, M] partial sums of squares; the product is scaled by
-// rsqrt(sum / K + in_eps) per row.  Needs M <= 16, K a multiple of 8, 16-byte aligned rows;
+// rsqrt(sum / K + in_eps) per row.  Needs M <= 16, K a multiple of 64 (the weights travel in pieces of 64 k), 16-byte aligned rows;
 // otherwise it returns LLM_ERR_UNSUPPORTED and the caller takes another route.  error_flag (host-visible
 // int, or null) is set to 1 if a bounded wait inside the kernel ever gives up.
 LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int ldx,
@@ -188,7 +189,7 @@ LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int ou
                                  float* resid, const float* norm_w, void* xw_out, float* ss_out, int* error_flag,
                                  cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 16 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return LLM_ERR_UNSUPPORTED;
+    if (M > 16 || K < 64 || (K & 63) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return LLM_ERR_UNSUPPORTED;
     LinearParams p = {};
     p.x = (const __nv_bfloat16*)x;
     p.w = (const __nv_bfloat16*)w;
@@ -224,13 +225,13 @@ LLM_EXPORT int llm_linear_decode(const void* x, const void* w, void* out, int ou
 // bfloat16 x [M, K] times the stacked projection w [(H + 2 KV) D, K]: query heads, rotated by each token's
 // row of `rotary` ([positions, D] = cos | sin halves; null: no rotation), go to q_out [M, H D]; key heads,
 // rotated, and value heads go into `pool` [pages, 2, KV, page_size, D] at slot_map[m].  KV = 0: w holds
-// query heads only and nothing is written to the pool.  Needs M <= 16, K and D multiples of 8 and 16.
+// query heads only and nothing is written to the pool.  Needs M <= 16, K and D multiples of 64 and 16.
 LLM_EXPORT int llm_linear_decode_qkv(const void* x, const void* w, void* q_out, int M, int K, int ldx, const float* in_ss,
                                      int in_parts, float in_eps, const int* positions, const float* rotary, int rotary_rows,
                                      const int* slot_map, void* pool, int H, int KV, int D, int page_size, int* error_flag,
                                      cudaStream_t stream) {
     if (M <= 0) return 0;
-    if (M > 16 || K < 8 || (K & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || D < 16 || (D & 15) || H < 1 || KV < 0)
+    if (M > 16 || K < 64 || (K & 63) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || D < 16 || (D & 15) || H < 1 || KV < 0)
         return LLM_ERR_UNSUPPORTED;
     if (KV > 0 && (!slot_map || !pool || page_size < 1)) return LLM_ERR_BAD_ARGUMENT;
     if (rotary && (!positions || rotary_rows < 1)) return LLM_ERR_BAD_ARGUMENT;

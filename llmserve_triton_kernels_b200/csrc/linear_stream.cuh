@@ -26,6 +26,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Which row of a box (of eight, or of each eight of sixteen) holds the weights of MMA row g: rows g and g + 1 of the
+// MMA are read by the same quarter of a warp, and in the swizzled box rows r and r + 4 use different banks.  The
+// features of a tile are therefore numbered so: the thread that holds MMA row g holds feature feature_row(g).
+__device__ __forceinline__ int feature_row(int g) { return ((g & 1) << 2) | (g >> 1); }
+
 struct LinearParams {
     const __nv_bfloat16* x;
     const __nv_bfloat16* w;
@@ -118,15 +123,16 @@ __device__ __forceinline__ void arm_next(StreamState& st, const CUtensorMap* wma
     const int tile = st.first + st.a_ti * st.stride, sl = (st.base + st.armed) & (st.slots - 1);
     __nv_bfloat16* dst = my_ring + (size_t)sl * SLOT_ELEMS;
     tma::mbar_expect_tx(&my_full[sl], (unsigned)(SLOT_ELEMS * 2));
+    const int piece = st.a_kb * (BOXK / 64);  // the box's two 64-k pieces of its rows (see tma::make_map_row_pieces_bf16)
     if (st.mode == MODE_SWIGLU) {  // the map's box is 8 rows: gate rows, then up rows
-        tma::load_2d(dst, wmap, st.a_kb * BOXK, tile * 8, &my_full[sl]);
-        tma::load_2d(dst + 8 * BOXK, wmap, st.a_kb * BOXK, st.up_offset + tile * 8, &my_full[sl]);
+        tma::load_3d(dst, wmap, 0, tile * 8, piece, &my_full[sl]);
+        tma::load_3d(dst + 8 * BOXK, wmap, 0, st.up_offset + tile * 8, piece, &my_full[sl]);
     } else if (st.mode == MODE_QKV) {  // 8 lanes of a head's first half, then their partners in the second half
         const int per_head = st.D >> 4, head = tile / per_head, y = head * st.D + (tile - head * per_head) * 8;
-        tma::load_2d(dst, wmap, st.a_kb * BOXK, y, &my_full[sl]);
-        tma::load_2d(dst + 8 * BOXK, wmap, st.a_kb * BOXK, y + (st.D >> 1), &my_full[sl]);
+        tma::load_3d(dst, wmap, 0, y, piece, &my_full[sl]);
+        tma::load_3d(dst + 8 * BOXK, wmap, 0, y + (st.D >> 1), piece, &my_full[sl]);
     } else {
-        tma::load_2d(dst, wmap, st.a_kb * BOXK, tile * 16, &my_full[sl]);
+        tma::load_3d(dst, wmap, 0, tile * 16, piece, &my_full[sl]);
     }
     ++st.armed;
     st.a_kb += st.group;
@@ -164,7 +170,7 @@ __device__ __forceinline__ void stream_plan(StreamState& st, const LinearParams&
     st.early = false;
     st.have_resid = false;
     if (st.member == 0 && st.my_tiles > 0) {
-        const int qr = lane >> 2, qc = lane & 3, tile = st.first;
+        const int qr = feature_row(lane >> 2), qc = lane & 3, tile = st.first;
         if constexpr (MODE == MODE_QKV) {
             const int D = p.D, half = D >> 1, per_head = D >> 4;
             const int head = tile / per_head, j = (tile - head * per_head) * 8 + qr;
@@ -201,7 +207,7 @@ __device__ __forceinline__ void stream_plan(StreamState& st, const LinearParams&
 template <int MT>
 __device__ __forceinline__ void stream_fetch_resid(StreamState& st, const LinearParams& p) {
     if (st.member != 0 || st.my_tiles <= 0) return;
-    const int lane = threadIdx.x & 31, qr = lane >> 2, qc = lane & 3, n0 = st.first * 16;
+    const int lane = threadIdx.x & 31, qr = feature_row(lane >> 2), qc = lane & 3, n0 = st.first * 16;
 #pragma unroll
     for (int t = 0; t < MT; ++t)
 #pragma unroll
@@ -281,7 +287,8 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
     constexpr int CHAINS = MT == 1 ? 4 : 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qr = lane >> 2, qc = lane & 3;
+    const int qr = lane >> 2, qc = lane & 3;  // MMA row (a feature of the tile) and column pair (tokens) of this thread
+    const int fr = feature_row(qr);           // the feature of the tile that MMA row qr stands for
     const int M = p.M, N = p.N, K = p.K, x_pitch = K + X_PAD;
     const int group = st.group, member = st.member, kblocks = st.kblocks, first = st.first, stride = st.stride;
     const int my_tiles = st.my_tiles, units = st.units;
@@ -299,7 +306,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
         // a rotation pair.  Query heads go to `out` rotated, key heads rotated into their page, value heads as
         // they are into theirs.
         const int D = p.D, half = D >> 1, per_head = D >> 4;
-        const int head = tile / per_head, j = (tile - head * per_head) * 8 + qr;
+        const int head = tile / per_head, j = (tile - head * per_head) * 8 + fr;
 #pragma unroll
         for (int t = 0; t < MT; ++t)
 #pragma unroll
@@ -334,8 +341,8 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 dst[half] = __float2bfloat16_rn(b);
             }
     } else if constexpr (MODE == MODE_SWIGLU) {
-        // this thread: gate (e = 0, 1) and up (e = 2, 3) sums of feature qr for tokens 8 t + 2 qc and + 1
-        const int n = n0 + qr;
+        // this thread: gate (e = 0, 1) and up (e = 2, 3) sums of feature fr for tokens 8 t + 2 qc and + 1
+        const int n = n0 + fr;
 #pragma unroll
         for (int t = 0; t < MT; ++t)
 #pragma unroll
@@ -345,13 +352,13 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 if (m < M && n < N) reinterpret_cast<TO*>(p.out)[(size_t)m * p.ldo + n] = from_float<TO>(g / (1.f + expf(-g)) * u);
             }
     } else {
-        // this thread: features qr (e = 0, 1) and qr + 8 (e = 2, 3) of tokens 8 t + 2 qc and + 1
+        // this thread: features fr (e = 0, 1) and fr + 8 (e = 2, 3) of tokens 8 t + 2 qc and + 1
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
             float sq[2] = {0.f, 0.f};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int n = n0 + qr + 8 * (e >> 1), m = 8 * t + 2 * qc + (e & 1);
+                const int n = n0 + fr + 8 * (e >> 1), m = 8 * t + 2 * qc + (e & 1);
                 const bool live = m < M && n < N;
                 const float s = acc[t][e] * row_scale[m];
                 if constexpr (MODE == MODE_RESIDUAL) {
@@ -403,13 +410,16 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 if (p.error_flag) atomicExch(p.error_flag, 1);
             }
             TL(const long long c1 = clock64(); tl_w += c1 - c0;)
-            const __nv_bfloat16* slot = my_ring + (size_t)sl * SLOT_ELEMS + qc * 8;
+            // the box lies as [2 pieces of 64 k][rows][64] with the 128-byte swizzle: chunk c of row r at chunk c ^ (r & 7)
+            const __nv_bfloat16* slot = my_ring + (size_t)sl * SLOT_ELEMS + fr * 64;
             const int k0 = kb * BOXK;
             uint4 a[PIECES][2], b[PIECES][MT];
 #pragma unroll
             for (int i = 0; i < PIECES; ++i) {
-                a[i][0] = *reinterpret_cast<const uint4*>(slot + qr * BOXK + i * 32);
-                a[i][1] = *reinterpret_cast<const uint4*>(slot + (qr + 8) * BOXK + i * 32);
+                constexpr bool SPLIT = MODE == MODE_SWIGLU || MODE == MODE_QKV;  // two loads of eight rows, else one of sixteen
+                const int chunk = ((((i & 1) << 2) | qc) ^ fr) * 8, piece = (i >> 1) * (SPLIT ? 8 * 64 : 16 * 64);
+                a[i][0] = *reinterpret_cast<const uint4*>(slot + piece + chunk);
+                a[i][1] = *reinterpret_cast<const uint4*>(slot + piece + chunk + (SPLIT ? 8 * BOXK : 8 * 64));
                 // beyond K the weights arrived as zeros and x is not read (its row ends there)
                 const bool have = k0 + i * 32 + qc * 8 < K;
 #pragma unroll

@@ -45,6 +45,21 @@ inline bool make_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// A map over a row-major 16-bit matrix [rows, cols], cols a multiple of 64, seen as [cols / 64][rows][64]: a box is
+// `box_rows` rows of two consecutive 64-element pieces, laid down in shared memory as [2][box_rows][64] with the
+// 128-byte swizzle (the 16-byte chunk c of row r lies at chunk c ^ (r & 7)).  Coordinates: (0, row, piece).
+inline bool make_map_row_pieces_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || cols % 64) return false;
+    const cuuint64_t dims[3] = {64, rows, cols / 64};
+    const cuuint64_t strides[2] = {cols * 2, 128};  // bytes between rows, between pieces
+    const cuuint32_t box[3] = {64, box_rows, 2};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Maps are cached by (address, shape, box): weights and cache pools live for the life of the model, and
 // activations of a shape come back to the same addresses from a caching allocator.  Null if the driver refuses.
 inline const CUtensorMap* cached_map_2d_bf16(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
@@ -111,6 +126,10 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 __device__ __forceinline__ void load_2d(void* smem, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                  ::"r"(smem_addr(smem)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void load_3d(void* smem, const CUtensorMap* map, int x, int y, int z, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+                 ::"r"(smem_addr(smem)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar)) : "memory");
 }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(map) : "memory");

@@ -359,8 +359,10 @@ def _library_is_faster(kind: str, m: int) -> bool:
 
 def _library_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     library()  # the engine never runs without its kernels, even where a matrix product is the vendor's
+    if out_dtype == torch.float32 and x.dtype == torch.bfloat16:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)  # the 32-bit sums as they are, not rounded on the way
     out = torch.matmul(x, w.t())
-    return out if out_dtype == torch.bfloat16 else out.to(out_dtype)
+    return out if out_dtype == out.dtype else out.to(out_dtype)
 
 
 def _tcgen05_linear(x, w, out_dtype, mode: int, n_out: int, up_offset: int = 0):

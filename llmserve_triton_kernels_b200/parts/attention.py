@@ -127,13 +127,14 @@ class PagedAttention(Mixer):
             scale=self.scale,
             window=self.window,
         )
+        # the contribution to the 32-bit residual stream leaves the product in 32-bit: it is the sum's largest addend
         if self.b_out is not None:
-            return ops.add_bias(ops.linear(out, self.w_out), self.b_out)
+            return ops.add_bias(ops.linear(out, self.w_out, out_dtype=torch.float32), self.b_out.float())
         if sink is not None:
             handed_on = sink.linear(out, self.w_out)
             if handed_on is not None:
                 return handed_on
-        return ops.linear(out, self.w_out)
+        return ops.linear(out, self.w_out, out_dtype=torch.float32)
 
     def _project_rotate_store(self, x, ctx, cache, table):
         H, KV, D = self.num_heads, self.num_kv_heads, self.head_dim

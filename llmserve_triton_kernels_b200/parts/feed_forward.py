@@ -54,13 +54,14 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx, sink=None):
         if self.bias:
             act = ops.swiglu(ops.add_bias(ops.linear(x, self.w_gate_up), self.b_gate_up))
-            return ops.add_bias(ops.linear(act, self.w_down), self.b_down)
+            return ops.add_bias(ops.linear(act, self.w_down, out_dtype=torch.float32), self.b_down.float())
         act = ops.linear_swiglu(x, self.w_gate_up)
         if sink is not None:
             handed_on = sink.linear(act, self.w_down)
             if handed_on is not None:
                 return handed_on
-        return ops.linear(act, self.w_down)
+        # the contribution to the 32-bit residual stream leaves the product in 32-bit: it is the sum's largest addend
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

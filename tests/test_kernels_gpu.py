@@ -114,8 +114,9 @@ def test_linear_swiglu_fused_for_few_rows(m, inter, k, policy, monkeypatch):
     torch.testing.assert_close(got.double(), want, atol=2e-2 * 0.05 * k**0.5, rtol=2e-2)
 
 
-@pytest.mark.parametrize("m,hidden,k,n_next", [(1, 2048, 5632, 2560), (8, 2048, 2048, 11264), (16, 96, 256, 40), (3, 72, 24, 172),
-                                              (128, 96, 256, 40), (300, 2048, 5632, 2560), (2048, 2048, 2048, 11264), (131, 72, 24, 172)])
+@pytest.mark.parametrize("m,hidden,k,n_next", [(1, 2048, 5632, 2560), (8, 2048, 2048, 11264), (16, 96, 256, 40), (3, 72, 64, 172),
+                                              (5, 128, 320, 100), (128, 96, 256, 40), (300, 2048, 5632, 2560), (2048, 2048, 2048, 11264),
+                                              (131, 72, 24, 172)])
 def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
     """A product that adds into the residual stream and hands it on in factored normalised form,
     and the next product that consumes that form: together they must equal
@@ -147,8 +148,8 @@ def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
 
 
 @pytest.mark.parametrize("m,H,KV,D,hidden,page_size,rotate", [(1, 32, 4, 64, 2048, 16, True), (8, 4, 2, 16, 64, 8, True),
-                                                            (16, 3, 1, 32, 96, 4, True), (5, 6, 3, 128, 72, 16, False),
-                                                            (2, 5, 0, 48, 40, 1, True)])
+                                                            (16, 3, 1, 32, 192, 4, True), (5, 6, 3, 128, 320, 16, False),
+                                                            (2, 5, 0, 48, 128, 1, True), (9, 32, 4, 64, 2048, 16, True)])
 def test_linear_qkv_rope_fused_for_few_rows(m, H, KV, D, hidden, page_size, rotate):
     """Projection, rotation and cache write in one kernel against the three done plainly."""
     o = ops()
@@ -163,6 +164,9 @@ def test_linear_qkv_rope_fused_for_few_rows(m, H, KV, D, hidden, page_size, rota
     pool_b = pool_a.clone() if KV else None
     got_q = o.linear_qkv_rope(x, w, positions, table, slot_map if KV else None, pool_a, H, KV, D, write_kv=KV > 0)
     assert got_q is not None
+    # a width that is no multiple of 64 (the weights travel in pieces of 64) is not taken: the caller goes the other way
+    assert o.linear_qkv_rope(x[:, :40].contiguous(), w[:, :40].contiguous(), positions, table, slot_map if KV else None, pool_a, H, KV, D,
+                             write_kv=KV > 0) is None
     qkv = plain_ops.linear(x, w, out_dtype=torch.float32)  # the plain chain keeps 32 bits until the stores
     plain_ops.rope_kv_write(qkv, positions, table, slot_map if KV else None, pool_b, H, KV, D, write_kv=KV > 0)
     scale = float(qkv.abs().max())
