@@ -32,10 +32,9 @@ namespace {
 
 using namespace lin;
 
-// One product: MT 8-token tiles (M <= 8 MT), one CTA per SM (see linear_stream.cuh for how it streams).
+// One product: MT 8-token tiles (M <= 8 MT); see linear_stream.cuh for how a CTA streams.
 template <int MT, int MODE, typename TO>
-__global__ void __launch_bounds__(THREADS, 1)
-linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
+__device__ __forceinline__ void linear_decode_body(const LinearParams& p, const CUtensorMap& wmap) {
     TL(tl::Marks marks;)
     extern __shared__ __align__(1024) unsigned char smem_all[];
     unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_all + 1023) & ~(uintptr_t)1023);  // the swizzle's period
@@ -68,6 +67,18 @@ linear_decode_kernel(const LinearParams p, const __grid_constant__ CUtensorMap w
     if (!stream_run<MT, MODE, TO>(st, p, &wmap, my_ring, full[warp], red, x_s, row_scale) && lane == 0 && p.error_flag)
         atomicExch(p.error_flag, 1);
     TL(__syncthreads(); if (threadIdx.x == 0) { marks.mark(4); marks.t[1] = ((unsigned long long)(unsigned)st.tl_sec[0] << 48) | ((unsigned long long)(unsigned)(st.tl_sec[1] & 0xffff) << 32) | ((unsigned long long)(unsigned)(st.tl_sec[2] & 0xffff) << 16) | (unsigned)(st.tl_sec[3] & 0xffff); marks.t[3] = (marks.t[3] & ~0xffull) | (unsigned)st.tl_sec[4]; marks.t[5] = ((unsigned long long)(unsigned)st.tl_loop << 40) | ((unsigned long long)(unsigned)st.tl_sync << 20) | (unsigned)st.tl_all; marks.write(MODE, p.tl_launch, blockIdx.x, p.N, p.K); })
+}
+
+// Up to 8 tokens: at most 120 registers a thread, so that two CTAs of 256 threads share an SM's registers with room to
+// spare (two CTAs of 128 registers a thread fill the file to the last register, and were then seen to run one after
+// the other); 9 to 16 tokens carry twice the accumulators and fragments and take what they need.
+template <int MODE, typename TO>
+__global__ void __maxnreg__(120) linear_decode_kernel_8(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
+    linear_decode_body<1, MODE, TO>(p, wmap);
+}
+template <int MODE, typename TO>
+__global__ void __launch_bounds__(THREADS, 1) linear_decode_kernel_16(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
+    linear_decode_body<2, MODE, TO>(p, wmap);
 }
 
 int sm_count() {
@@ -139,7 +150,9 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     q.ring_warps = busy_teams * q.group;
     const size_t smem = ring_bytes(q.slots, q.ring_warps) + x_bytes + (size_t)q.red_floats * sizeof(float) + 1024;  // and room to align
     if (smem > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;
-    auto kernel = linear_decode_kernel<MT, MODE, TO>;
+    void (*kernel)(const LinearParams, const CUtensorMap);
+    if constexpr (MT == 1) kernel = linear_decode_kernel_8<MODE, TO>;
+    else kernel = linear_decode_kernel_16<MODE, TO>;
     static size_t configured = 0;  // per instantiation: the most dynamic shared memory asked for so far
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
