@@ -1,6 +1,7 @@
 """Trace replay: feeds given token ids through a model step by step and writes logits.
 
     bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    bin/trace_run --random PRESET [--seed S] ...        (random weights of a named configuration, no folder)
 
 It samples nothing and has no forward pass, cache or loader of its own: it drives the same
 model, step function, cache manager and kernels that generation uses.  Steps are read from
@@ -29,14 +30,19 @@ import torch
 
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(prog="trace_run", description="replay token ids step by step and write logits")
-    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    ap.add_argument("--model", help="folder with config.json and model.safetensors")
+    ap.add_argument("--random", metavar="PRESET", help="instead of --model: random weights of a named configuration (config/presets.py)")
+    ap.add_argument("--seed", type=int, default=0, help="seed of the random weights (with --random)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True, help="most tokens that live requests hold at any time")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per page of the cache")
     ap.add_argument("--max-requests", type=int, default=16, help="most requests alive at a time")
     ap.add_argument("--device", default="cuda:0")
-    return ap.parse_args(argv)
+    args = ap.parse_args(argv)
+    if (args.model is None) == (args.random is None):
+        ap.error("give a model folder with --model, or a configuration's name with --random")
+    return args
 
 
 def main(argv=None) -> int:
@@ -46,7 +52,9 @@ def main(argv=None) -> int:
     from .cache import CacheManager
     from .engine.batch import StepEntry
     from .engine.step import StepFunction
-    from .models.load import load_model, resolve_dtype
+    from .config.presets import PRESETS
+    from .config.registry import architecture_of
+    from .models.load import load_model, random_model, resolve_dtype
 
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
@@ -54,7 +62,13 @@ def main(argv=None) -> int:
     if device.type == "cuda":
         torch.cuda.set_device(device)
     dtype = resolve_dtype(args.dtype)
-    model, _ = load_model(args.model, dtype, device)
+    if args.random is not None:
+        if args.random not in PRESETS:
+            raise SystemExit(f"trace_run: no configuration named {args.random!r}; known: {sorted(PRESETS)}")
+        cfg_dict = PRESETS[args.random]
+        model = random_model(architecture_of(cfg_dict).config_class.from_dict(cfg_dict), args.seed, dtype, device)
+    else:
+        model, _ = load_model(args.model, dtype, device)
     num_pages = max(1, -(-args.max_tokens // args.page_size))
     cache = CacheManager(
         model.cache_specs(), model.plan.schedule, page_size=args.page_size, num_pages=num_pages,

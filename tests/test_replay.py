@@ -125,3 +125,32 @@ def test_replay_at_real_layer_sizes(preset, dtype, model_folder, tmp_path):
     assert len(got) == sum(len(v) for v in trace.rows.values())
     worst = trace_tools.compare(got, expected_logits(folder, flat), tolerance(dtype))
     print(f"worst row (fraction of tolerance, (request, position, diff)): {worst}")
+
+
+def test_replay_program_with_random_weights_of_a_named_configuration(tmp_path, plain_ops_engine):
+    """``--random PRESET --seed S`` stands in for a model folder: the same weights as ``write_random_model`` writes for
+    that configuration and seed, so the logits equal those of the folder's replay."""
+    import io
+    import json
+    import sys
+
+    from llmserve_triton_kernels_b200 import replay
+    from llmserve_triton_kernels_b200.config import LlamaConfig
+    from llmserve_triton_kernels_b200.config.presets import PRESETS
+    from llmserve_triton_kernels_b200.weights import write_random_model
+
+    tokens = tiny_configs.seeded_tokens(256, [9], 5)[0]
+    step = json.dumps({"step": 0, "entries": [{"id": "a", "tokens": tokens, "want": [0, 8]}], "end": ["a"]}) + "\n"
+    folder = write_random_model(tmp_path / "m", LlamaConfig.from_dict(PRESETS["tiny"]), seed=3, dtype=torch.bfloat16)
+    outs = []
+    for name, source in (("folder", ["--model", str(folder)]), ("random", ["--random", "tiny", "--seed", "3"])):
+        stdin, stdout = sys.stdin, sys.stdout
+        sys.stdin, sys.stdout = io.StringIO(step), io.StringIO()
+        try:
+            assert replay.main([*source, "--dtype", "float32", "--out", str(tmp_path / name), "--max-tokens", "64", "--device", "cpu"]) == 0
+        finally:
+            sys.stdin, sys.stdout = stdin, stdout
+        outs.append(np.fromfile(tmp_path / name / "0.f32", dtype="<f4"))
+    assert outs[0].shape == (2 * 256,) and np.array_equal(outs[0], outs[1])
+    with pytest.raises(SystemExit):
+        replay.parse_args(["--out", "x", "--max-tokens", "1"])
