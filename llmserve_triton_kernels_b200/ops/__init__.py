@@ -79,7 +79,6 @@ _TC_ATTENTION_ENABLED = True
 _TC_ATTENTION_HEAD_DIM = 64
 _TC_ATTENTION_PAGE_SIZES = (8, 16, 32, 64)
 _TC_ATTENTION_MIN_TOKENS = 128  # a request with at least this many tokens in the step: attention on tcgen05
-_TCGEN05_RESIDUAL_SINK = False  # see ResidualSink.usable
 _TCGEN05_MIN_ROWS = 128  # from this many rows a bfloat16 product runs on tcgen05 with TMA-fed tiles (own kernel)
 _DECODE_LINEAR_MAX_ROWS = 16  # up to this many rows a bfloat16 matrix product streams the weights once (own kernel)
 _FORCE_GENERIC_ATTENTION = False  # tests switch the tensor-core attention off to reach the general kernel in bfloat16
@@ -229,58 +228,77 @@ class NormedInput:
         return (self.xw.float() * scale[:, None]).to(self.xw.dtype)
 
 
-class ResidualSink:
-    """Where a part's last matrix product may put its result: added to the 32-bit residual
-    stream ``resid`` in place, which is then handed on normalised for ``norm`` (an RMS norm's
-    ``weight`` and ``eps``) as a :class:`NormedInput`.  Built by a block when the step is small
-    enough for the fused decode kernels."""
+class _Added:
+    """What :meth:`ResidualSink.linear` returns when the product has been added to the residual stream and nothing is
+    left pending: the next norm normalises the stream as it stands."""
 
-    def __init__(self, resid: torch.Tensor, weight: torch.Tensor, eps: float, norm=None):
+    def __repr__(self) -> str:
+        return "ADDED"
+
+
+ADDED = _Added()
+
+
+class ResidualSink:
+    """Where a part's last matrix product may put its result: added to the 32-bit residual stream ``resid`` in place.
+    For few rows the fused decode kernel does it and hands the stream on normalised for ``norm`` (an RMS norm's
+    ``weight`` and ``eps``; None: a norm that cannot be folded into a product's end) as a :class:`NormedInput`; for
+    more rows the product's own epilogue adds into the stream (the library's product with the stream as its addend,
+    accumulated and written in 32-bit), and :data:`ADDED` is returned: no contribution travels through memory to be
+    added by the norm's kernel, which then only reads the stream.  Built by a block for bfloat16 steps."""
+
+    def __init__(self, resid: torch.Tensor, weight: torch.Tensor | None, eps: float, norm=None):
         self.resid, self.weight, self.eps, self.norm = resid, weight, float(eps), norm
 
     @staticmethod
     def usable(num_tokens: int, dtype: torch.dtype) -> bool:
-        """Steps of few rows end their products this way (the weight-streaming kernel).  The tcgen05 kernel
-        for many rows can too (``linear`` below takes any row count; its four epilogue warps turn each 32 x 32
-        piece round in shared memory so that the 32-bit stream is read and written 128 bytes at a time), but four
-        warps per SM do not keep enough of the stream in flight: 6.04 ms against 5.46 ms with the norm as a kernel of
-        its own for a prompt of 2,048 tokens on a 1.1B model.  Steps of many rows run the norms as kernels."""
-        return dtype == torch.bfloat16 and (num_tokens <= _DECODE_LINEAR_MAX_ROWS or
-                                            (_TCGEN05_RESIDUAL_SINK and num_tokens >= _TCGEN05_MIN_ROWS))
+        return dtype == torch.bfloat16
 
-    def linear(self, x: torch.Tensor, w: torch.Tensor) -> "NormedInput | None":
-        """``resid += x @ w^T``; returns the stream normalised for ``norm``, or None if the
-        fused kernel refuses the shape (then nothing was changed)."""
+    def linear(self, x: torch.Tensor, w: torch.Tensor) -> "NormedInput | _Added | None":
+        """``resid += x @ w^T``; returns the stream normalised for ``norm``, or :data:`ADDED`, or None if no way
+        takes the operands (then nothing was changed)."""
         m, k = x.shape
         n = w.shape[0]
-        if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous()):
+        if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous() and self.resid.is_contiguous()):
             return None
-        if m >= _TCGEN05_MIN_ROWS:
-            parts = library().llm_gemm_tcgen05_parts(n)
+        if m <= _DECODE_LINEAR_MAX_ROWS and self.weight is not None:
+            parts = -(-n // 16)
             xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
             ss = torch.empty((parts, m), dtype=torch.float32, device=x.device)
             code = _launch(
-                "llm_gemm_tcgen05_fused", _ptr(x), x.stride(0), _ptr(w), None, _BF16, m, n, k, n, 2, 0, None, 0, 0.0,
+                "llm_linear_decode", _ptr(x), _ptr(w), None, _BF16, m, n, k, x.stride(0), n, None, 0, 0.0, 2, 0,
                 _ptr(self.resid), _ptr(self.weight), _ptr(xw), _ptr(ss), _error_flag_ptr(), _stream(),
             )
-            if code == 10002:
-                add_launches(-1)
-                return None
-            _check(code, "linear into the residual stream (tcgen05)")
-            return NormedInput(xw, ss, self.eps, self.norm)
-        if m > _DECODE_LINEAR_MAX_ROWS:
+            if code != 10002:
+                _check(code, "linear into the residual stream")
+                return NormedInput(xw, ss, self.eps, self.norm)
+            add_launches(-1)  # a shape the kernel refuses: the library's way below
+        if _GEMM_POLICY == "own" and m >= _TCGEN05_MIN_ROWS:
+            return None  # the caller runs the own tcgen05 product and leaves the sum to the norm's kernel
+        library()
+        torch.addmm(self.resid, x, w.t(), out_dtype=torch.float32, out=self.resid)
+        return ADDED
+
+    def linear_tcgen05(self, x: torch.Tensor, w: torch.Tensor) -> "NormedInput | None":
+        """The same by the own tcgen05 kernel for 128 rows and more, whose four epilogue warps turn each 32 x 32 piece
+        round in shared memory so that the 32-bit stream is read and written 128 bytes at a time.  Correct, and kept
+        under test, but four warps per SM do not keep enough of the stream in flight: a prompt of 2,048 tokens on a
+        1.1B model took 6.04 ms this way against 5.46 ms with the sum left to the norm's kernel, so no part calls it."""
+        m, k = x.shape
+        n = w.shape[0]
+        if not (x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.is_contiguous() and m >= _TCGEN05_MIN_ROWS and self.weight is not None):
             return None
-        parts = -(-n // 16)
+        parts = library().llm_gemm_tcgen05_parts(n)
         xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
         ss = torch.empty((parts, m), dtype=torch.float32, device=x.device)
         code = _launch(
-            "llm_linear_decode", _ptr(x), _ptr(w), None, _BF16, m, n, k, x.stride(0), n, None, 0, 0.0, 2, 0,
+            "llm_gemm_tcgen05_fused", _ptr(x), x.stride(0), _ptr(w), None, _BF16, m, n, k, n, 2, 0, None, 0, 0.0,
             _ptr(self.resid), _ptr(self.weight), _ptr(xw), _ptr(ss), _error_flag_ptr(), _stream(),
         )
         if code == 10002:
             add_launches(-1)
             return None
-        _check(code, "linear into the residual stream")
+        _check(code, "linear into the residual stream (tcgen05)")
         return NormedInput(xw, ss, self.eps, self.norm)
 
 

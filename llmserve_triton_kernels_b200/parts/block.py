@@ -3,9 +3,9 @@
 Parity: src/llmserve/model/llama.py:131-135 — ``x += mixer(norm(x)); x += ff(norm(x))``.
 The residual stream is a 32-bit tensor that the norms update in place: each part returns its
 contribution, and the next norm adds it before normalising (one pass over the row instead of
-three).  For small steps the last product of a part adds into the stream itself and hands it on
-already normalised for the next norm (see ``ops.ResidualSink``), so a decode step has no norm
-launches of its own.
+three).  In bfloat16 the last product of a part adds into the stream itself (see ``ops.ResidualSink``): a
+small step's product also hands the stream on already normalised for the next norm, so a decode step has
+no norm launches of its own; a large step's product leaves a norm kernel that only reads the stream.
 """
 
 from __future__ import annotations
@@ -44,18 +44,21 @@ class PreNormBlock(Block):
             if pending.norm is not norm:
                 raise RuntimeError("a part handed the residual stream on normalised for another norm")
             return pending if getattr(consumer, "accepts_sink", False) else pending.materialize()
+        if pending is ops.ADDED:  # the part's last product added its result to the stream itself
+            pending = None
         return norm.add_forward(resid, pending)
 
     @staticmethod
     def _sink(part, norm, resid, ctx):
-        """A sink for the part's last product, if the step is small, the part takes one and the
-        norm after it is an RMS norm that can be folded into the product's ends."""
+        """A sink for the part's last product, if the part takes one and another norm follows (the last part of the
+        last layer keeps its contribution: only the rows whose logits are wanted are summed).  Where that norm is an
+        RMS norm its weight goes along, so that a small step's product can hand the stream on normalised."""
+        if norm is None or not getattr(part, "accepts_sink", False):
+            return None
+        if not ops.ResidualSink.usable(ctx.num_tokens, getattr(norm, "out_dtype", None)):
+            return None
         fused = getattr(norm, "fused_params", None)
-        if norm is None or fused is None or not getattr(part, "accepts_sink", False):
-            return None
-        if not ops.ResidualSink.usable(ctx.num_tokens, norm.out_dtype):
-            return None
-        weight, eps = fused()
+        weight, eps = fused() if fused is not None else (None, 0.0)
         return ops.ResidualSink(resid, weight, eps, norm)
 
 

@@ -132,10 +132,18 @@ def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
     want_norm = want_resid * torch.rsqrt(want_resid.pow(2).mean(-1, keepdim=True) + eps) * norm_w.double()
     want_next = want_norm @ w_next.double().t()
 
-    handed = o.ResidualSink(resid, norm_w, eps).linear(x, w)
-    assert handed is not None
+    before = resid.clone()
+    sink = o.ResidualSink(resid, norm_w, eps)
+    # few rows: the weight-streaming kernel; many: the own tcgen05 kernel's end (kept under test; serving lets the
+    # library's product add into the stream, below)
+    handed = sink.linear(x, w) if m <= 16 else sink.linear_tcgen05(x, w)
+    assert isinstance(handed, o.NormedInput)
     torch.testing.assert_close(resid.double(), want_resid, atol=2e-2 * 0.05 * k**0.5, rtol=1e-2)
     torch.testing.assert_close(handed.materialize().double(), want_norm, atol=3e-2, rtol=2e-2)
+    if m > 16:
+        stream = before.clone()
+        assert o.ResidualSink(stream, None, 0.0).linear(x, w) is o.ADDED
+        torch.testing.assert_close(stream.double(), want_resid, atol=2e-2 * 0.05 * k**0.5, rtol=1e-2)
     got_next = o.linear(handed, w_next, out_dtype=torch.float32)
     torch.testing.assert_close(got_next.double(), want_next, atol=3e-2 * 0.05 * hidden**0.5, rtol=2e-2)
     if n_next % 2 == 0:
