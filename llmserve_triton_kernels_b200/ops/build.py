@@ -26,7 +26,10 @@ LIB_NAME = "libllmserve_b200_kernels.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # a profiling build whose decode kernels leave global-timer stamps per CTA (csrc/timeline.cuh); built into a folder of
 # its own so that it never stands in for the product's library
-TIMELINE = bool(os.environ.get("LLMSERVE_B200_TIMELINE"))
+def timeline_build() -> bool:
+    return bool(os.environ.get("LLMSERVE_B200_TIMELINE"))
+
+
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
 
 
@@ -72,9 +75,9 @@ def build_dirs() -> tuple[Path, Path]:
         return base / "obj", base
     lib_dir = PACKAGE_DIR / "ops"
     obj_dir = CSRC / "_build"
-    if not TIMELINE and _writable(lib_dir) and _writable(obj_dir):
+    if not timeline_build() and _writable(lib_dir) and _writable(obj_dir):
         return obj_dir, lib_dir
-    tag = hashlib.sha1((str(PACKAGE_DIR) + ("+timeline" if TIMELINE else "")).encode()).hexdigest()[:12]
+    tag = hashlib.sha1((str(PACKAGE_DIR) + ("+timeline" if timeline_build() else "")).encode()).hexdigest()[:12]
     base = Path(tempfile.gettempdir()) / f"llmserve_b200_{os.getuid()}_{tag}"
     base.mkdir(parents=True, exist_ok=True)
     return base / "obj", base
@@ -124,7 +127,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
     try:
         def compile_one(src: Path) -> None:
             obj = obj_dir / (src.stem + ".o")
-            flags = NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else []) + (["-DLLM_TIMELINE"] if TIMELINE else [])
+            flags = NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else []) + (["-DLLM_TIMELINE"] if timeline_build() else [])
             _run([nvcc, *ARCH_FLAGS, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)], f"nvcc {src.name}")
             _say(f"compiled {src.name}")
 
