@@ -111,6 +111,8 @@ class Model:
     def forward(self, ctx, caches) -> torch.Tensor:
         """Run the tokens of ``ctx`` through every entry of the order; ``caches[i]`` is the view
         of entry i's cache.  Returns 32-bit logits ``[len(ctx.logit_rows), vocab]``."""
+        if ops.checked():
+            self._check_step(ctx, caches)
         resid = self.embed_tokens(ctx)
         pending = None
         order = self.plan.schedule
@@ -122,6 +124,16 @@ class Model:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
         x = self.final_norm.add_forward(resid, pending, rows=ctx.logit_rows)
         return self.project_logits(x)
+
+    def _check_step(self, ctx, caches) -> None:
+        """Checked mode: the step's arrays are looked over on the device before any kernel indexes with them."""
+        slots = next((c.states.shape[0] for c in caches if hasattr(c, "states")), 0)
+        ops.check_step_arrays(ctx, self.plan.vocab_size, self.plan.max_positions, slots)
+        seen = []
+        for c in caches:
+            if hasattr(c, "page_table") and all(c.page_table.data_ptr() != t.data_ptr() for t in seen):
+                ops.check_page_group(ctx, c.page_table, c.slot_map, c.page_size, c.pool.shape[0], c.spec.window, len(seen))
+                seen.append(c.page_table)
 
     def embed_tokens(self, ctx) -> torch.Tensor:
         """The residual stream that the first layer meets: the tokens' rows of the table, in 32-bit ``[N, hidden]``.

@@ -28,6 +28,8 @@ _SIGNATURES = {
     "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "llm_add_bias": [_vp, _i, _i, _i, _i, _vp, _vp],
     "llm_fetch_words": [_vp, _vp, _vp, _i, _i, _vp],
+    "llm_check_step_arrays": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "llm_check_page_group": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_linear_decode": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_linear_decode_qkv": [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp],
@@ -205,10 +207,70 @@ def _error_flag_ptr() -> int:
 
 
 def check_device_errors() -> None:
-    """Raise if a kernel reported that a bounded wait gave up (call after a synchronisation)."""
+    """Raise if a kernel reported that a bounded wait gave up, or (checked mode) that a step's arrays held an index out
+    of its bounds (call after a synchronisation)."""
     if _error_flag is not None and int(_error_flag[0]) != 0:
         _error_flag[0] = 0
         raise KernelError("a kernel's wait for an asynchronous copy gave up; its results are not valid")
+    if _check_status is not None and int(_check_status[0]) != 0:
+        code, group, index, value, limit, count = (int(v) for v in _check_status[:6])
+        _check_status.zero_()
+        what = _CHECK_CODES.get(code, f"violation {code}")
+        where = f" of page group {group}" if group >= 0 else ""
+        raise KernelError(
+            f"checked mode: {what}{where}: entry {index} holds {value} against {limit} ({count} violations in all); the entries were "
+            "replaced by harmless ones before any kernel used them, and the step's results are not valid"
+        )
+
+
+# Checked mode (the environment variable LLMSERVE_B200_CHECKED=1, or set_checked): every step starts with kernels that
+# look over its integer arrays on the device, where the step's kernels will read them (csrc/step_check.cu).
+_checked = bool(os.environ.get("LLMSERVE_B200_CHECKED"))
+_check_status: torch.Tensor | None = None
+_CHECK_CODES = {
+    1: "a token id outside the vocabulary", 2: "a position beyond the model's positions", 3: "a token that names a request it does not belong to",
+    4: "token offsets that do not rise or do not end at the number of tokens", 5: "a context length shorter than the request's new tokens or beyond the model's positions",
+    6: "a wanted row beyond the step's tokens", 7: "a state slot beyond the slots there are", 8: "a page table entry outside the pool",
+    9: "a slot that is outside the pool or disagrees with the page table", 10: "a page table narrower than a request's pages",
+}
+
+
+def checked() -> bool:
+    return _checked
+
+
+def set_checked(on: bool) -> None:
+    """Turn checked mode on or off for steps that run, or are captured as graphs, from now on."""
+    global _checked
+    _checked = bool(on)
+
+
+def _check_status_ptr() -> int:
+    global _check_status
+    if _check_status is None:
+        _check_status = torch.zeros(8, dtype=torch.int32).pin_memory()
+    return _check_status.data_ptr()
+
+
+def check_step_arrays(ctx, vocab: int, max_positions: int, state_slot_count: int = 0) -> None:
+    """Checked mode: compare a step's token ids, positions, request indices, offsets, lengths, wanted rows and state
+    slots with their limits on the device; a violation is recorded for :func:`check_device_errors` and repaired."""
+    _check(_launch(
+        "llm_check_step_arrays", _ptr(ctx.token_ids), _ptr(ctx.positions), _ptr(ctx.token_request), _ptr(ctx.cu_tokens),
+        _ptr(ctx.context_lens), _ptr(ctx.logit_rows) if ctx.num_logits else None, _ptr(ctx.state_slots), ctx.num_tokens,
+        ctx.num_requests, ctx.num_logits, vocab, max_positions, state_slot_count, _check_status_ptr(), _stream(),
+    ), "check_step_arrays")
+
+
+def check_page_group(ctx, page_table: torch.Tensor, slot_map: torch.Tensor, page_size: int, num_pages: int,
+                     window: int | None, group: int) -> None:
+    """Checked mode, after :func:`check_step_arrays`: every page table entry that the step may read lies inside the pool
+    of ``num_pages`` pages, and every new token's slot is the one its page table gives."""
+    _check(_launch(
+        "llm_check_page_group", _ptr(page_table), page_table.shape[1], _ptr(slot_map), _ptr(ctx.positions), _ptr(ctx.token_request),
+        _ptr(ctx.cu_tokens), _ptr(ctx.context_lens), ctx.num_tokens, ctx.num_requests, page_size, num_pages, window or 0, group,
+        _check_status_ptr(), _stream(),
+    ), "check_page_group")
 
 
 class NormedInput:
