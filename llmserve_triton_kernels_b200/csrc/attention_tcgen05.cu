@@ -6,16 +6,16 @@
 // One CTA computes 128 query tokens of one head against the keys they may see, 64 keys at a time:
 //   warps 0-3 : softmax.  Thread i owns query row i, which is lane i of tensor memory: it reads its 64
 //               scores with tcgen05.ld, keeps the running maximum and sum of the row (no shuffles: the
-//               whole row is the thread's), writes the probabilities as bfloat16 into shared memory in
-//               the layout the next product reads, and folds the product's result into the 64 output
-//               values it keeps in registers (rescaled by the change of the maximum).
+//               whole row is the thread's) and writes the probabilities as bfloat16 into shared memory in
+//               the layout the next product reads.  The output accumulates in tensor memory over all key tiles;
+//               a row's shift follows its maximum only when the maximum has risen by more than 2^8, and only then
+//               does the warp rescale its 32 rows of the output (load, multiply, store).
 //   warp 4    : producer.  Looks up pages (32 entries of the page table per load, handed round by
 //               shuffles) and issues one TMA box per page for keys and one for values, each from a lane
 //               of its own, into a ring of STAGES tiles.
 //   warp 5    : one thread issues the products; the warp owns the allocation of tensor memory.
 // Scores and probabilities have two buffers each: the scores of tile j+1 are computed while the softmax of
-// tile j runs, and the second product of tile j runs while the softmax of tile j+1 does (its result is
-// folded into the output one tile late).  Two CTAs share an SM.  Softmax, running sums and the output are
+// tile j runs, and the second product of tile j runs while the softmax of tile j+1 does.  Two CTAs share an SM.  Softmax, running sums and the output are
 // 32-bit; probabilities are rounded to bfloat16 for the second product, as in the mma.sync kernel.
 //
 // Keys past a request's length inside its last page, and pages outside the range a CTA needs, are
@@ -35,7 +35,8 @@ using attn::AttnParams;
 
 constexpr int BM = 128, BN = 64, HD = 64, STAGES = 3, THREADS = 192;
 constexpr int Q_BYTES = BM * HD * 2, P_BYTES = BM * BN * 2, K_BYTES = BN * HD * 2, STAGE_BYTES = 2 * K_BYTES;
-constexpr int TMEM_COLS = 256;  // two tiles of scores in columns [0, 64) and [64, 128), the second product's result in [128, 192)
+constexpr float LAZY = 8.f;  // log2 of how far a row's maximum may rise before its shift follows
+constexpr int TMEM_COLS = 256;  // two tiles of scores in columns [0, 64) and [64, 128), the output in [128, 192)
 
 struct TcParams {
     AttnParams a;
@@ -180,7 +181,8 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                 const unsigned long long p_desc = umma::desc_sw128(p_s + (size_t)(j & 1) * P_BYTES);
                 const unsigned long long v_desc = umma::desc_sw128(kv_s + (size_t)s * STAGE_BYTES + K_BYTES, 1024 >> 4);
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k) umma::mma_bf16(o_tmem, p_desc + 2 * k, v_desc + (2048 >> 4) * k, IDESC_PV, k != 0);
+                for (int k = 0; k < BN / 16; ++k)  // the output accumulates over the tiles
+                    umma::mma_bf16(o_tmem, p_desc + 2 * k, v_desc + (2048 >> 4) * k, IDESC_PV, k != 0 || j != 0);
                 umma::commit(&o_full);
                 umma::commit(&kv_empty[s]);
             }
@@ -193,29 +195,9 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
         const int pos = pos0 + tok;
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
         const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16);
-        float o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+        float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        // the result of the second product of tile j is folded into the output one tile later, after the
-        // probabilities of tile j + 1 have been computed: the product runs meanwhile
-        auto fold = [&](int j) -> bool {  // o = o * alpha_j + P_j V_j
-            if (!__all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, j & 1))) return false;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            static_assert(HD == 64, "the product's result is read with one 64-column load");
-            float pv[HD];
-            umma::tmem_ld64(lane_base + 2 * BN, pv);
-            // two values per instruction (packed 32-bit arithmetic): the same roundings as one by one
-            const float2 a2 = make_float2(alpha_prev, alpha_prev);
-#pragma unroll
-            for (int i = 0; i < HD; i += 2) {
-                const float2 r = __ffma2_rn(make_float2(o[i], o[i + 1]), a2, make_float2(pv[i], pv[i + 1]));
-                o[i] = r.x;
-                o[i + 1] = r.y;
-            }
-            return true;
-        };
+        const unsigned o_taddr = lane_base + 2 * BN;
         for (int j = 0; j < n_tiles; ++j) {
             const int key_base = (t_begin + j) * BN;
             ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&s_full[j & 1], (j >> 1) & 1));
@@ -246,9 +228,16 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                 }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-            const float m_new = fmaxf(m_run, mx);
+            // The output accumulates in tensor memory, scaled by 2^-m_run.  The row keeps its old shift while the new
+            // maximum is less than 2^LAZY above it (any shift gives the same quotient in the end; probabilities then
+            // reach 2^LAZY at most, which bfloat16 holds with its usual relative error), so the accumulated output
+            // has to be rescaled only on the few tiles where a row's maximum jumps.
+            const float m_cand = fmaxf(m_run, mx);
+            const bool grow = m_cand > m_run + LAZY || m_run == -INFINITY;
+            const float m_new = grow ? m_cand : m_run;
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = attn::fast_exp2(m_run - m_use);
+            const float alpha = attn::fast_exp2(m_run - m_use);  // 1 where the shift stays
+            const bool rescale = grow && m_run != -INFINITY;  // (a row that has seen no key yet has an output of zeros)
             m_run = m_new;
             // the probabilities (a masked score is -inf: its probability is exactly 0), into shared memory as the
             // second product's A (K-major, 128-byte swizzle: row `row`, 16-byte piece c at c ^ (row % 8))
@@ -272,19 +261,46 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                 *reinterpret_cast<uint4*>(p_tile + row * 128 + ((c ^ (row & 7)) << 4)) = u;
             }
             l_run = l_run * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
-            // the tile before: its product has had this tile's softmax to finish in; its result must be read before
-            // the issuer learns of this tile's probabilities (the next product overwrites the result)
-            if (j > 0 && !(ok = fold(j - 1))) break;
-            alpha_prev = alpha;
+            // The product of the tile before has had this tile's softmax to finish in.  Its barrier is waited for at
+            // every tile, needed or not: a phase is told from the one two before it only by its parity, and a warp
+            // that skipped phases could take an old one for the one it wants.
+            if (j > 0) {
+                ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, (j - 1) & 1));
+                if (!ok) break;
+            }
+            if (__any_sync(0xffffffffu, rescale)) {
+                // this tile's product must not start before the rows are rescaled: the issuer learns of the
+                // probabilities only below
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                float o[HD];
+                umma::tmem_ld64(o_taddr, o);
+                const float a = rescale ? alpha : 1.f;
+                const float2 a2 = make_float2(a, a);
+#pragma unroll
+                for (int i = 0; i < HD; i += 2) {
+                    const float2 r = __fmul2_rn(make_float2(o[i], o[i + 1]), a2);
+                    o[i] = r.x;
+                    o[i + 1] = r.y;
+                }
+                umma::tmem_st64(o_taddr, o);
+            }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[j & 1]);
         }
-        if (ok && n_tiles > 0) ok = fold(n_tiles - 1);
+        float o[HD];
+        if (ok && n_tiles > 0) {
+            ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, (n_tiles - 1) & 1));
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                static_assert(HD == 64, "the output is read with one 64-column load");
+                umma::tmem_ld64(o_taddr, o);
+            }
+        }
         if (!ok) {
             if (lane == 0) fail();
-        } else if (row_ok) {
+        } else if (row_ok && n_tiles > 0) {
             const float inv = 1.f / l_run;
             __nv_bfloat16* dst = p.out + (size_t)(q_begin + tok) * p.out_stride + (size_t)head * HD;
 #pragma unroll

@@ -32,6 +32,7 @@ def main() -> None:
     ap.add_argument("--first", type=int, default=20, help="first kernel of the step to print")
     ap.add_argument("--last", type=int, default=32, help="one past the last kernel to print")
     ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--sections", action="store_true", help="also print, for every product, where warp 0's cycles inside its loop went")
     args = ap.parse_args()
 
     os.environ["LLMSERVE_B200_TIMELINE"] = "1"
@@ -87,20 +88,20 @@ def main() -> None:
     rows = []
     for key in sorted(set(zip(lin["kernel"].tolist(), lin["launch"].tolist())), key=lambda k: k[1]):
         r = lin[(lin["kernel"] == key[0]) & (lin["launch"] == key[1])]
-        rows.append((f"{mode[key[0]]} [{r['a'][0]} x {r['b'][0]}]", r["t"].astype(np.int64) - t0, True))
+        rows.append((f"{mode[key[0]]} [{r['a'][0]} x {r['b'][0]}]", r["t"].astype(np.int64) - t0, True, r["t"]))
     if len(att):
         a = att[np.argsort(att["t"][:, 0])]
         t = a["t"].astype(np.int64) - t0
         first = 0
         for i in range(1, len(a) + 1):
             if i == len(a) or t[i, 0] - t[i - 1, 0] > 2500:  # launches are several microseconds apart
-                rows.append((f"attention, {a['kernel'][first] - 100} key warps", t[first:i], False))
+                rows.append((f"attention, {a['kernel'][first] - 100} key warps", t[first:i], False, None))
                 first = i
     rows.sort(key=lambda row: row[1][:, 0].min())
     print("times in us from the end of the last CTA of the kernel in front; medians over the CTAs that had work")
     print(f"{'#':>3} {'kernel':44s} {'CTAs':>4} {'entered':>8} {'let go':>7} {'inputs in':>9} {'ended':>6} {'last end':>8} {'span':>6}")
     previous_end = None
-    for i, (label, t, is_product) in enumerate(rows):
+    for i, (label, t, is_product, raw) in enumerate(rows):
         busy = t[(t[:, 4] - t[:, 0]) > 1000] if is_product else t[t[:, 2] > -10**12]
         if not len(busy):
             busy = t
@@ -110,6 +111,16 @@ def main() -> None:
             f = lambda x: f"{(float(x) - ref) / 1e3:.2f}"
             print(f"{i:3d} {label:44s} {len(busy):4d} {f(np.median(busy[:, 0])):>8} {f(np.median(busy[:, 2])):>7} "
                   f"{f(np.median(busy[:, 3])):>9} {f(np.median(busy[:, 4])):>6} {f(last):>8} {(last - int(t[:, 0].min())) / 1e3:6.2f}")
+            if args.sections and raw is not None:
+                # warp 0 of every CTA: SM cycles inside the product's loop over weight boxes, by what they were spent on
+                live = raw[(raw[:, 4] - raw[:, 0]) > 1000] if ((raw[:, 4] - raw[:, 0]) > 1000).any() else raw
+                sec, n = live[:, 1], np.maximum(live[:, 3] & 0xFF, 1)
+                wait, load, arm, mma = (sec >> 48) & 0xFFFF, (sec >> 32) & 0xFFFF, (sec >> 16) & 0xFFFF, sec & 0xFFFF
+                loop, meet, whole = live[:, 5] >> 40, (live[:, 5] >> 20) & 0xFFFFF, live[:, 5] & 0xFFFFF
+                m = lambda v: float(np.median(v))
+                print(f"      warp 0: {m(n):.0f} boxes; cycles a box: wait for it {m(wait / n):.0f}, shared loads {m(load / n):.0f}, "
+                      f"next request {m(arm / n):.0f}, products {m(mma / n):.0f}; loop {m(loop):.0f}, to the team's meeting {m(meet):.0f}, "
+                      f"to the end {m(whole):.0f} cycles")
         previous_end = last
     print(f"first entry to last end: {(rows[-1][1][:, 4].max() - rows[0][1][:, 0].min()) / 1e3:.1f} us over {len(rows)} kernels")
 

@@ -327,6 +327,29 @@ def test_paged_attention_tcgen05_finds_one_far_key(far_key):
     torch.testing.assert_close(got, plain, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("rise", [0.02, 0.08, 0.3])
+def test_paged_attention_tcgen05_scores_that_keep_rising(rise):
+    """The tcgen05 kernel keeps its output in tensor memory and rescales a row only when its maximum has risen by more than
+    2^8 since the row's shift was last set.  Here every key scores higher than the one before it, by ``rise`` nats a
+    key: the shift is left behind and follows in jumps (every 277, 69 or 18 keys), several times inside one portion, and the keys just before a jump carry weights of up to 2^8 against the stale shift.  A jump that is missed,
+    scaled wrongly or applied a tile late shows against the plain attention, whose weights fall off over the last few
+    keys only."""
+    H, KV, D, page_size, n, q_len = 4, 2, 64, 16, 1100, 600
+    pool, table, keys, values = make_cache([n], KV, D, page_size, torch.bfloat16, seed=8)
+    direction = torch.nn.functional.normalize(rnd(D, seed=9), dim=0)
+    ramp = torch.arange(n, device=DEV, dtype=torch.float32) * rise  # the score of key j, before the scale by 1/sqrt(D)
+    keys[0][:] = keys[0] * 0.02 + (ramp[:, None, None] * direction) * (D**0.5 / 8.0)
+    fill_pool(pool, table, keys, values, page_size)
+    q = rnd(q_len, H * D, dtype=torch.bfloat16, seed=10, std=0.05)
+    q.view(q_len, H, D)[:] += (direction * 8.0).to(torch.bfloat16)
+    ctx = step_ctx([n], [q_len])
+    kw = dict(num_heads=H, num_kv_heads=KV, head_dim=D, scale=D**-0.5)
+    got = ops().paged_attention(q, pool, table, ctx, **kw).float()
+    ops().check_device_errors()
+    plain = plain_ops.paged_attention(q, pool, table, ctx, **kw).float()
+    torch.testing.assert_close(got, plain, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("far_key,n", [(0, 701), (15, 701), (16, 701), (511, 701), (512, 701), (700, 701), (0, 2101), (1023, 2101),
                                        (1024, 2101), (2100, 2101)])
