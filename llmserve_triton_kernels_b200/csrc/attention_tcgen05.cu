@@ -1,22 +1,23 @@
 // Causal (optionally windowed) grouped-query attention over the paged cache for prompt portions, on the
 // fifth-generation tensor cores: both products of a key tile (scores = Q K^T, output += P V) are
-// tcgen05.mma with their accumulators in tensor memory; queries, keys and values come into shared
-// memory by TMA (128-byte swizzle), page by page through the request's page table.
+// tcgen05.mma with their accumulators AND their A operands (queries, probabilities) in tensor memory; keys and
+// values come into shared memory by TMA (128-byte swizzle), page by page through the request's page table.
 //
 // One CTA computes 128 query tokens of one head against the keys they may see, 64 keys at a time:
-//   warps 0-3 : softmax.  Thread i owns query row i, which is lane i of tensor memory: it reads its 64
-//               scores with tcgen05.ld, keeps the running maximum and sum of the row (no shuffles: the
-//               whole row is the thread's) and writes the probabilities as bfloat16 into shared memory in
-//               the layout the next product reads.  The output accumulates in tensor memory over all key tiles;
-//               a row's shift follows its maximum only when the maximum has risen by more than 2^8, and only then
-//               does the warp rescale its 32 rows of the output (load, multiply, store).
-//   warp 4    : producer.  Looks up pages (32 entries of the page table per load, handed round by
-//               shuffles) and issues one TMA box per page for keys and one for values, each from a lane
-//               of its own, into a ring of STAGES tiles.
-//   warp 5    : one thread issues the products; the warp owns the allocation of tensor memory.
-// Scores and probabilities have two buffers each: the scores of tile j+1 are computed while the softmax of
-// tile j runs, and the second product of tile j runs while the softmax of tile j+1 does.  Two CTAs share an SM.  Softmax, running sums and the output are
-// 32-bit; probabilities are rounded to bfloat16 for the second product, as in the mma.sync kernel.
+//   warps 0-3 : softmax.  Thread i owns query row i, which is lane i of tensor memory: it puts its queries there
+//               once, reads its 64 scores with tcgen05.ld, keeps the running maximum and sum of the row (no
+//               shuffles: the whole row is the thread's) and stores the probabilities as bfloat16 into its lane,
+//               where the second product reads them.  The output accumulates in tensor memory over all key
+//               tiles; a row's shift follows its maximum only when the maximum has risen by more than 2^8, and
+//               only then does the warp rescale its 32 rows of the output (load, multiply, store).
+//   warps 4, 6: producers of keys and of values.  Each looks up pages (32 entries of the page table per load,
+//               handed round by shuffles) and issues one TMA box per page, each from a lane of its own, into
+//               rings of STAGES tiles; a stage of keys is free as soon as its scores are computed.
+//   warps 5, 7: one thread of each issues a product (5 the scores, 7 the output); warp 5 owns the allocation of
+//               tensor memory.
+// Scores have two buffers: those of tile j+1 are computed while the softmax of tile j runs, and the second
+// product of tile j runs while the softmax of tile j+1 does.  Two CTAs share an SM.  Softmax, running sums and
+// the output are 32-bit; probabilities are rounded to bfloat16 for the second product, as in the mma.sync kernel.
 //
 // Keys past a request's length inside its last page, and pages outside the range a CTA needs, are
 // never looked at: a score outside [window start, position] is -inf before the exponential, and the
@@ -27,16 +28,21 @@
 // Every mbarrier wait is bounded; a wait that gives up sets *error_flag, the roles leave their loops,
 // tensor memory is freed and the kernel returns.
 #include "attention_tile.cuh"
+#ifdef ATT_PROF
+#include <cstdio>
+#endif
 #include "umma.cuh"
 
 namespace {
 
 using attn::AttnParams;
 
-constexpr int BM = 128, BN = 64, HD = 64, STAGES = 3, THREADS = 192;
-constexpr int Q_BYTES = BM * HD * 2, P_BYTES = BM * BN * 2, K_BYTES = BN * HD * 2, STAGE_BYTES = 2 * K_BYTES;
+constexpr int BM = 128, BN = 64, HD = 64, STAGES = 3, THREADS = 256;
+constexpr int K_BYTES = BN * HD * 2, STAGE_BYTES = 2 * K_BYTES;
 constexpr float LAZY = 8.f;  // log2 of how far a row's maximum may rise before its shift follows
-constexpr int TMEM_COLS = 256;  // two tiles of scores in columns [0, 64) and [64, 128), the output in [128, 192)
+// Tensor memory: two tiles of scores in columns [0, 64) and [64, 128); the output in [128, 192); the queries in
+// [192, 224) and a tile's probabilities in [224, 256), two bfloat16 to a column.
+constexpr int TMEM_COLS = 256, O_COL = 2 * BN, Q_COL = 2 * BN + HD, P_COL = Q_COL + HD / 2;
 
 struct TcParams {
     AttnParams a;
@@ -48,7 +54,7 @@ struct TcParams {
 __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) { tma::mbar_arrive(bar); }
 
 __global__ void __launch_bounds__(THREADS, 2)
-attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kvmap) {
+attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap kvmap) {
     const AttnParams& p = tp.a;
     const int head = blockIdx.x, kvh = head / p.G;
     const int r = blockIdx.y / tp.tiles_per_request;
@@ -68,31 +74,30 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_s = base;
-    unsigned char* p_s = base + Q_BYTES;
-    unsigned char* kv_s = p_s + 2 * P_BYTES;  // [STAGES][keys | values]; before it, two tiles of probabilities
-    __shared__ __align__(8) unsigned long long q_full, kv_full[STAGES], kv_empty[STAGES], s_full[2], s_empty[2], p_full[2], o_full;
+    unsigned char* kv_s = base;  // [STAGES][keys | values]
+    __shared__ __align__(8) unsigned long long q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], s_empty[2], p_full, o_full;
     __shared__ unsigned tmem_base;
     __shared__ int gave_up;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        tma::mbar_init(&q_full, 1);
+        tma::mbar_init(&q_full, 4);
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) {
-            tma::mbar_init(&kv_full[s], 1);
-            tma::mbar_init(&kv_empty[s], 1);
+            tma::mbar_init(&k_full[s], 1);
+            tma::mbar_init(&k_empty[s], 1);
+            tma::mbar_init(&v_full[s], 1);
+            tma::mbar_init(&v_empty[s], 1);
         }
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
             tma::mbar_init(&s_full[b], 1);
             tma::mbar_init(&s_empty[b], 4);
-            tma::mbar_init(&p_full[b], 4);
         }
+        tma::mbar_init(&p_full, 4);
         tma::mbar_init(&o_full, 1);
         gave_up = 0;
         tma::mbar_fence_init();
-        tma::prefetch_map(&qmap);
         tma::prefetch_map(&kvmap);
     }
     if (warp == 5) {
@@ -110,18 +115,20 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
         if (tp.error_flag) atomicExch(tp.error_flag, 1);
     };
 
-    if (warp == 4) {
-        // ---- producer ----
+    if (warp == 4 || warp == 6) {
+        // ---- producers: warp 4 brings the queries and the keys, warp 6 the values ----
+        // Keys and values have rings of their own: a stage of keys is free again as soon as its scores are computed,
+        // which is more than a tile before the values of the same tile have been used, so the keys of three tiles on
+        // are requested that much earlier (with one ring for both, the scores waited for their keys).
+        const bool is_v = warp == 6;
+        unsigned long long* full = is_v ? v_full : k_full;
+        unsigned long long* empty = is_v ? v_empty : k_empty;
         const int ps = p.page_size, pages_per_tile = BN / ps;
         const int lp_lo = key_lo / ps, lp_hi = key_hi / ps;
         const int* table = p.page_table + (size_t)r * p.table_width;
-        if (lane == 0) {
-            tma::mbar_expect_tx(&q_full, Q_BYTES);
-            tma::load_2d(q_s, &qmap, head * HD, q_begin + row0, &q_full);
-        }
-        // One box per page and per kind (keys, values): 2 * pages_per_tile boxes a tile, each issued by a lane of
-        // its own (a thread's TMA instructions follow one another slowly; several threads' overlap).  The page
-        // table is read 32 entries at a time; a page outside the needed range is replaced by one inside it.
+        // One box per page, each issued by a lane of its own (a thread's TMA instructions follow one another slowly;
+        // several threads' overlap).  The page table is read 32 entries at a time; a page outside the needed range is
+        // replaced by one inside it.
         const int first_page = t_begin * pages_per_tile;
         int my_page = 0, loaded_from = -32;
         bool alive = true;
@@ -132,59 +139,60 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                 my_page = table[min(max(first_page + idx0 + lane, lp_lo), lp_hi)];
             }
             if (lane == 0) {
-                if (gave_up || (j >= STAGES && !tma::mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1))) {
+                if (gave_up || (j >= STAGES && !tma::mbar_wait(&empty[s], ((j / STAGES) - 1) & 1))) {
                     if (!gave_up) fail();
                     alive = false;
                 } else {
-                    tma::mbar_expect_tx(&kv_full[s], STAGE_BYTES);
+                    tma::mbar_expect_tx(&full[s], K_BYTES);
                 }
             }
             alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
-            const int in_tile = lane >> 1, is_v = lane & 1;
-            const int page = __shfl_sync(0xffffffffu, my_page, (idx0 - loaded_from + in_tile) & 31);
-            if (alive && in_tile < pages_per_tile) {
-                unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (size_t)is_v * K_BYTES + (size_t)in_tile * ps * (HD * 2);
-                tma::load_2d(dst, &kvmap, 0, ((page * 2 + is_v) * p.KV + kvh) * ps, &kv_full[s]);
+            const int page = __shfl_sync(0xffffffffu, my_page, (idx0 - loaded_from + lane) & 31);
+            if (alive && lane < pages_per_tile) {
+                unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (size_t)is_v * K_BYTES + (size_t)lane * ps * (HD * 2);
+                tma::load_2d(dst, &kvmap, 0, ((page * 2 + (int)is_v) * p.KV + kvh) * ps, &full[s]);
             }
         }
     } else if (warp == 5) {
-        // ---- issuer of the products ----
+        // ---- issuer of the scores: S[j % 2] = Q K_j^T, as soon as the keys are there and the buffer has been read ----
+        // One thread spends about a hundred cycles on every tcgen05.mma it issues and sixty on a commit, so the two
+        // products of a tile have an issuing thread each: together in one thread they, not the softmax, set the pace.
+        // Both products take their A operand (queries, probabilities) from tensor memory: read from shared memory, a
+        // 128 x 64 x 16 step would want 6 KB in 32 cycles, more than shared memory gives.
         if (lane == 0) {
-            constexpr unsigned IDESC_QK = umma::idesc_bf16(BM, BN, false), IDESC_PV = umma::idesc_bf16(BM, HD, true);
-            const unsigned o_tmem = tmem_base + 2 * BN;
-            const unsigned long long q_desc = umma::desc_sw128(q_s);
-            auto scores = [&](int j) {  // S[j % 2] = Q K_j^T
+            constexpr unsigned IDESC_QK = umma::idesc_bf16(BM, BN, false);
+            const unsigned q_tmem = tmem_base + Q_COL;
+            bool ok = tma::mbar_wait(&q_full, 0);
+            for (int j = 0; j < n_tiles && ok && !gave_up; ++j) {
+                ok = tma::mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1) && (j < 2 || tma::mbar_wait(&s_empty[j & 1], ((j >> 1) - 1) & 1));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const unsigned long long k_desc = umma::desc_sw128(kv_s + (size_t)(j % STAGES) * STAGE_BYTES);
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) umma::mma_bf16(tmem_base + (j & 1) * BN, q_desc + 2 * k, k_desc + 2 * k, IDESC_QK, k != 0);
+                for (int k = 0; k < HD / 16; ++k) umma::mma_bf16_ts(tmem_base + (j & 1) * BN, q_tmem + 8 * k, k_desc + 2 * k, IDESC_QK, k != 0);
                 umma::commit(&s_full[j & 1]);
-            };
-            bool ok = tma::mbar_wait(&q_full, 0) && tma::mbar_wait(&kv_full[0], 0);
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                scores(0);
+                umma::commit(&k_empty[j % STAGES]);
             }
+            if (!ok) fail();
+        }
+    } else if (warp == 7) {
+        // ---- issuer of the second product: O += P_j V_j, as soon as the probabilities and the values are there ----
+        if (lane == 0) {
+            constexpr unsigned IDESC_PV = umma::idesc_bf16(BM, HD, true);
+            const unsigned o_tmem = tmem_base + O_COL, p_tmem = tmem_base + P_COL;
+            bool ok = true;
             for (int j = 0; j < n_tiles && ok && !gave_up; ++j) {
                 const int s = j % STAGES;
-                if (j + 1 < n_tiles) {
-                    // the scores of the next tile, as soon as its keys are there and the scores two tiles back have been read
-                    ok = tma::mbar_wait(&kv_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1) &&
-                         (j < 1 || tma::mbar_wait(&s_empty[(j + 1) & 1], (((j + 1) >> 1) - 1) & 1));
-                    if (!ok) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    scores(j + 1);
-                }
-                ok = tma::mbar_wait(&p_full[j & 1], (j >> 1) & 1);
+                ok = tma::mbar_wait(&v_full[s], (j / STAGES) & 1) && tma::mbar_wait(&p_full, j & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 // the values lie [key][d]: B with N contiguous; 16 keys are two atoms of 8 rows, 2048 bytes further per step
-                const unsigned long long p_desc = umma::desc_sw128(p_s + (size_t)(j & 1) * P_BYTES);
                 const unsigned long long v_desc = umma::desc_sw128(kv_s + (size_t)s * STAGE_BYTES + K_BYTES, 1024 >> 4);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)  // the output accumulates over the tiles
-                    umma::mma_bf16(o_tmem, p_desc + 2 * k, v_desc + (2048 >> 4) * k, IDESC_PV, k != 0 || j != 0);
+                    umma::mma_bf16_ts(o_tmem, p_tmem + 8 * k, v_desc + (2048 >> 4) * k, IDESC_PV, k != 0 || j != 0);
                 umma::commit(&o_full);
-                umma::commit(&kv_empty[s]);
+                umma::commit(&v_empty[s]);
             }
             if (!ok) fail();
         }
@@ -197,10 +205,30 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
         const unsigned lane_base = tmem_base + ((unsigned)(warp * 32) << 16);
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        const unsigned o_taddr = lane_base + 2 * BN;
+        const unsigned o_taddr = lane_base + O_COL;
+        {   // the row's queries, as they lie in memory (two to a word), into the row's lane of tensor memory
+            unsigned qw[32];
+            const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + tok) * p.q_stride + (size_t)head * HD);
+#pragma unroll
+            for (int c = 0; c < HD / 8; ++c) {
+                const uint4 u = row_ok ? src[c] : make_uint4(0, 0, 0, 0);
+                qw[4 * c] = u.x; qw[4 * c + 1] = u.y; qw[4 * c + 2] = u.z; qw[4 * c + 3] = u.w;
+            }
+            umma::tmem_st32(lane_base + Q_COL, qw);
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&q_full);
+        }
+#ifdef ATT_PROF
+        long long pc[6] = {0, 0, 0, 0, 0, 0}, c0 = clock64(), c1;
+#define PH(i) { c1 = clock64(); pc[i] += c1 - c0; c0 = c1; }
+#else
+#define PH(i)
+#endif
         for (int j = 0; j < n_tiles; ++j) {
             const int key_base = (t_begin + j) * BN;
             ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&s_full[j & 1], (j >> 1) & 1));
+            PH(0)
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const bool whole = key_base + BN - 1 <= tile_pos_min && key_base >= tile_lo_max && rows_here == BM;
@@ -212,7 +240,8 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             umma::tmem_ld64(lane_base + (j & 1) * BN, v);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[j & 1]);
+            if (lane == 0) mbar_arrive(&s_empty[j & 1]);  // the buffer may take the scores two tiles on
+            PH(1)
             // the row's maximum (four chains, so that the comparisons do not wait for one another; the scale is
             // positive and is applied to the maximum alone)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -239,9 +268,10 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             const float alpha = attn::fast_exp2(m_run - m_use);  // 1 where the shift stays
             const bool rescale = grow && m_run != -INFINITY;  // (a row that has seen no key yet has an output of zeros)
             m_run = m_new;
-            // the probabilities (a masked score is -inf: its probability is exactly 0), into shared memory as the
-            // second product's A (K-major, 128-byte swizzle: row `row`, 16-byte piece c at c ^ (row % 8))
-            unsigned char* p_tile = p_s + (size_t)(j & 1) * P_BYTES;
+            PH(2)
+            // the probabilities (a masked score is -inf: its probability is exactly 0), two to a word: the second
+            // product's A operand, stored into the row's lane of tensor memory once the product before has read its own
+            unsigned pw[BN / 2];
             float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};  // four chains, two per packed add
             const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
 #pragma unroll
@@ -253,25 +283,25 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                     v[c * 8 + i + 1] = attn::fast_exp2(x.y);
                     sum2[(i >> 1) & 1] = __fadd2_rn(sum2[(i >> 1) & 1], make_float2(v[c * 8 + i], v[c * 8 + i + 1]));
                 }
-                uint4 u;
-                u.x = attn::pack_bf16(v[c * 8], v[c * 8 + 1]);
-                u.y = attn::pack_bf16(v[c * 8 + 2], v[c * 8 + 3]);
-                u.z = attn::pack_bf16(v[c * 8 + 4], v[c * 8 + 5]);
-                u.w = attn::pack_bf16(v[c * 8 + 6], v[c * 8 + 7]);
-                *reinterpret_cast<uint4*>(p_tile + row * 128 + ((c ^ (row & 7)) << 4)) = u;
+                pw[4 * c] = attn::pack_bf16(v[c * 8], v[c * 8 + 1]);
+                pw[4 * c + 1] = attn::pack_bf16(v[c * 8 + 2], v[c * 8 + 3]);
+                pw[4 * c + 2] = attn::pack_bf16(v[c * 8 + 4], v[c * 8 + 5]);
+                pw[4 * c + 3] = attn::pack_bf16(v[c * 8 + 6], v[c * 8 + 7]);
             }
             l_run = l_run * alpha + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
+            PH(3)
             // The product of the tile before has had this tile's softmax to finish in.  Its barrier is waited for at
             // every tile, needed or not: a phase is told from the one two before it only by its parity, and a warp
             // that skipped phases could take an old one for the one it wants.
+            // It has also read the probabilities of the tile before, whose place this tile's take below.
             if (j > 0) {
                 ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, (j - 1) & 1));
                 if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             }
             if (__any_sync(0xffffffffu, rescale)) {
                 // this tile's product must not start before the rows are rescaled: the issuer learns of the
                 // probabilities only below
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 float o[HD];
                 umma::tmem_ld64(o_taddr, o);
                 const float a = rescale ? alpha : 1.f;
@@ -284,11 +314,19 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                 }
                 umma::tmem_st64(o_taddr, o);
             }
+            PH(4)
+            umma::tmem_st32(lane_base + P_COL, pw);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[j & 1]);
+            if (lane == 0) mbar_arrive(&p_full);
+            PH(5)
         }
+#ifdef ATT_PROF
+        if (threadIdx.x == 0 && blockIdx.x == 3 && (blockIdx.y % 5) == 0)
+            printf("tile %d n_tiles %d: per tile wait_s %lld ld %lld max %lld exp+store %lld o_wait %lld arrive %lld total %lld\n", tile, n_tiles,
+                   pc[0] / n_tiles, pc[1] / n_tiles, pc[2] / n_tiles, pc[3] / n_tiles, pc[4] / n_tiles, pc[5] / n_tiles,
+                   (pc[0] + pc[1] + pc[2] + pc[3] + pc[4] + pc[5]) / n_tiles);
+#endif
         float o[HD];
         if (ok && n_tiles > 0) {
             ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, (n_tiles - 1) & 1));
@@ -316,8 +354,10 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
     }
     // after a failed wait, copies may still be on their way into this CTA's shared memory: wait for them (bounded)
     if (gave_up && threadIdx.x == 0) {
-        tma::mbar_wait(&q_full, 0);
-        for (int j = max(0, n_tiles - STAGES); j < n_tiles; ++j) tma::mbar_wait(&kv_full[j % STAGES], (j / STAGES) & 1);
+        for (int j = max(0, n_tiles - STAGES); j < n_tiles; ++j) {
+            tma::mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1);
+            tma::mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1);
+        }
     }
     // everyone is done with tensor memory: the allocating warp gives it back
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -348,10 +388,11 @@ LLM_EXPORT int llm_attention_tcgen05(const void* q, int q_stride, void* out, int
         return LLM_ERR_UNSUPPORTED;
     const long long kv_rows = pool_pages * 2 * KV * page_size;
     if (kv_rows <= 0 || kv_rows > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
-    const CUtensorMap* qmap = tma::cached_map_2d_bf16(q, (uint64_t)n_tokens, (uint64_t)H * HD, (uint64_t)q_stride, BM, HD, CU_TENSOR_MAP_SWIZZLE_128B);
     const CUtensorMap* kvmap = tma::cached_map_2d_bf16(pool, (uint64_t)kv_rows, HD, HD, (uint32_t)page_size, HD, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (!qmap || !kvmap) return LLM_ERR_UNSUPPORTED;
+    if (!kvmap) return LLM_ERR_UNSUPPORTED;
     TcParams tp = {};
+    tp.a.q = (const __nv_bfloat16*)q;
+    tp.a.q_stride = q_stride;
     tp.a.out = (__nv_bfloat16*)out;
     tp.a.out_stride = out_stride;
     tp.a.page_table = page_table;
@@ -369,12 +410,12 @@ LLM_EXPORT int llm_attention_tcgen05(const void* q, int q_stride, void* out, int
     tp.error_flag = error_flag;
     const long long y = (long long)requests * tp.tiles_per_request;
     if (y > 65535) return LLM_ERR_UNSUPPORTED;
-    constexpr size_t smem = 1024 + Q_BYTES + 2 * P_BYTES + (size_t)STAGES * STAGE_BYTES;
+    constexpr size_t smem = 1024 + (size_t)STAGES * STAGE_BYTES;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return launch_pdl(attention_tcgen05_kernel, dim3((unsigned)H, (unsigned)y), dim3(THREADS), smem, stream, tp, *qmap, *kvmap);
+    return launch_pdl(attention_tcgen05_kernel, dim3((unsigned)H, (unsigned)y), dim3(THREADS), smem, stream, tp, *kvmap);
 }
