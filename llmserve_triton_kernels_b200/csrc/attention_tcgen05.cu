@@ -37,12 +37,27 @@ namespace {
 
 using attn::AttnParams;
 
-constexpr int BM = 128, BN = 64, HD = 64, STAGES = 3, THREADS = 256;
-constexpr int K_BYTES = BN * HD * 2, STAGE_BYTES = 2 * K_BYTES;
+constexpr int BM = 128, BN = 64, THREADS = 256, TMEM_COLS = 256;
 constexpr float LAZY = 8.f;  // log2 of how far a row's maximum may rise before its shift follows
-// Tensor memory: two tiles of scores in columns [0, 64) and [64, 128); the output in [128, 192); the queries in
-// [192, 224) and a tile's probabilities in [224, 256), two bfloat16 to a column.
-constexpr int TMEM_COLS = 256, O_COL = 2 * BN, Q_COL = 2 * BN + HD, P_COL = Q_COL + HD / 2;
+
+// What differs between the head sizes.  256 columns of tensor memory a CTA (two CTAs share an SM's 512), two
+// bfloat16 to a column where an A operand lies:
+//   head size 64 : two tiles of scores [0, 64), [64, 128); the output [128, 192); the queries [192, 224); a tile's
+//                  probabilities [224, 256).  Three stages of keys and of values (16 KB a stage): 49 KB of shared memory.
+//   head size 128: one tile of scores [0, 64); the output [64, 192); probabilities [192, 224).  The queries do not fit
+//                  and stay in shared memory (32 KB, the first product's A operand from there); two stages of keys
+//                  and of values (32 KB a stage): 97 KB.  With one buffer of scores the product of tile j+1 starts when
+//                  the softmax has read tile j; the other CTA of the SM fills the gap.
+template <int HD>
+struct Shape {
+    static constexpr bool Q_IN_TMEM = HD == 64;
+    static constexpr int S_BUFFERS = HD == 64 ? 2 : 1, STAGES = HD == 64 ? 3 : 2;
+    static constexpr int O_COL = S_BUFFERS * BN, Q_COL = O_COL + HD, P_COL = Q_IN_TMEM ? Q_COL + HD / 2 : O_COL + HD;
+    static constexpr int HALVES = HD / 64;                // 64-wide pieces of a row of keys, values, queries: one TMA box each
+    static constexpr int K_BYTES = BN * HD * 2, STAGE_BYTES = 2 * K_BYTES, Q_BYTES = Q_IN_TMEM ? 0 : BM * HD * 2;
+    static constexpr size_t SMEM = 1024 + (size_t)Q_BYTES + (size_t)STAGES * STAGE_BYTES;
+    static_assert(P_COL + BN / 2 <= TMEM_COLS, "tensor memory");
+};
 
 struct TcParams {
     AttnParams a;
@@ -53,8 +68,12 @@ struct TcParams {
 
 __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) { tma::mbar_arrive(bar); }
 
+template <int HD>
 __global__ void __launch_bounds__(THREADS, 2)
-attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap kvmap) {
+attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kvmap) {
+    using Sh = Shape<HD>;
+    constexpr int STAGES = Sh::STAGES, NBUF = Sh::S_BUFFERS, K_BYTES = Sh::K_BYTES, STAGE_BYTES = Sh::STAGE_BYTES, HALVES = Sh::HALVES;
+    constexpr int O_COL = Sh::O_COL, Q_COL = Sh::Q_COL, P_COL = Sh::P_COL;
     const AttnParams& p = tp.a;
     const int head = blockIdx.x, kvh = head / p.G;
     const int r = blockIdx.y / tp.tiles_per_request;
@@ -74,14 +93,15 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* kv_s = base;  // [STAGES][keys | values]
-    __shared__ __align__(8) unsigned long long q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], s_empty[2], p_full, o_full;
+    unsigned char* q_s = base;                // [halves][128 rows][64]: head size 128 only
+    unsigned char* kv_s = base + Sh::Q_BYTES;  // [STAGES][keys | values], each [halves][64 keys][64]
+    __shared__ __align__(8) unsigned long long q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[NBUF], s_empty[NBUF], p_full, o_full;
     __shared__ unsigned tmem_base;
     __shared__ int gave_up;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        tma::mbar_init(&q_full, 4);
+        tma::mbar_init(&q_full, Sh::Q_IN_TMEM ? 4 : 1);
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) {
             tma::mbar_init(&k_full[s], 1);
@@ -90,7 +110,7 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             tma::mbar_init(&v_empty[s], 1);
         }
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < NBUF; ++b) {
             tma::mbar_init(&s_full[b], 1);
             tma::mbar_init(&s_empty[b], 4);
         }
@@ -99,6 +119,7 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
         gave_up = 0;
         tma::mbar_fence_init();
         tma::prefetch_map(&kvmap);
+        if (!Sh::Q_IN_TMEM) tma::prefetch_map(&qmap);
     }
     if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tma::smem_addr(&tmem_base)), "n"(TMEM_COLS) : "memory");
@@ -126,7 +147,12 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
         const int ps = p.page_size, pages_per_tile = BN / ps;
         const int lp_lo = key_lo / ps, lp_hi = key_hi / ps;
         const int* table = p.page_table + (size_t)r * p.table_width;
-        // One box per page, each issued by a lane of its own (a thread's TMA instructions follow one another slowly;
+        if (!Sh::Q_IN_TMEM && !is_v && lane == 0) {
+            tma::mbar_expect_tx(&q_full, Sh::Q_BYTES);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) tma::load_2d(q_s + (size_t)h * (BM * 128), &qmap, head * HD + h * 64, q_begin + row0, &q_full);
+        }
+        // One box per page and 64-wide piece, each issued by a lane of its own (a thread's TMA instructions follow one another slowly;
         // several threads' overlap).  The page table is read 32 entries at a time; a page outside the needed range is
         // replaced by one inside it.
         const int first_page = t_begin * pages_per_tile;
@@ -147,10 +173,11 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                 }
             }
             alive = __shfl_sync(0xffffffffu, (int)alive, 0) != 0;
-            const int page = __shfl_sync(0xffffffffu, my_page, (idx0 - loaded_from + lane) & 31);
-            if (alive && lane < pages_per_tile) {
-                unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (size_t)is_v * K_BYTES + (size_t)lane * ps * (HD * 2);
-                tma::load_2d(dst, &kvmap, 0, ((page * 2 + (int)is_v) * p.KV + kvh) * ps, &full[s]);
+            const int in_tile = lane / HALVES, half = lane % HALVES;
+            const int page = __shfl_sync(0xffffffffu, my_page, (idx0 - loaded_from + in_tile) & 31);
+            if (alive && in_tile < pages_per_tile) {
+                unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (size_t)is_v * K_BYTES + (size_t)half * (BN * 128) + (size_t)in_tile * ps * 128;
+                tma::load_2d(dst, &kvmap, half * 64, ((page * 2 + (int)is_v) * p.KV + kvh) * ps, &full[s]);
             }
         }
     } else if (warp == 5) {
@@ -164,13 +191,22 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             const unsigned q_tmem = tmem_base + Q_COL;
             bool ok = tma::mbar_wait(&q_full, 0);
             for (int j = 0; j < n_tiles && ok && !gave_up; ++j) {
-                ok = tma::mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1) && (j < 2 || tma::mbar_wait(&s_empty[j & 1], ((j >> 1) - 1) & 1));
+                ok = tma::mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1) &&
+                     (j < NBUF || tma::mbar_wait(&s_empty[j % NBUF], ((j / NBUF) - 1) & 1));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned long long k_desc = umma::desc_sw128(kv_s + (size_t)(j % STAGES) * STAGE_BYTES);
+                const unsigned char* k_tile = kv_s + (size_t)(j % STAGES) * STAGE_BYTES;
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) umma::mma_bf16_ts(tmem_base + (j & 1) * BN, q_tmem + 8 * k, k_desc + 2 * k, IDESC_QK, k != 0);
-                umma::commit(&s_full[j & 1]);
+                for (int k = 0; k < HD / 16; ++k) {  // 16 of the head's lanes a step: piece k / 4 of the tile, 32 bytes further per step
+                    const unsigned long long k_desc = umma::desc_sw128(k_tile + (size_t)(k / 4) * (BN * 128)) + 2 * (k % 4);
+                    if constexpr (Sh::Q_IN_TMEM) {
+                        umma::mma_bf16_ts(tmem_base + (j % NBUF) * BN, q_tmem + 8 * k, k_desc, IDESC_QK, k != 0);
+                    } else {
+                        const unsigned long long q_desc = umma::desc_sw128(q_s + (size_t)(k / 4) * (BM * 128)) + 2 * (k % 4);
+                        umma::mma_bf16(tmem_base + (j % NBUF) * BN, q_desc, k_desc, IDESC_QK, k != 0);
+                    }
+                }
+                umma::commit(&s_full[j % NBUF]);
                 umma::commit(&k_empty[j % STAGES]);
             }
             if (!ok) fail();
@@ -187,7 +223,8 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 // the values lie [key][d]: B with N contiguous; 16 keys are two atoms of 8 rows, 2048 bytes further per step
-                const unsigned long long v_desc = umma::desc_sw128(kv_s + (size_t)s * STAGE_BYTES + K_BYTES, 1024 >> 4);
+                // (a head of 128 lanes is two such pieces side by side, BN * 128 bytes apart: the leading offset)
+                const unsigned long long v_desc = umma::desc_sw128(kv_s + (size_t)s * STAGE_BYTES + K_BYTES, (HALVES > 1 ? BN * 128 : 1024) >> 4);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)  // the output accumulates over the tiles
                     umma::mma_bf16_ts(o_tmem, p_tmem + 8 * k, v_desc + (2048 >> 4) * k, IDESC_PV, k != 0 || j != 0);
@@ -206,7 +243,7 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         const unsigned o_taddr = lane_base + O_COL;
-        {   // the row's queries, as they lie in memory (two to a word), into the row's lane of tensor memory
+        if constexpr (Sh::Q_IN_TMEM) {  // the row's queries, as they lie in memory (two to a word), into the row's lane of tensor memory
             unsigned qw[32];
             const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q_begin + tok) * p.q_stride + (size_t)head * HD);
 #pragma unroll
@@ -227,7 +264,7 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
 #endif
         for (int j = 0; j < n_tiles; ++j) {
             const int key_base = (t_begin + j) * BN;
-            ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&s_full[j & 1], (j >> 1) & 1));
+            ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&s_full[j % NBUF], (j / NBUF) & 1));
             PH(0)
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -237,10 +274,10 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             // the row's 64 scores in one load; once they are in registers the buffer may take the scores two tiles on
             static_assert(BN == 64, "the softmax reads a tile's scores with one 64-column load");
             float v[BN];
-            umma::tmem_ld64(lane_base + (j & 1) * BN, v);
+            umma::tmem_ld64(lane_base + (j % NBUF) * BN, v);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[j & 1]);  // the buffer may take the scores two tiles on
+            if (lane == 0) mbar_arrive(&s_empty[j % NBUF]);  // the buffer may take the scores of a later tile
             PH(1)
             // the row's maximum (four chains, so that the comparisons do not wait for one another; the scale is
             // positive and is applied to the maximum alone)
@@ -302,17 +339,20 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
             if (__any_sync(0xffffffffu, rescale)) {
                 // this tile's product must not start before the rows are rescaled: the issuer learns of the
                 // probabilities only below
-                float o[HD];
-                umma::tmem_ld64(o_taddr, o);
                 const float a = rescale ? alpha : 1.f;
                 const float2 a2 = make_float2(a, a);
+#pragma unroll 1
+                for (int h = 0; h < HALVES; ++h) {
+                    float o[64];
+                    umma::tmem_ld64(o_taddr + 64 * h, o);
 #pragma unroll
-                for (int i = 0; i < HD; i += 2) {
-                    const float2 r = __fmul2_rn(make_float2(o[i], o[i + 1]), a2);
-                    o[i] = r.x;
-                    o[i + 1] = r.y;
+                    for (int i = 0; i < 64; i += 2) {
+                        const float2 r = __fmul2_rn(make_float2(o[i], o[i + 1]), a2);
+                        o[i] = r.x;
+                        o[i + 1] = r.y;
+                    }
+                    umma::tmem_st64(o_taddr + 64 * h, o);
                 }
-                umma::tmem_st64(o_taddr, o);
             }
             PH(4)
             umma::tmem_st32(lane_base + P_COL, pw);
@@ -327,28 +367,28 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
                    pc[0] / n_tiles, pc[1] / n_tiles, pc[2] / n_tiles, pc[3] / n_tiles, pc[4] / n_tiles, pc[5] / n_tiles,
                    (pc[0] + pc[1] + pc[2] + pc[3] + pc[4] + pc[5]) / n_tiles);
 #endif
-        float o[HD];
-        if (ok && n_tiles > 0) {
-            ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, (n_tiles - 1) & 1));
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                static_assert(HD == 64, "the output is read with one 64-column load");
-                umma::tmem_ld64(o_taddr, o);
-            }
-        }
+        if (ok && n_tiles > 0) ok = __all_sync(0xffffffffu, !gave_up && tma::mbar_wait(&o_full, (n_tiles - 1) & 1));
         if (!ok) {
             if (lane == 0) fail();
-        } else if (row_ok && n_tiles > 0) {
+        } else if (n_tiles > 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = 1.f / l_run;
             __nv_bfloat16* dst = p.out + (size_t)(q_begin + tok) * p.out_stride + (size_t)head * HD;
+#pragma unroll 1
+            for (int h = 0; h < HALVES; ++h) {
+                float o[64];
+                umma::tmem_ld64(o_taddr + 64 * h, o);  // (by all lanes of the warp: the load is the warp's)
+                if (row_ok) {
 #pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
-                uint4 u;
-                u.x = attn::pack_bf16(o[c * 8] * inv, o[c * 8 + 1] * inv);
-                u.y = attn::pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-                u.z = attn::pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
-                u.w = attn::pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-                *reinterpret_cast<uint4*>(dst + c * 8) = u;
+                    for (int c = 0; c < 8; ++c) {
+                        uint4 u;
+                        u.x = attn::pack_bf16(o[c * 8] * inv, o[c * 8 + 1] * inv);
+                        u.y = attn::pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+                        u.z = attn::pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
+                        u.w = attn::pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + 64 * h + c * 8) = u;
+                    }
+                }
             }
         }
     }
@@ -373,23 +413,41 @@ attention_tcgen05_kernel(const TcParams tp, const __grid_constant__ CUtensorMap 
 // The fewest tokens a request must bring for this kernel to take it (its CTAs are 128 tokens of one head).
 LLM_EXPORT int llm_attention_tcgen05_min_tokens() { return 128; }
 
+namespace {
+template <int HD>
+int launch_tcgen05(const TcParams& tp, const void* q, int q_stride, int n_tokens, const void* pool, long long kv_rows, int page_size,
+                   unsigned grid_y, cudaStream_t stream) {
+    using Sh = Shape<HD>;
+    // one box of keys or values: a page's rows, 64 of the head's lanes; one box of queries: 128 tokens, 64 lanes of a head
+    const CUtensorMap* kvmap = tma::cached_map_2d_bf16(pool, (uint64_t)kv_rows, HD, HD, (uint32_t)page_size, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    const CUtensorMap* qmap = Sh::Q_IN_TMEM ? kvmap
+                                            : tma::cached_map_2d_bf16(q, (uint64_t)n_tokens, (uint64_t)tp.a.H * HD, (uint64_t)q_stride, BM, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!kvmap || !qmap) return LLM_ERR_UNSUPPORTED;
+    static bool configured = false;  // per head size
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return launch_pdl(attention_tcgen05_kernel<HD>, dim3((unsigned)tp.a.H, grid_y), dim3(THREADS), Sh::SMEM, stream, tp, *qmap, *kvmap);
+}
+}  // namespace
+
 // Attention of the requests that bring at least min_tokens tokens (others are left untouched: another kernel's).
-// q: bfloat16 rows of q_stride elements that start with the H query heads; out: [tokens, H * 64] with row stride
-// out_stride; pool: one layer's plane [pool_pages, 2, KV, page_size, 64]; max_tokens: the most tokens of any request.
-// Takes head size 64, pages of 8, 16, 32 or 64 keys, 16-byte aligned rows; else LLM_ERR_UNSUPPORTED (nothing ran).
+// q: bfloat16 rows of q_stride elements that start with the H query heads; out: [tokens, H * D] with row stride
+// out_stride; pool: one layer's plane [pool_pages, 2, KV, page_size, D]; max_tokens: the most tokens of any request.
+// Takes head sizes 64 and 128, pages of 8, 16, 32 or 64 keys, 16-byte aligned rows; else LLM_ERR_UNSUPPORTED (nothing ran).
 LLM_EXPORT int llm_attention_tcgen05(const void* q, int q_stride, void* out, int out_stride, const void* pool, long long pool_pages,
                                      const int* page_table, int table_width, const int* cu_tokens, const int* ctx_lens,
                                      int requests, int n_tokens, int H, int KV, int D, int page_size, int window, float scale,
                                      int min_tokens, int max_tokens, int* error_flag, cudaStream_t stream) {
     if (n_tokens <= 0 || requests <= 0 || max_tokens < min_tokens) return 0;
-    if (D != HD || (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)) return LLM_ERR_UNSUPPORTED;
+    if ((D != 64 && D != 128) || (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64)) return LLM_ERR_UNSUPPORTED;
     if (H <= 0 || KV <= 0 || H % KV || table_width <= 0 || min_tokens < 1 || !(scale > 0.f)) return LLM_ERR_BAD_ARGUMENT;
-    if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)pool & 127) || q_stride < H * HD)
+    if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) || ((uintptr_t)pool & 127) || q_stride < H * D)
         return LLM_ERR_UNSUPPORTED;
     const long long kv_rows = pool_pages * 2 * KV * page_size;
     if (kv_rows <= 0 || kv_rows > 0x7fffffffLL) return LLM_ERR_UNSUPPORTED;
-    const CUtensorMap* kvmap = tma::cached_map_2d_bf16(pool, (uint64_t)kv_rows, HD, HD, (uint32_t)page_size, HD, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (!kvmap) return LLM_ERR_UNSUPPORTED;
     TcParams tp = {};
     tp.a.q = (const __nv_bfloat16*)q;
     tp.a.q_stride = q_stride;
@@ -410,12 +468,6 @@ LLM_EXPORT int llm_attention_tcgen05(const void* q, int q_stride, void* out, int
     tp.error_flag = error_flag;
     const long long y = (long long)requests * tp.tiles_per_request;
     if (y > 65535) return LLM_ERR_UNSUPPORTED;
-    constexpr size_t smem = 1024 + (size_t)STAGES * STAGE_BYTES;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    return launch_pdl(attention_tcgen05_kernel, dim3((unsigned)H, (unsigned)y), dim3(THREADS), smem, stream, tp, *kvmap);
+    return D == 64 ? launch_tcgen05<64>(tp, q, q_stride, n_tokens, pool, kv_rows, page_size, (unsigned)y, stream)
+                   : launch_tcgen05<128>(tp, q, q_stride, n_tokens, pool, kv_rows, page_size, (unsigned)y, stream);
 }

@@ -78,7 +78,7 @@ _SMALL_ROWS = 16  # requests with at most this many (token, group member) rows t
 _SMALL_TILE_KEYS = 128  # keys one CTA of that shape covers per tile
 _SPLIT_SCRATCH_BYTES = 16 << 20  # most scratch memory the split-key attention's partial results may take per call
 _TC_ATTENTION_ENABLED = True
-_TC_ATTENTION_HEAD_DIM = 64
+_TC_ATTENTION_HEAD_DIMS = (64, 128)
 _TC_ATTENTION_PAGE_SIZES = (8, 16, 32, 64)
 _TC_ATTENTION_MIN_TOKENS = 128  # a request with at least this many tokens in the step: attention on tcgen05
 _TCGEN05_MIN_ROWS = 128  # from this many rows a bfloat16 product runs on tcgen05 with TMA-fed tiles (own kernel)
@@ -600,10 +600,10 @@ def paged_attention(
     out = torch.empty((n, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     if qkv.dtype == torch.bfloat16 and head_dim in _MMA_HEAD_DIMS and not _FORCE_GENERIC_ATTENTION:
         group = num_heads // num_kv_heads
-        # requests that bring at least 128 tokens: 128-token tiles of one head on tcgen05 (head size 64, pages of 8
-        # to 64 keys); the others: rows of (token, group member) on mma.sync, 64 rows a tile or the split-key shape
+        # requests that bring at least 128 tokens: 128-token tiles of one head on tcgen05 (head sizes 64 and 128, pages
+        # of 8 to 64 keys); the others: rows of (token, group member) on mma.sync, 64 rows a tile or the split-key shape
         tc_min = 0
-        if head_dim == _TC_ATTENTION_HEAD_DIM and pool.shape[3] in _TC_ATTENTION_PAGE_SIZES and _TC_ATTENTION_ENABLED:
+        if head_dim in _TC_ATTENTION_HEAD_DIMS and pool.shape[3] in _TC_ATTENTION_PAGE_SIZES and _TC_ATTENTION_ENABLED:
             tc_min = _TC_ATTENTION_MIN_TOKENS
         num_requests, tc_longest, small, max_rows_large, other_rows = _attention_route(ctx, group, tc_min)
         if tc_longest:

@@ -277,13 +277,13 @@ def _filled(ctx_lens, KV, D, page_size, seed, key_scale=1.0):
     return filled, table, keys, values
 
 
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("H,KV,page_size,window", [(32, 4, 16, None), (8, 8, 8, None), (6, 2, 32, 200), (4, 1, 64, 64), (2, 2, 16, 1),
                                                    (3, 1, 16, 129)])
-def test_paged_attention_tcgen05_portions(H, KV, page_size, window, monkeypatch):
-    """Portions of 128 tokens and more at head size 64 run on tcgen05 (128-token tiles of one head, 64 keys a
+def test_paged_attention_tcgen05_portions(H, KV, page_size, window, D, monkeypatch):
+    """Portions of 128 tokens and more at head sizes 64 and 128 run on tcgen05 (128-token tiles of one head, 64 keys a
     time): whole prompts of exactly one and two tiles, portions behind hundreds of cached tokens, ragged ends,
     windows that end inside a tile, beside short portions and decode tokens that take the other kernels."""
-    D = 64
     ctx_lens, q_lens = [128, 700, 1700, 129, 5, 256, 40], [128, 572, 1000, 129, 1, 256, 40]
     pool, table, _, _ = _filled(ctx_lens, KV, D, page_size, seed=31)
     ctx = step_ctx(ctx_lens, q_lens)
@@ -304,11 +304,12 @@ def test_paged_attention_tcgen05_portions(H, KV, page_size, window, monkeypatch)
     torch.testing.assert_close(got.float(), want.float(), **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("far_key", [0, 63, 64, 499, 500, 563, 564, 627, 628, 899])
-def test_paged_attention_tcgen05_finds_one_far_key(far_key):
+def test_paged_attention_tcgen05_finds_one_far_key(far_key, D):
     """A portion of 400 tokens behind 500 cached ones; one key is made to match every query.  Every token at or
     behind that key must return the key's value, whichever tile, page or stage of the ring the key lies in."""
-    H, KV, D, page_size, n, q_len = 4, 2, 64, 16, 900, 400
+    H, KV, page_size, n, q_len = 4, 2, 16, 900, 400
     pool, table, keys, values = make_cache([n], KV, D, page_size, torch.bfloat16, seed=3)
     direction = torch.nn.functional.normalize(rnd(D, seed=6), dim=0)
     keys[0][:] = keys[0] * 0.05
@@ -327,14 +328,15 @@ def test_paged_attention_tcgen05_finds_one_far_key(far_key):
     torch.testing.assert_close(got, plain, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("rise", [0.02, 0.08, 0.3])
-def test_paged_attention_tcgen05_scores_that_keep_rising(rise):
+def test_paged_attention_tcgen05_scores_that_keep_rising(rise, D):
     """The tcgen05 kernel keeps its output in tensor memory and rescales a row only when its maximum has risen by more than
     2^8 since the row's shift was last set.  Here every key scores higher than the one before it, by ``rise`` nats a
     key: the shift is left behind and follows in jumps (every 277, 69 or 18 keys), several times inside one portion, and the keys just before a jump carry weights of up to 2^8 against the stale shift.  A jump that is missed,
     scaled wrongly or applied a tile late shows against the plain attention, whose weights fall off over the last few
     keys only."""
-    H, KV, D, page_size, n, q_len = 4, 2, 64, 16, 1100, 600
+    H, KV, page_size, n, q_len = 4, 2, 16, 1100, 600
     pool, table, keys, values = make_cache([n], KV, D, page_size, torch.bfloat16, seed=8)
     direction = torch.nn.functional.normalize(rnd(D, seed=9), dim=0)
     ramp = torch.arange(n, device=DEV, dtype=torch.float32) * rise  # the score of key j, before the scale by 1/sqrt(D)
