@@ -103,9 +103,68 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
     }
 }
 
+// The same for rows whose length is a multiple of 4 and at most 8 float4 a thread: the row stays in registers, and all
+// of a thread's loads are asked for before the first is used (the kernel is a chain of trips to L2 otherwise: load, sum,
+// weight, store).  Few threads a row, so that many rows are in flight on an SM.
+template <typename TD, typename TO, int NV>
+__global__ void __launch_bounds__(256) rmsnorm_registers_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                                                const float* __restrict__ weight, float eps,
+                                                                const int* __restrict__ rows, TO* __restrict__ out, int hidden) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    const int o = blockIdx.x, t4 = threadIdx.x * 4, step = blockDim.x * 4;
+    float w[NV][4];
+#pragma unroll
+    for (int j = 0; j < NV; ++j)  // the weights do not depend on the kernel in front
+        if (t4 + j * step < hidden) load4(weight + t4 + j * step, w[j]);
+    pdl_wait();
+    const int r = rows ? rows[o] : o;
+    float* x = resid + (size_t)r * hidden;
+    const TD* d = delta ? delta + (size_t)r * hidden : nullptr;
+    float v[NV][4], dv[NV][4];
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (t4 + j * step < hidden) {
+            load4(x + t4 + j * step, v[j]);
+            if (d) load4(d + t4 + j * step, dv[j]);
+        }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (t4 + j * step < hidden) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (d) v[j][e] += dv[j][e];
+                ss += v[j][e] * v[j][e];
+            }
+        }
+    ss = block_sum(ss, scratch);
+    const float scale = rsqrtf(ss / (float)hidden + eps);
+    TO* y = out + (size_t)o * hidden;
+    const bool write_back = d && !rows;
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+        if (t4 + j * step < hidden) {
+            if (write_back) store4(x + t4 + j * step, v[j]);
+            float n[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) n[e] = v[j][e] * scale * w[j][e];
+            store4(y + t4 + j * step, n);
+        }
+}
+
 template <typename TD, typename TO>
 static int rmsnorm_launch(float* resid, const void* delta, const float* weight, float eps, const int* rows, void* out,
                           int n_out, int hidden, cudaStream_t stream) {
+    if ((hidden & 3) == 0 && hidden <= 8192) {  // the row in registers
+        const int threads = hidden <= 512 ? 32 : (hidden <= 4096 ? 128 : 256), nv = (hidden / 4 + threads - 1) / threads;
+        auto go = [&](auto kernel) {
+            return launch_pdl(kernel, dim3(n_out), dim3(threads), 0, stream, resid, (const TD*)delta, weight, eps, rows, (TO*)out, hidden);
+        };
+        if (nv <= 2) return go(rmsnorm_registers_kernel<TD, TO, 2>);
+        if (nv <= 4) return go(rmsnorm_registers_kernel<TD, TO, 4>);
+        return go(rmsnorm_registers_kernel<TD, TO, 8>);
+    }
     const size_t smem = (size_t)(hidden + 33) * sizeof(float);
     if (smem > 200 * 1024) return LLM_ERR_UNSUPPORTED;
     auto kernel = rmsnorm_kernel<TD, TO>;
@@ -143,7 +202,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                                      const float* __restrict__ table, int table_rows, const int* __restrict__ slot_map,
                                      T* __restrict__ pool, int H, int KV, int D, int page_size, int write_kv) {
     pdl_trigger();
-    pdl_wait();
+    // the token's position and slot are the step's own arrays, written long before: they are read while the kernel in
+    // front still runs, so that only one trip to memory (the row itself) is left behind the wait
     const int t = blockIdx.x;
     T* row = qkv + (size_t)t * row_stride;
     const int half = D >> 1;
@@ -160,6 +220,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
         v_base = ((size_t)(page * 2 + 1) * KV) * page_size * D + (size_t)off * D;
     }
     const size_t head_stride = (size_t)page_size * D;
+    pdl_wait();
 
     if ((D & 7) == 0 && (row_stride & 3) == 0) {
         // four pairs (j, j + D/2) at a time
