@@ -68,7 +68,7 @@ template <int D, int ROW_WARPS, int KEY_WARPS, int BN, int STAGES>
 int launch_shape(const AttnParams& p, int requests, cudaStream_t stream) {
     constexpr int BNC = BN * KEY_WARPS;
     size_t smem = (size_t)STAGES * 2 * BNC * D * sizeof(__nv_bfloat16);
-    const size_t merge = ((size_t)KEY_WARPS * 16 * (D + 2) + 16 * KEY_WARPS + 32) * sizeof(float);
+    const size_t merge = ((size_t)KEY_WARPS * 16 * (attn::merge_pitch(D) + 2) + 16 * KEY_WARPS + 32) * sizeof(float);
     if (KEY_WARPS > 1 && merge > smem) smem = merge;
     auto kernel = attention_mma_kernel<D, ROW_WARPS, KEY_WARPS, BN, STAGES>;
     if (smem > 40 * 1024) {  // with the kernel's static shared memory beside it, more than the 48 KB that need no opt-in

@@ -71,6 +71,9 @@ struct AttnParams {
     int skip_tokens_from;   // requests that bring at least this many tokens are another kernel's (0: none are)
 };
 
+// Floats between the rows of a warp's share where the split-key shape merges its warps through shared memory.
+__host__ __device__ constexpr int merge_pitch(int D) { return D + 8; }
+
 // Stages of the key/value ring: four where shared memory allows, three for the largest tiles.
 __host__ __device__ constexpr int stages_of(int D, int key_warps) { return D <= 64 ? 4 : 3; }
 
@@ -141,6 +144,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     constexpr int CPT = CHUNKS / TPK;         // 16-byte pieces per thread
     static_assert(THREADS % BNC == 0 && CHUNKS % TPK == 0, "a key row must split evenly over its threads");
     const int load_key = tid / TPK, load_c0 = (tid % TPK) * CPT;
+    constexpr bool WARP_PRIVATE = ROW_WARPS == 1 && TPK * BN == 32;  // thread tid copies key tid / TPK: warp w the keys [w BN, (w + 1) BN)
     // the page of this thread's key row in tile t (-1: the row lies outside the piece's keys and reads as zeros);
     // looked up one tile ahead of the copies that use it, so that a tile's latency is one trip to memory, not two
     auto page_of = [&](int t) -> int {
@@ -218,7 +222,12 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) % STAGES;
         cp_async_wait<STAGES - 2>();  // tile t has landed (this thread's copies) ...
-        cta_sync<THREADS>();              // ... everyone's; and the stage refilled next is no longer read
+        // ... everyone's; and the stage refilled next is no longer read.  Where a warp's threads copy exactly the keys
+        // that the warp itself reads (the split-key shape: two threads a key, sixteen keys a warp), "everyone" is the
+        // warp: its tiles follow one another without a meeting of the CTA, and a warp whose keys include the step's own
+        // (copied after the wait for the kernel in front) does not hold up the others
+        if constexpr (WARP_PRIVATE) __syncwarp();
+        else cta_sync<THREADS>();
         if (t + STAGES - 1 < t_end) load_tile(t + STAGES - 1, (t - t_begin + STAGES - 1) % STAGES, page_next);
         cp_async_commit();
         page_next = page_of(t + STAGES);
@@ -347,18 +356,20 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
             }
         }
     } else {
-        // merge the four warps' shares of the keys through shared memory (the key tiles are done with)
-        float* o_sm = reinterpret_cast<float*>(smem_raw);    // [KEY_WARPS][16][D]
-        float* ml_sm = o_sm + KEY_WARPS * 16 * D;            // [KEY_WARPS][16][2]
+        // merge the warps' shares of the keys through shared memory (the key tiles are done with).  A row of a share
+        // is MERGE_PITCH floats long: with D, the eight rows that a warp stores at once would meet in one bank (their
+        // places are 64 or 128 floats apart), eight times over for every one of the 2 x D / 8 stores; with D + 8 and
+        // two values a store, each half warp's sixteen stores fall into sixteen different pairs of banks.
+        constexpr int DP = merge_pitch(D);
+        float* o_sm = reinterpret_cast<float*>(smem_raw);    // [KEY_WARPS][16][DP]
+        float* ml_sm = o_sm + KEY_WARPS * 16 * DP;           // [KEY_WARPS][16][2]
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int row = qr + 8 * i;
-            float* dst = o_sm + (key_warp * 16 + row) * D + qc * 2;
+            if (row >= rows_total) continue;  // (a decode step has no more rows than the group has heads)
+            float* dst = o_sm + (key_warp * 16 + row) * DP + qc * 2;
 #pragma unroll
-            for (int nt = 0; nt < NT_O; ++nt) {
-                dst[nt * 8] = oacc[nt][2 * i];
-                dst[nt * 8 + 1] = oacc[nt][2 * i + 1];
-            }
+            for (int nt = 0; nt < NT_O; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(oacc[nt][2 * i], oacc[nt][2 * i + 1]);
             if (qc == 0) {
                 ml_sm[(key_warp * 16 + row) * 2] = m_run[i];
                 ml_sm[(key_warp * 16 + row) * 2 + 1] = l_run[i];
@@ -386,7 +397,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
 #pragma unroll
             for (int w = 0; w < KEY_WARPS; ++w) {  // a fixed order
                 const float f = f_sm[row * KEY_WARPS + w];
-                o += o_sm[(w * 16 + row) * D + d] * f;
+                o += o_sm[(w * 16 + row) * DP + d] * f;
                 l += ml_sm[(w * 16 + row) * 2 + 1] * f;
             }
             const int tok = row / G, head = kvh * G + (row - tok * G);
