@@ -67,7 +67,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 template <int D, int ROW_WARPS, int KEY_WARPS, int BN, int STAGES>
 int launch_shape(const AttnParams& p, int requests, cudaStream_t stream) {
     constexpr int BNC = BN * KEY_WARPS;
-    size_t smem = (size_t)STAGES * 2 * BNC * D * sizeof(__nv_bfloat16);
+    size_t smem = (size_t)STAGES * 2 * BNC * attn::tile_pitch(D, ROW_WARPS, KEY_WARPS, BN) * sizeof(__nv_bfloat16);
     const size_t merge = ((size_t)KEY_WARPS * 16 * (attn::merge_pitch(D) + 2) + 16 * KEY_WARPS + 32) * sizeof(float);
     if (KEY_WARPS > 1 && merge > smem) smem = merge;
     auto kernel = attention_mma_kernel<D, ROW_WARPS, KEY_WARPS, BN, STAGES>;
@@ -174,6 +174,7 @@ LLM_EXPORT int llm_attention_mma_routed(const void* q, int q_stride, void* out, 
     p.part_ml = scratch_ml;
     p.counters = counters;
     p.skip_tokens_from = skip_tokens_from;
+    p.error_flag = library_error_flag();
     switch (D) {
         case 16: return launch_all<16>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);
         case 32: return launch_all<32>(p, requests, n_tokens, token_request, max_rows_large, splits_small, splits_large, have_small, stream);

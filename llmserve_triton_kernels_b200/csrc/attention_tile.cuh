@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "timeline.cuh"
+#include "tma.cuh"
 
 namespace attn {
 
@@ -69,10 +70,23 @@ struct AttnParams {
     float* part_ml;         // [tokens, H, splits, 2]: (max in the base-2 domain, sum)
     int* counters;          // [requests * KV] zeros: how many splits of a (request, kv head) have finished
     int skip_tokens_from;   // requests that bring at least this many tokens are another kernel's (0: none are)
+    int* error_flag;        // host-visible word set to 1 if a bounded wait gave up, or null
 };
 
 // Floats between the rows of a warp's share where the split-key shape merges its warps through shared memory.
 __host__ __device__ constexpr int merge_pitch(int D) { return D + 8; }
+
+// Whether a shape brings its keys row by row with bulk copies (see attention_tile), and the elements between the rows of a
+// tile in shared memory.
+// Rows of 256 bytes and more only: with 128-byte rows (head size 64) the bulk copies themselves were the slower way
+// (35.0 against 22.4 us for 64 requests of 1,600 keys), with 256-byte rows the faster (41 against 50 us at head size 128).
+__host__ __device__ constexpr bool bulk_rows(int D, int row_warps, int key_warps, int bn) { return row_warps == 1 && key_warps > 1 && bn == 16 && D >= 128; }
+__host__ __device__ constexpr int tile_pitch(int D, int row_warps, int key_warps, int bn) { return bulk_rows(D, row_warps, key_warps, bn) ? D + 8 : D; }
+
+__device__ __forceinline__ void bulk_copy_row(void* smem, const void* gmem, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem), "r"(bytes), "r"((unsigned)__cvta_generic_to_shared(bar)) : "memory");
+}
 
 // Stages of the key/value ring: four where shared memory allows, three for the largest tiles.
 __host__ __device__ constexpr int stages_of(int D, int key_warps) { return D <= 64 ? 4 : 3; }
@@ -90,9 +104,18 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     constexpr int NT_S = BN / 8;  // 8-key tiles of a warp's scores
     constexpr int NT_O = D / 8;   // 8-wide tiles of the output
     constexpr bool SMALL = KEY_WARPS > 1;
+    // The split-key shape with 16 keys a warp: a warp's 32 lanes bring exactly the 16 key rows and 16 value rows that
+    // the warp itself reads, so no meeting of the CTA is needed between tiles (WARP_PRIVATE).  At head size 128 and more
+    // each lane brings its row as ONE bulk copy (cp.async.bulk, completion counted on a barrier of the warp's own) instead
+    // of D / 8 sixteen-byte copies: the copies' instructions, not their bytes, were what this shape waited for (the
+    // load/store unit's queue).  A bulk copy cannot swizzle, so rows then lie PITCH = D + 8 elements apart: eight rows'
+    // 16-byte pieces fall into eight different groups of four banks.
+    constexpr bool BULK = bulk_rows(D, ROW_WARPS, KEY_WARPS, BN);
+    constexpr int PITCH = tile_pitch(D, ROW_WARPS, KEY_WARPS, BN);
     // STAGES tiles in flight: a tile's latency is a page lookup plus a trip to HBM
-    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][BNC][D]
-    __nv_bfloat16* v_s = k_s + STAGES * BNC * D;                      // [STAGES][BNC][D]
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][BNC][PITCH]
+    __nv_bfloat16* v_s = k_s + STAGES * BNC * PITCH;                  // [STAGES][BNC][PITCH]
+    __shared__ __align__(8) unsigned long long rows_full[BULK ? KEY_WARPS : 1][STAGES];  // per warp and stage
 
     const int q_begin = p.cu_tokens[r], q_len = p.cu_tokens[r + 1] - q_begin;
     const int G = p.G, rows_total = q_len * G;
@@ -151,6 +174,39 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
         const int j = t * BNC + load_key;
         return t < t_end && j >= key_lo && j <= key_hi ? table[j / p.page_size] : -1;
     };
+    // ---- the bulk loader of the split-key shape: lane l < 16 brings key row l of the warp's sixteen, lane 16 + l value row l
+    const int my_row = lane & 15, is_v = lane >> 4;
+    unsigned long long* my_full = rows_full[BULK ? key_warp : 0];
+    bool waits_ok = true;
+    if constexpr (BULK) {
+        if (lane == 0) {
+#pragma unroll
+            for (int s2 = 0; s2 < STAGES; ++s2) tma::mbar_init(&my_full[s2], 1);
+            tma::mbar_fence_init();
+        }
+        __syncwarp();
+    }
+    auto bulk_page_of = [&](int t) -> int {  // the page of this lane's row in tile t, -1 if the row is not among the piece's keys
+        const int j = t * BNC + key_warp * BN + my_row;
+        return t < t_end && j >= key_lo && j <= key_hi ? table[j / p.page_size] : -1;
+    };
+    auto bulk_expect = [&](int t, int stage) {  // lane 0: the bytes that the warp's rows of tile t will bring
+        const int lo = max(t * BNC + key_warp * BN, key_lo), hi = min(t * BNC + key_warp * BN + BN - 1, key_hi);
+        const int rows = t < t_end && hi >= lo ? hi - lo + 1 : 0;
+        tma::mbar_expect_tx(&my_full[stage], (unsigned)(rows * 2 * D * 2));
+    };
+    auto bulk_row = [&](int t, int stage, int page) {  // this lane's row of tile t: copied, or zeros where there is no such key
+        const int j = t * BNC + key_warp * BN + my_row;
+        __nv_bfloat16* dst = (is_v ? v_s : k_s) + (size_t)(stage * BNC + key_warp * BN + my_row) * PITCH;
+        if (page >= 0) {
+            const size_t off = ((size_t)(page * 2 + is_v) * p.KV + kvh) * head_stride + (size_t)(j % p.page_size) * D;
+            bulk_copy_row(dst, p.pool + off, D * 2, &my_full[stage]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // (a later tile's copy may land on these bytes)
+        }
+    };
     auto load_tile = [&](int t, int stage, int page) {
         const int j = t * BNC + load_key;
         const bool valid = page >= 0;
@@ -170,8 +226,8 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     // before the wait for the kernel in front
     int first_pages[STAGES - 1];
 #pragma unroll
-    for (int i = 0; i < STAGES - 1; ++i) first_pages[i] = page_of(t_begin + i);
-    int page_next = page_of(t_begin + STAGES - 1);
+    for (int i = 0; i < STAGES - 1; ++i) first_pages[i] = BULK ? bulk_page_of(t_begin + i) : page_of(t_begin + i);
+    int page_next = BULK ? bulk_page_of(t_begin + STAGES - 1) : page_of(t_begin + STAGES - 1);
 
     // One commit group per tile, empty past the end, so that the wait in the loop counts tiles.  A tile whose keys
     // all lie before the step's first position was written by earlier steps: its copies go out before the wait for
@@ -179,10 +235,18 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
     bool asked[STAGES - 1];
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
-        asked[i] = use_pdl && t_begin + i < t_end && (t_begin + i + 1) * BNC <= pos0;
-        if (asked[i]) {
-            load_tile(t_begin + i, i, first_pages[i]);
-            cp_async_commit();
+        if constexpr (BULK) {
+            // row by row: a row that earlier steps wrote (or that does not exist) goes out now, the step's own rows behind the wait
+            const int j = (t_begin + i) * BNC + key_warp * BN + my_row;
+            if (lane == 0) bulk_expect(t_begin + i, i);
+            asked[i] = use_pdl && (j < pos0 || first_pages[i] < 0);
+            if (asked[i]) bulk_row(t_begin + i, i, first_pages[i]);
+        } else {
+            asked[i] = use_pdl && t_begin + i < t_end && (t_begin + i + 1) * BNC <= pos0;
+            if (asked[i]) {
+                load_tile(t_begin + i, i, first_pages[i]);
+                cp_async_commit();
+            }
         }
     }
     // up to here only the step's descriptor arrays and keys of earlier steps were read, which no kernel of this step
@@ -196,8 +260,12 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i) {
         if (asked[i]) continue;
-        if (t_begin + i < t_end) load_tile(t_begin + i, i, first_pages[i]);
-        cp_async_commit();
+        if constexpr (BULK) {
+            bulk_row(t_begin + i, i, first_pages[i]);
+        } else {
+            if (t_begin + i < t_end) load_tile(t_begin + i, i, first_pages[i]);
+            cp_async_commit();
+        }
     }
 
     // query fragments, straight from global memory
@@ -221,18 +289,37 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
 
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) % STAGES;
-        cp_async_wait<STAGES - 2>();  // tile t has landed (this thread's copies) ...
-        // ... everyone's; and the stage refilled next is no longer read.  Where a warp's threads copy exactly the keys
-        // that the warp itself reads (the split-key shape: two threads a key, sixteen keys a warp), "everyone" is the
-        // warp: its tiles follow one another without a meeting of the CTA, and a warp whose keys include the step's own
-        // (copied after the wait for the kernel in front) does not hold up the others
-        if constexpr (WARP_PRIVATE) __syncwarp();
-        else cta_sync<THREADS>();
-        if (t + STAGES - 1 < t_end) load_tile(t + STAGES - 1, (t - t_begin + STAGES - 1) % STAGES, page_next);
-        cp_async_commit();
-        page_next = page_of(t + STAGES);
-        const __nv_bfloat16* ks_tile = k_s + (stage * BNC + key_warp * BN) * D;
-        const __nv_bfloat16* vs_tile = v_s + (stage * BNC + key_warp * BN) * D;
+        if constexpr (BULK) {
+            // the warp's rows of tile t have landed (every lane looks at the warp's barrier: bounded); the zeros that lanes
+            // stored themselves are shown to the warp by __syncwarp, which also says that the stage refilled next (the
+            // one read in the round before) is no longer read
+            if (waits_ok && !tma::mbar_wait(&my_full[stage], ((t - t_begin) / STAGES) & 1)) {
+                waits_ok = false;
+                if (p.error_flag) atomicExch(p.error_flag, 1);
+            }
+            __syncwarp();
+            const int ahead = t + STAGES - 1, ahead_stage = (t - t_begin + STAGES - 1) % STAGES;
+            if (ahead < t_end) {
+                if (lane == 0) bulk_expect(ahead, ahead_stage);
+                bulk_row(ahead, ahead_stage, page_next);
+            }
+            page_next = bulk_page_of(t + STAGES);
+        } else {
+            cp_async_wait<STAGES - 2>();  // tile t has landed (this thread's copies) ...
+            // ... everyone's; and the stage refilled next is no longer read.  Where a warp's threads copy exactly the
+            // keys that the warp itself reads, "everyone" is the warp: its tiles follow one another without a meeting of
+            // the CTA, and a warp whose keys include the step's own (copied after the wait for the kernel in front) does
+            // not hold up the others
+            if constexpr (WARP_PRIVATE) __syncwarp();
+            else cta_sync<THREADS>();
+            if (t + STAGES - 1 < t_end) load_tile(t + STAGES - 1, (t - t_begin + STAGES - 1) % STAGES, page_next);
+            cp_async_commit();
+            page_next = page_of(t + STAGES);
+        }
+        const __nv_bfloat16* ks_tile = k_s + (stage * BNC + key_warp * BN) * PITCH;
+        const __nv_bfloat16* vs_tile = v_s + (stage * BNC + key_warp * BN) * PITCH;
+        // where 16-byte piece `chunk` of row `key` of the warp's part of the tile lies: swizzled, or rows PITCH apart
+        auto piece = [&](int key, int chunk) { return BULK ? key * PITCH + chunk * 8 : key * D + ((chunk ^ (key & SWZ)) * 8); };
         const int key_base = t * BNC + key_warp * BN;
 
         // scores: S = Q K^T
@@ -249,7 +336,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
                 const int key = np * 16 + (mi >> 1) * 8 + ri;  // row of the tile; key_warp*BN is a multiple of 8
                 const int chunk = ks * 2 + (mi & 1);
                 unsigned b[4];
-                ldmatrix_x4(b, ks_tile + key * D + ((chunk ^ (key & SWZ)) * 8));
+                ldmatrix_x4(b, ks_tile + piece(key, chunk));
                 mma_bf16(sacc[2 * np], qa[ks], b[0], b[1]);
                 mma_bf16(sacc[2 * np + 1], qa[ks], b[2], b[3]);
             }
@@ -316,7 +403,7 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
                 const int key = kk * 16 + (mi & 1) * 8 + ri;
                 const int chunk = dp * 2 + (mi >> 1);
                 unsigned b[4];
-                ldmatrix_x4_trans(b, vs_tile + key * D + ((chunk ^ (key & SWZ)) * 8));
+                ldmatrix_x4_trans(b, vs_tile + piece(key, chunk));
                 mma_bf16(oacc[2 * dp], pa, b[0], b[1]);
                 mma_bf16(oacc[2 * dp + 1], pa, b[2], b[3]);
             }

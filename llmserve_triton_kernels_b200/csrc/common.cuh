@@ -89,6 +89,10 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
+// The host-visible word that kernels without an error-flag argument of their own set when a bounded wait gives up
+// (llm_set_error_flag; null until it is set).
+int* library_error_flag();
+
 template <typename... KArgs, typename... Args>
 static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};

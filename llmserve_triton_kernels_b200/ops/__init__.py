@@ -28,6 +28,7 @@ _SIGNATURES = {
     "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "llm_add_bias": [_vp, _i, _i, _i, _i, _vp, _vp],
     "llm_fetch_words": [_vp, _vp, _vp, _i, _i, _vp],
+    "llm_set_error_flag": [_vp],
     "llm_check_step_arrays": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_check_page_group": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "llm_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -69,6 +70,8 @@ def library():
             lib.llm_error_string.argtypes = [ctypes.c_int]
             lib.llm_error_string.restype = ctypes.c_char_p
             _lib = lib
+            if torch.cuda.is_available():
+                lib.llm_set_error_flag(_error_flag_ptr())  # for kernels whose entry points take no flag of their own
     return _lib
 
 
