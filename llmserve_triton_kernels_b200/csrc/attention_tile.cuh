@@ -88,6 +88,8 @@ __device__ __forceinline__ void bulk_copy_row(void* smem, const void* gmem, unsi
                  ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem), "r"(bytes), "r"((unsigned)__cvta_generic_to_shared(bar)) : "memory");
 }
 
+constexpr float LAZY_RISE = 8.f;  // log2 of how far a row's maximum may rise before the split-key shape moves the row's shift
+
 // Stages of the key/value ring: four where shared memory allows, three for the largest tiles.
 __host__ __device__ constexpr int stages_of(int D, int key_warps) { return D <= 64 ? 4 : 3; }
 
@@ -369,9 +371,14 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
         for (int i = 0; i < 2; ++i) {
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-            const float m_new = fmaxf(m_run[i], mx[i]);
+            // the row keeps its shift while its maximum has risen by less than 2^LAZY_RISE since the shift was set (any
+            // shift gives the same quotient in the end; probabilities then reach 2^LAZY_RISE at most): the sums so far
+            // are rescaled on few tiles only
+            const float m_cand = fmaxf(m_run[i], mx[i]);
+            const bool grow = SMALL && m_run[i] != -INFINITY ? m_cand > m_run[i] + LAZY_RISE : true;
+            const float m_new = grow ? m_cand : m_run[i];
             m_use[i] = m_new == -INFINITY ? 0.f : m_new;
-            alpha[i] = fast_exp2(m_run[i] - m_use[i]);
+            alpha[i] = fast_exp2(m_run[i] - m_use[i]);  // exactly 1 where the shift stays
             m_run[i] = m_new;
             l_run[i] *= alpha[i];
         }
@@ -383,12 +390,14 @@ __device__ __forceinline__ void attention_tile(const AttnParams& p, int split, i
                 sacc[nt][e] = pv;
                 l_run[e >> 1] += pv;
             }
+        if (!SMALL || __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-        for (int nt = 0; nt < NT_O; ++nt) {
-            oacc[nt][0] *= alpha[0];
-            oacc[nt][1] *= alpha[0];
-            oacc[nt][2] *= alpha[1];
-            oacc[nt][3] *= alpha[1];
+            for (int nt = 0; nt < NT_O; ++nt) {
+                oacc[nt][0] *= alpha[0];
+                oacc[nt][1] *= alpha[0];
+                oacc[nt][2] *= alpha[1];
+                oacc[nt][3] *= alpha[1];
+            }
         }
         // O += P V
 #pragma unroll
