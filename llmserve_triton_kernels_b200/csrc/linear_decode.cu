@@ -33,7 +33,7 @@ namespace {
 using namespace lin;
 
 // One product: MT 8-token tiles (M <= 8 MT); see linear_stream.cuh for how a CTA streams.
-template <int MT, int MODE, typename TO>
+template <int MT, int MODE, typename TO, bool XREG>
 __device__ __forceinline__ void linear_decode_body(const LinearParams& p, const CUtensorMap& wmap) {
     TL(tl::Marks marks;)
     extern __shared__ __align__(1024) unsigned char smem_all[];
@@ -61,11 +61,22 @@ __device__ __forceinline__ void linear_decode_body(const LinearParams& p, const 
     pdl_wait();
     TL(marks.mark(2);)
     if constexpr (MODE == MODE_RESIDUAL) stream_fetch_resid<MT>(st, p);
-    stream_stage_x<MT>(p, x_s, row_scale);
-    __syncthreads();  // the only CTA-wide barrier
-    TL(marks.mark(3);)
-    if (!stream_run<MT, MODE, TO>(st, p, &wmap, my_ring, full[warp], red, x_s, row_scale) && lane == 0 && p.error_flag)
-        atomicExch(p.error_flag, 1);
+    bool ok;
+    if constexpr (XREG) {
+        // x straight into the registers of the lanes that multiply with it; the rows' scales are shown to the warps that
+        // end the tiles by the meeting of the team (all eight warps) that comes before any tile's end
+        uint4 xb[XREG_KB][PIECES][MT];
+        stream_fetch_x<MT>(p, st, xb);
+        stream_row_scales<MT>(p, row_scale);
+        TL(marks.mark(3);)
+        ok = stream_run<MT, MODE, TO, true>(st, p, &wmap, my_ring, full[warp], red, nullptr, row_scale, xb);
+    } else {
+        stream_stage_x<MT>(p, x_s, row_scale);
+        __syncthreads();  // the only CTA-wide barrier
+        TL(marks.mark(3);)
+        ok = stream_run<MT, MODE, TO, false>(st, p, &wmap, my_ring, full[warp], red, x_s, row_scale);
+    }
+    if (!ok && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
     TL(__syncthreads(); if (threadIdx.x == 0) { marks.mark(4); marks.t[1] = ((unsigned long long)(unsigned)st.tl_sec[0] << 48) | ((unsigned long long)(unsigned)(st.tl_sec[1] & 0xffff) << 32) | ((unsigned long long)(unsigned)(st.tl_sec[2] & 0xffff) << 16) | (unsigned)(st.tl_sec[3] & 0xffff); marks.t[3] = (marks.t[3] & ~0xffull) | (unsigned)st.tl_sec[4]; marks.t[5] = ((unsigned long long)(unsigned)st.tl_loop << 40) | ((unsigned long long)(unsigned)st.tl_sync << 20) | (unsigned)st.tl_all; marks.write(MODE, p.tl_launch, blockIdx.x, p.N, p.K); })
 }
 
@@ -74,11 +85,20 @@ __device__ __forceinline__ void linear_decode_body(const LinearParams& p, const 
 // the other); 9 to 16 tokens carry twice the accumulators and fragments and take what they need.
 template <int MODE, typename TO>
 __global__ void __maxnreg__(120) linear_decode_kernel_8(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
-    linear_decode_body<1, MODE, TO>(p, wmap);
+    linear_decode_body<1, MODE, TO, false>(p, wmap);
 }
 template <int MODE, typename TO>
 __global__ void __launch_bounds__(THREADS, 1) linear_decode_kernel_16(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
-    linear_decode_body<2, MODE, TO>(p, wmap);
+    linear_decode_body<2, MODE, TO, false>(p, wmap);
+}
+// The same with x in registers (short k, every tile shared by the CTA's eight warps): see stream_fetch_x.
+template <int MODE, typename TO>
+__global__ void __maxnreg__(120) linear_decode_xreg_kernel_8(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
+    linear_decode_body<1, MODE, TO, true>(p, wmap);
+}
+template <int MODE, typename TO>
+__global__ void __launch_bounds__(THREADS, 1) linear_decode_xreg_kernel_16(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
+    linear_decode_body<2, MODE, TO, true>(p, wmap);
 }
 
 int sm_count() {
@@ -122,16 +142,22 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     int grid = tiles < sms ? tiles : sms;
     LinearParams q = p;
     TL(static int tl_launches = 0; q.tl_launch = tl_launches++;)
-    const size_t x_bytes = (size_t)8 * MT * (p.K + X_PAD) * 2;
+    // x in registers: k short enough for XREG_KB boxes a warp when eight warps share a tile, few enough tiles a CTA for
+    // their partial sums, and not the output matrix's many tiles (their ends would all wait for one meeting)
+    static const bool xreg_on = [] { const char* e = getenv("LLMSERVE_B200_XREG"); return !e || atoi(e) != 0; }();
+    const bool xreg = xreg_on && kblocks <= XREG_KB * WARPS && (tiles + sms - 1) / sms <= 6;
+    const size_t x_bytes = xreg ? 0 : (size_t)8 * MT * (p.K + X_PAD) * 2;
     auto ring_bytes = [](int slots, int warps = WARPS) { return (size_t)warps * slots * SLOT_ELEMS * 2; };
     // A product of a few more tiles than SMs whose k is short (the stacked projection of a small model): one tile per
     // CTA, shared by its eight warps, on as many CTAs as tiles.  Each CTA then needs two boxes per warp, two such
     // CTAs fit an SM, and none has twice the work of the others.
     const size_t pair_limit = (SMEM_LIMIT + 1024) / 2 - 1024;
-    const bool one_each = MT == 1 && tiles > sms && tiles <= 2 * sms && (kblocks + WARPS - 1) / WARPS <= 2 &&
+    const bool one_each = (MT == 1 || xreg) && tiles > sms && tiles <= 2 * sms && (kblocks + WARPS - 1) / WARPS <= 2 &&
                           ring_bytes(2) + x_bytes + (size_t)WARPS * MT * 4 * 32 * sizeof(float) <= pair_limit;
     if (one_each) {
         grid = tiles;
+        q.group = WARPS;
+    } else if (xreg) {
         q.group = WARPS;
     } else {
         if (ring_bytes(SLOTS) + x_bytes > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;  // x does not fit beside the rings
@@ -151,9 +177,10 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     const size_t smem = ring_bytes(q.slots, q.ring_warps) + x_bytes + (size_t)q.red_floats * sizeof(float) + 1024;  // and room to align
     if (smem > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;
     void (*kernel)(const LinearParams, const CUtensorMap);
-    if constexpr (MT == 1) kernel = linear_decode_kernel_8<MODE, TO>;
-    else kernel = linear_decode_kernel_16<MODE, TO>;
-    static size_t configured = 0;  // per instantiation: the most dynamic shared memory asked for so far
+    if constexpr (MT == 1) kernel = xreg ? linear_decode_xreg_kernel_8<MODE, TO> : linear_decode_kernel_8<MODE, TO>;
+    else kernel = xreg ? linear_decode_xreg_kernel_16<MODE, TO> : linear_decode_kernel_16<MODE, TO>;
+    static size_t configured_of[2] = {0, 0};  // per instantiation and kernel: the most dynamic shared memory asked for so far
+    size_t& configured = configured_of[xreg ? 1 : 0];
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;

@@ -7,6 +7,7 @@
 // boxes the ring has carried so far (`base`): slots and mbarrier phases go on from one product to
 // the next.
 #pragma once
+#include <type_traits>
 
 #include "common.cuh"
 #include "tma.cuh"
@@ -232,6 +233,48 @@ __device__ __forceinline__ void stream_begin(StreamState& st, const LinearParams
     stream_arm(st, wmap, my_ring, my_full, 0);
 }
 
+// A product whose k is short (at most XREG_KB boxes a warp when its eight warps share every tile) keeps x in REGISTERS:
+// a warp multiplies the same k-blocks in every one of its tiles, so the B fragments of those blocks are loaded once,
+// straight from L2 by the lanes that use them, and no shared memory, no copy into it and no meeting of the CTA stands
+// between the wait for the kernel in front and the first product; the CTA is then small enough (its rings and the
+// partial sums) to sit beside the kernel in front also with two token tiles.
+constexpr int XREG_KB = 2;
+
+template <int MT>
+__device__ __forceinline__ void stream_fetch_x(const LinearParams& p, const StreamState& st, uint4 (&xb)[XREG_KB][PIECES][MT]) {
+    const int lane = threadIdx.x & 31, qr = lane >> 2, qc = lane & 3;
+#pragma unroll
+    for (int j = 0; j < XREG_KB; ++j) {
+        const int kb = st.member + j * st.group;
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i)
+#pragma unroll
+            for (int t = 0; t < MT; ++t) {
+                const int m = 8 * t + qr, k = kb * BOXK + i * 32 + qc * 8;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (m < p.M && kb < st.kblocks && k < p.K) v = __ldcg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + k));
+                xb[j][i][t] = v;
+            }
+    }
+}
+
+// The input rows' RMS scales into row_scale (visible to the CTA after its next barrier): row m = warp + 8 t by warp `warp`.
+template <int MT>
+__device__ __forceinline__ void stream_row_scales(const LinearParams& p, float* row_scale) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+        const int m = warp + WARPS * t;
+        float s = 1.f;
+        if (p.in_ss && m < p.M) {
+            float sum = 0.f;
+            for (int i = lane; i < p.in_parts; i += 32) sum += __ldcg(p.in_ss + (size_t)i * p.M + m);  // a fixed order: parts lane, lane + 32, ...
+            s = rsqrtf(warp_sum(sum) / (float)p.K + p.in_eps);
+        }
+        if (lane == 0) row_scale[m] = s;
+    }
+}
+
 // x into shared memory (rows beyond M as zeros) and the input rows' RMS scales; the caller synchronises the CTA.
 // Every load is asked for before the first is used: one trip to memory, not one per loop.
 template <int MT>
@@ -280,10 +323,10 @@ __device__ __forceinline__ void stream_stage_x(const LinearParams& p, __nv_bfloa
 }
 
 // The products of every box of this warp's tiles and the tiles' epilogues.  Returns false if a wait gave up.
-template <int MT, int MODE, typename TO>
+template <int MT, int MODE, typename TO, bool XREG = false>
 __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& p, const CUtensorMap* wmap, __nv_bfloat16* my_ring,
                                            unsigned long long* my_full, float* red, const __nv_bfloat16* x_s,
-                                           const float* row_scale) {
+                                           const float* row_scale, const uint4 (*xb)[PIECES][MT] = nullptr) {
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
     constexpr int CHAINS = MT == 1 ? 4 : 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -402,7 +445,9 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
             for (int c = 0; c < CHAINS; ++c)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) part[t][c][e] = 0.f;
-        for (int kb = member; kb < kblocks; kb += group, ++unit) {
+        auto box = [&](const int kb, auto jtag) {  // one box: k-block kb of this tile (jtag: which of the warp's k-blocks it is)
+            constexpr int j = decltype(jtag)::value;
+            (void)j;
             const unsigned at = st.base + unit, sl = at & (unsigned)(st.slots - 1);
             TL(const long long c0 = clock64();)
             if (!gave_up && !tma::mbar_wait(&my_full[sl], (at >> st.slots_log2) & 1)) {
@@ -423,13 +468,13 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 // beyond K the weights arrived as zeros and x is not read (its row ends there)
                 const bool have = k0 + i * 32 + qc * 8 < K;
 #pragma unroll
-                for (int t = 0; t < MT; ++t)
-                    b[i][t] = have ? *reinterpret_cast<const uint4*>(xrow[t] + k0 + i * 32) : make_uint4(0, 0, 0, 0);
+                for (int t = 0; t < MT; ++t) {
+                    if constexpr (XREG) b[i][t] = xb[j][i][t];
+                    else b[i][t] = have ? *reinterpret_cast<const uint4*>(xrow[t] + k0 + i * 32) : make_uint4(0, 0, 0, 0);
+                }
             }
-            __syncwarp();  // every lane holds its pieces of the slot in registers: the slot takes the next box
             TL(if (a[PIECES - 1][1].w == 0x7fc12345u && b[PIECES - 1][0].w == 0x7fc12345u) ++tl_dummy; const long long c2 = clock64(); tl_l += c2 - c1;)
-            if (lane == 0 && st.armed < units) arm_next(st, wmap, my_ring, my_full);
-            TL(__syncwarp(); const long long c3 = clock64(); tl_a += c3 - c2;)
+            TL(const long long c3 = c2;)
 #pragma unroll
             for (int i = 0; i < PIECES; ++i)
 #pragma unroll
@@ -437,7 +482,22 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                     mma_bf16(part[t][(2 * i) % CHAINS], a[i][0].x, a[i][1].x, a[i][0].y, a[i][1].y, b[i][t].x, b[i][t].y);
                     mma_bf16(part[t][(2 * i + 1) % CHAINS], a[i][0].z, a[i][1].z, a[i][0].w, a[i][1].w, b[i][t].z, b[i][t].w);
                 }
-            TL(if (part[0][0][0] + part[0][1][0] + part[0][CHAINS - 1][0] == -1.2345e30f) ++tl_dummy; tl_m += clock64() - c3; ++tl_n;)
+            TL(if (part[0][0][0] + part[0][1][0] + part[0][CHAINS - 1][0] == -1.2345e30f) ++tl_dummy; const long long c4 = clock64(); tl_m += c4 - c3; ++tl_n;)
+            // The slot takes the next box only now, when the products above have been issued and so have read every
+            // lane's pieces of it out of the registers: a load from shared memory is complete when its first user is
+            // issued, not when the lanes meet.  (Asked for between the loads and the products, the next box was seen
+            // to land in the slot before the loads had read it, when loads from global memory stood in the way.)
+            __syncwarp();
+            if (lane == 0 && st.armed < units) arm_next(st, wmap, my_ring, my_full);
+            TL(__syncwarp(); tl_a += clock64() - c4;)
+            ++unit;
+        };
+        if constexpr (XREG) {  // unrolled, so that xb[j] is a register
+            if (member < kblocks) box(member, std::integral_constant<int, 0>{});
+            if (member + group < kblocks) box(member + group, std::integral_constant<int, 1>{});
+            static_assert(XREG_KB == 2, "one call per k-block of a warp");
+        } else {
+            for (int kb = member; kb < kblocks; kb += group) box(kb, std::integral_constant<int, 0>{});
         }
         float acc[MT][4];
 #pragma unroll

@@ -114,6 +114,29 @@ def test_linear_swiglu_fused_for_few_rows(m, inter, k, policy, monkeypatch):
     torch.testing.assert_close(got.double(), want, atol=2e-2 * 0.05 * k**0.5, rtol=2e-2)
 
 
+@pytest.mark.parametrize("m", [1, 3, 5, 8, 11, 16])
+@pytest.mark.parametrize("inter", [5632, 1184])
+def test_weight_streaming_product_when_warps_reach_their_first_box_early(m, inter):
+    """A short k (x stays in registers, no meeting of the CTA before the first product) with fewer rows than warps:
+    the warps without a row to scale reach their first box of weights while it is still on its way, and with several
+    tiles a CTA the slot is asked for again as soon as it is read.  Repeated, with a factored norm and without, since
+    what goes wrong here goes wrong in some runs only."""
+    o = ops()
+    k, parts, eps = 2048, 128, 1e-5
+    w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=61, std=0.02)
+    for rep in range(6):
+        resid = rnd(m, k, seed=62 + rep, std=1.0 + rep % 3)
+        norm_w = 1 + rnd(k, seed=70, std=0.1)
+        xw = (resid * norm_w).to(torch.bfloat16)
+        ss = resid.view(m, parts, k // parts).pow(2).sum(-1).t().contiguous()
+        scale = torch.rsqrt(resid.double().pow(2).mean(-1, keepdim=True) + eps)
+        for x_in, x_plain in ((o.NormedInput(xw, ss, eps), xw.double() * scale), (xw, xw.double())):
+            got = o.linear_swiglu(x_in, w)
+            gate_up = x_plain @ w.double().t()
+            want = torch.nn.functional.silu(gate_up[:, :inter]) * gate_up[:, inter:]
+            torch.testing.assert_close(got.double(), want, atol=0.03, rtol=0.02)
+
+
 @pytest.mark.parametrize("m,hidden,k,n_next", [(1, 2048, 5632, 2560), (8, 2048, 2048, 11264), (16, 96, 256, 40), (3, 72, 64, 172),
                                               (5, 128, 320, 100), (128, 96, 256, 40), (300, 2048, 5632, 2560), (2048, 2048, 2048, 11264),
                                               (131, 72, 24, 172)])
