@@ -466,7 +466,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
                 a[i][0] = *reinterpret_cast<const uint4*>(slot + piece + chunk);
                 a[i][1] = *reinterpret_cast<const uint4*>(slot + piece + chunk + (SPLIT ? 8 * BOXK : 8 * 64));
                 // beyond K the weights arrived as zeros and x is not read (its row ends there)
-                const bool have = k0 + i * 32 + qc * 8 < K;
+                [[maybe_unused]] const bool have = k0 + i * 32 + qc * 8 < K;
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
                     if constexpr (XREG) b[i][t] = xb[j][i][t];
@@ -524,20 +524,20 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
     if (group > 1) {
         asm volatile("bar.sync %0, %1;\n" ::"r"(1 + warp / group), "r"(group * 32) : "memory");
         TL(tl_sync = clock64() - tl0;)
-        if (member == 0) {
-            for (int ti = 0; ti < my_tiles; ++ti) {
-                float acc[MT][4];
+        // the team's tiles are ended by its members in turn (tile ti by member ti mod group), not all by one warp while
+        // the others have nothing left to do; the first tile, whose end has values fetched early, is member 0's
+        for (int ti = member; ti < my_tiles; ti += group) {
+            float acc[MT][4];
+#pragma unroll
+            for (int t = 0; t < MT; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+            for (int w2 = warp - member; w2 < warp - member + group; ++w2)  // a fixed order
 #pragma unroll
                 for (int t = 0; t < MT; ++t)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
-                for (int w2 = warp; w2 < warp + group; ++w2)  // a fixed order
-#pragma unroll
-                    for (int t = 0; t < MT; ++t)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) acc[t][e] += red[(((size_t)ti * WARPS + w2) * (MT * 4) + t * 4 + e) * 32 + lane];
-                finish(ti, acc);
-            }
+                    for (int e = 0; e < 4; ++e) acc[t][e] += red[(((size_t)ti * WARPS + w2) * (MT * 4) + t * 4 + e) * 32 + lane];
+            finish(ti, acc);
         }
     }
     // nothing of this warp's is in flight: every armed unit was waited for above (after a failed wait, once
