@@ -33,13 +33,17 @@ namespace {
 using namespace lin;
 
 // One product: MT 8-token tiles (M <= 8 MT); see linear_stream.cuh for how a CTA streams.
-template <int MT, int MODE, typename TO, bool XREG>
-__device__ __forceinline__ void linear_decode_body(const LinearParams& p, const CUtensorMap& wmap) {
+enum { X_STAGED = 0, X_REGISTERS = 1, X_RIDES = 2 };  // where a kernel keeps x
+
+template <int MT, int MODE, typename TO, int XWHERE>
+__device__ __forceinline__ void linear_decode_body(const LinearParams& p, const CUtensorMap& wmap, const CUtensorMap* xmap = nullptr) {
+    constexpr bool XREG = XWHERE == X_REGISTERS, RIDE = XWHERE == X_RIDES;
+    constexpr int SLOT = slot_elems(MT, RIDE);
     TL(tl::Marks marks;)
     extern __shared__ __align__(1024) unsigned char smem_all[];
     unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_all + 1023) & ~(uintptr_t)1023);  // the swizzle's period
-    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [warps that have tiles][slots][SLOT_ELEMS]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)p.ring_warps * p.slots * SLOT_ELEMS * 2);  // [tiles of a team][WARPS][MT * 4][32]
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [warps that have tiles][slots][SLOT]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)p.ring_warps * p.slots * SLOT * 2);  // [tiles of a team][WARPS][MT * 4][32]
     __nv_bfloat16* x_s = reinterpret_cast<__nv_bfloat16*>(red + p.red_floats);  // [8 MT][K + X_PAD]
     __shared__ float row_scale[8 * MT];
     __shared__ __align__(8) unsigned long long full[WARPS][SLOTS];
@@ -51,11 +55,11 @@ __device__ __forceinline__ void linear_decode_body(const LinearParams& p, const 
         if (warp == 0) tma::prefetch_map(&wmap);
     }
     __syncwarp();
-    __nv_bfloat16* my_ring = ring + (size_t)warp * p.slots * SLOT_ELEMS;
+    __nv_bfloat16* my_ring = ring + (size_t)warp * p.slots * SLOT;
     StreamState st;
     // the weights do not depend on what ran before: their first boxes are asked for at once, while the
     // kernel before this one may still be running; everything else waits for it
-    stream_begin<MODE, MT>(st, p, &wmap, my_ring, full[warp], 0u);
+    stream_begin<MODE, MT, RIDE>(st, p, &wmap, my_ring, full[warp], 0u);
     pdl_trigger();
     TL(marks.mark(1);)
     pdl_wait();
@@ -70,6 +74,14 @@ __device__ __forceinline__ void linear_decode_body(const LinearParams& p, const 
         stream_row_scales<MT>(p, row_scale);
         TL(marks.mark(3);)
         ok = stream_run<MT, MODE, TO, true>(st, p, &wmap, my_ring, full[warp], red, nullptr, row_scale, xb);
+    } else if constexpr (RIDE) {
+        // every box brings its 128 k of x along: no copy of x as a whole and, when the CTA's warps are one team (whose
+        // meeting also shows the rows' scales), no barrier of the CTA
+        stream_ride_x<MT>(st, xmap, my_ring, full[warp]);
+        stream_row_scales<MT>(p, row_scale);
+        if (p.group < WARPS) __syncthreads();
+        TL(marks.mark(3);)
+        ok = stream_run<MT, MODE, TO, false, true>(st, p, &wmap, my_ring, full[warp], red, nullptr, row_scale);
     } else {
         stream_stage_x<MT>(p, x_s, row_scale);
         __syncthreads();  // the only CTA-wide barrier
@@ -85,20 +97,31 @@ __device__ __forceinline__ void linear_decode_body(const LinearParams& p, const 
 // the other); 9 to 16 tokens carry twice the accumulators and fragments and take what they need.
 template <int MODE, typename TO>
 __global__ void __maxnreg__(120) linear_decode_kernel_8(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
-    linear_decode_body<1, MODE, TO, false>(p, wmap);
+    linear_decode_body<1, MODE, TO, X_STAGED>(p, wmap);
 }
 template <int MODE, typename TO>
 __global__ void __launch_bounds__(THREADS, 1) linear_decode_kernel_16(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
-    linear_decode_body<2, MODE, TO, false>(p, wmap);
+    linear_decode_body<2, MODE, TO, X_STAGED>(p, wmap);
 }
 // The same with x in registers (short k, every tile shared by the CTA's eight warps): see stream_fetch_x.
 template <int MODE, typename TO>
 __global__ void __maxnreg__(120) linear_decode_xreg_kernel_8(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
-    linear_decode_body<1, MODE, TO, true>(p, wmap);
+    linear_decode_body<1, MODE, TO, X_REGISTERS>(p, wmap);
 }
 template <int MODE, typename TO>
 __global__ void __launch_bounds__(THREADS, 1) linear_decode_xreg_kernel_16(const LinearParams p, const __grid_constant__ CUtensorMap wmap) {
-    linear_decode_body<2, MODE, TO, true>(p, wmap);
+    linear_decode_body<2, MODE, TO, X_REGISTERS>(p, wmap);
+}
+// The same with x riding with the boxes (any k: x takes no shared memory of its own): see stream_ride_x.
+template <int MODE, typename TO>
+__global__ void __launch_bounds__(THREADS, 1) linear_decode_ride_kernel_8(const LinearParams p, const __grid_constant__ CUtensorMap wmap,
+                                                                          const __grid_constant__ CUtensorMap xmap) {
+    linear_decode_body<1, MODE, TO, X_RIDES>(p, wmap, &xmap);
+}
+template <int MODE, typename TO>
+__global__ void __launch_bounds__(THREADS, 1) linear_decode_ride_kernel_16(const LinearParams p, const __grid_constant__ CUtensorMap wmap,
+                                                                           const __grid_constant__ CUtensorMap xmap) {
+    linear_decode_body<2, MODE, TO, X_RIDES>(p, wmap, &xmap);
 }
 
 int sm_count() {
@@ -111,29 +134,71 @@ int sm_count() {
     return count;
 }
 
-// Tensor maps of weight matrices, made once per (address, shape, box).
-const CUtensorMap* weight_map(const void* w, int rows, int K, int box_rows) {
+// Tensor maps of row-major matrices [rows, K] (ld elements from row to row), made once per (address, shape, box): of
+// weight matrices, which live as long as the model, and of x where it rides with the boxes (activations of a shape come
+// back to the same addresses from a caching allocator, and a captured step keeps its buffers).
+const CUtensorMap* weight_map(const void* w, int rows, int K, int box_rows, int ld = 0) {
     struct Key {
         const void* w;
-        int rows, K, box;
-        bool operator==(const Key& o) const { return w == o.w && rows == o.rows && K == o.K && box == o.box; }
+        int rows, K, box, ld;
+        bool operator==(const Key& o) const { return w == o.w && rows == o.rows && K == o.K && box == o.box && ld == o.ld; }
     };
     struct Hash {
         size_t operator()(const Key& k) const {
-            return std::hash<const void*>()(k.w) ^ ((size_t)k.rows << 20) ^ ((size_t)k.K << 4) ^ (size_t)k.box;
+            return std::hash<const void*>()(k.w) ^ ((size_t)k.rows << 20) ^ ((size_t)k.K << 4) ^ (size_t)k.box ^ ((size_t)k.ld << 36);
         }
     };
     static std::unordered_map<Key, CUtensorMap, Hash> maps;
     static std::mutex lock;
     std::lock_guard<std::mutex> guard(lock);
-    auto it = maps.find(Key{w, rows, K, box_rows});
+    const Key key{w, rows, K, box_rows, ld};
+    auto it = maps.find(key);
     if (it != maps.end()) return &it->second;
+    if (maps.size() > 8192) maps.clear();  // maps are handed to kernels by value: none is in use between launches
     CUtensorMap map;
-    if (!tma::make_map_row_pieces_bf16(&map, w, rows, K, box_rows)) return nullptr;
-    return &maps.emplace(Key{w, rows, K, box_rows}, map).first->second;
+    if (!tma::make_map_row_pieces_bf16(&map, w, rows, K, box_rows, ld)) return nullptr;
+    return &maps.emplace(key, map).first->second;
 }
 
 constexpr size_t SMEM_LIMIT = 227 * 1024;
+
+// x rides with the boxes (stream_ride_x): a slot holds the box of weights and the same 128 k of x, and x as a whole takes no
+// shared memory, so any k is taken.  Chosen where x does not fit beside the rings, and where no CTA has more than one tile
+// (x would be read from its copy once: the copy and the barrier behind it are saved).
+template <int MT, int MODE, typename TO>
+int launch_ride(const LinearParams& p, cudaStream_t stream) {
+    constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
+    constexpr size_t SLOT_BYTES = (size_t)slot_elems(MT, true) * 2, RED_BYTES = (size_t)WARPS * MT * 4 * 32 * sizeof(float);
+    constexpr int RIDE_SLOTS = MT == 1 ? SLOTS : 3;  // 192 KB of rings either way
+    const int tiles = (p.N + FEATURES - 1) / FEATURES, kblocks = (p.K + BOXK - 1) / BOXK, sms = sm_count();
+    const int grid = tiles < sms ? tiles : sms;
+    LinearParams q = p;
+    TL(static int tl_launches = 1000; q.tl_launch = tl_launches++;)
+    const int room = (int)((SMEM_LIMIT - 1024 - (size_t)WARPS * RIDE_SLOTS * SLOT_BYTES) / RED_BYTES);
+    q.group = choose_group(tiles, kblocks, grid, room);
+    const int teams = grid * (WARPS / q.group);
+    const int boxes_each = ((tiles + teams - 1) / teams) * ((kblocks + q.group - 1) / q.group);
+    q.slots = boxes_each <= 2 ? 2 : RIDE_SLOTS;
+    q.red_floats = (int)red_floats(tiles, grid, q.group, MT);
+    const int busy_teams = (tiles + grid - 1) / grid < WARPS / q.group ? (tiles + grid - 1) / grid : WARPS / q.group;
+    q.ring_warps = busy_teams * q.group;
+    const size_t smem = (size_t)q.ring_warps * q.slots * SLOT_BYTES + (size_t)q.red_floats * sizeof(float) + 1024;
+    if (smem > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;
+    void (*kernel)(const LinearParams, const CUtensorMap, const CUtensorMap);
+    if constexpr (MT == 1) kernel = linear_decode_ride_kernel_8<MODE, TO>;
+    else kernel = linear_decode_ride_kernel_16<MODE, TO>;
+    static size_t configured = 0;  // per instantiation: the most dynamic shared memory asked for so far
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        configured = smem;
+    }
+    const CUtensorMap* wmap = weight_map(p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, MODE == MODE_QKV ? 8 : FEATURES);
+    const CUtensorMap* xmap = weight_map(p.x, p.M, p.K, 8 * MT, p.ldx);
+    if (!wmap || !xmap) return LLM_ERR_UNSUPPORTED;
+    return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, *wmap, *xmap);
+}
 
 template <int MT, int MODE, typename TO>
 int launch(const LinearParams& p, cudaStream_t stream) {
@@ -154,13 +219,16 @@ int launch(const LinearParams& p, cudaStream_t stream) {
     const size_t pair_limit = (SMEM_LIMIT + 1024) / 2 - 1024;
     const bool one_each = (MT == 1 || xreg) && tiles > sms && tiles <= 2 * sms && (kblocks + WARPS - 1) / WARPS <= 2 &&
                           ring_bytes(2) + x_bytes + (size_t)WARPS * MT * 4 * 32 * sizeof(float) <= pair_limit;
+    static const bool ride_on = [] { const char* e = getenv("LLMSERVE_B200_RIDE"); return !e || atoi(e) != 0; }();
     if (one_each) {
         grid = tiles;
         q.group = WARPS;
     } else if (xreg) {
         q.group = WARPS;
     } else {
-        if (ring_bytes(SLOTS) + x_bytes > SMEM_LIMIT) return LLM_ERR_UNSUPPORTED;  // x does not fit beside the rings
+        const bool fits = ring_bytes(SLOTS) + x_bytes <= SMEM_LIMIT;  // x beside the rings
+        if (ride_on && (!fits || tiles <= sms)) return launch_ride<MT, MODE, TO>(p, stream);
+        if (!fits) return LLM_ERR_UNSUPPORTED;
         // as many tiles of a team may be shared as their partial sums find room for
         const int room = (int)((SMEM_LIMIT - ring_bytes(SLOTS) - x_bytes) / ((size_t)WARPS * MT * 4 * 32 * sizeof(float)));
         q.group = choose_group(tiles, kblocks, grid, room);

@@ -47,7 +47,7 @@ struct LinearParams {
     float* ss_out;          // MODE_RESIDUAL: [tiles of 16 features, M]
     int* error_flag;        // set to 1 if a wait for a copy gave up (host-visible memory), or null
     int group;              // warps that share a tile: 1, 2, 4 or 8
-    int slots;              // boxes of a warp's ring: 2 or 4 (a power of two)
+    int slots;              // boxes of a warp's ring: 2 to SLOTS
     int ring_warps;         // warps that have a ring: the first ones of the CTA, those whose teams have tiles
     int red_floats;         // floats of shared memory for the teams' partial sums (red_floats() below)
     // MODE_QKV: w rows are [H query heads | KV key heads | KV value heads] x D; out is [M, H * D]
@@ -64,6 +64,8 @@ constexpr int SLOTS = 4;   // most boxes per warp, all in flight but for the mom
                            // a product whose warps never have more than two boxes is given two (LinearParams::slots)
 constexpr int BOXK = 128;  // k per box: a slot is 16 rows x 128 k = 4 KB
 constexpr int SLOT_ELEMS = 16 * BOXK;
+// elements of a slot: the box of weights and, where x rides with the boxes, the same 128 k of the MT token tiles of x
+__host__ __device__ constexpr int slot_elems(int MT, bool ride) { return SLOT_ELEMS + (ride ? MT * 8 * BOXK : 0); }
 constexpr int PIECES = BOXK / 32;
 constexpr int X_PAD = 32;  // elements between the rows of x in shared memory: 8 tokens x 64 bytes hit 8 bank groups
 
@@ -101,7 +103,10 @@ inline size_t red_floats(int tiles, int grid, int group, int MT) {
 
 struct StreamState {
     int group, member, tiles, kblocks, first, stride, my_tiles, units;
-    int slots, slots_log2;  // boxes of this warp's ring
+    int slots;              // boxes of this warp's ring
+    int arm_slot;           // the slot the next box asked for goes to
+    int my_kblocks;         // k-blocks of a tile that this warp multiplies
+    const CUtensorMap* xmap;  // x rides with the boxes and may be read (the kernel in front has ended): its map; else null
     int tl_sec[5];
     int tl_loop, tl_sync, tl_all;  // profiling builds: cycles from the start of stream_run to the end of the boxes, of the team's meeting, of all
     int a_ti, a_kb, armed;
@@ -120,10 +125,12 @@ struct StreamState {
 // Asks for the next box of the product whose state is `st` (lane 0 only).  The slot and its mbarrier phase follow
 // from the number of boxes the ring has carried, so a product's boxes may be asked for while the product before
 // it is still being computed.
+template <int MT = 1, bool RIDE = false>
 __device__ __forceinline__ void arm_next(StreamState& st, const CUtensorMap* wmap, __nv_bfloat16* my_ring, unsigned long long* my_full) {
-    const int tile = st.first + st.a_ti * st.stride, sl = (st.base + st.armed) & (st.slots - 1);
-    __nv_bfloat16* dst = my_ring + (size_t)sl * SLOT_ELEMS;
-    tma::mbar_expect_tx(&my_full[sl], (unsigned)(SLOT_ELEMS * 2));
+    constexpr int SLOT = slot_elems(MT, RIDE);
+    const int tile = st.first + st.a_ti * st.stride, sl = st.arm_slot;
+    __nv_bfloat16* dst = my_ring + (size_t)sl * SLOT;
+    tma::mbar_expect_tx(&my_full[sl], (unsigned)(SLOT * 2));  // the weights, and x where it rides
     const int piece = st.a_kb * (BOXK / 64);  // the box's two 64-k pieces of its rows (see tma::make_map_row_pieces_bf16)
     if (st.mode == MODE_SWIGLU) {  // the map's box is 8 rows: gate rows, then up rows
         tma::load_3d(dst, wmap, 0, tile * 8, piece, &my_full[sl]);
@@ -135,6 +142,10 @@ __device__ __forceinline__ void arm_next(StreamState& st, const CUtensorMap* wma
     } else {
         tma::load_3d(dst, wmap, 0, tile * 16, piece, &my_full[sl]);
     }
+    // the same k of every row of x behind the weights (before x may be read, stream_ride_x sends it after the box)
+    if constexpr (RIDE)
+        if (st.xmap) tma::load_3d(dst + SLOT_ELEMS, st.xmap, 0, 0, piece, &my_full[sl]);
+    if (++st.arm_slot == st.slots) st.arm_slot = 0;
     ++st.armed;
     st.a_kb += st.group;
     if (st.a_kb >= st.kblocks) {
@@ -152,15 +163,16 @@ __device__ __forceinline__ void stream_plan(StreamState& st, const LinearParams&
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     st.group = p.group;
     st.slots = p.slots;
-    st.slots_log2 = p.slots == 2 ? 1 : 2;
+    st.arm_slot = (int)(base % (unsigned)p.slots);
+    st.xmap = nullptr;
     st.member = warp % st.group;
     st.tiles = (p.N + FEATURES - 1) / FEATURES;
     st.kblocks = (p.K + BOXK - 1) / BOXK;
     st.first = blockIdx.x + (warp / st.group) * gridDim.x;
     st.stride = gridDim.x * (WARPS / st.group);
     st.my_tiles = st.tiles > st.first ? (st.tiles - 1 - st.first) / st.stride + 1 : 0;
-    const int my_kblocks = st.kblocks > st.member ? (st.kblocks - 1 - st.member) / st.group + 1 : 0;
-    st.units = st.my_tiles * my_kblocks;
+    st.my_kblocks = st.kblocks > st.member ? (st.kblocks - 1 - st.member) / st.group + 1 : 0;
+    st.units = st.my_tiles * st.my_kblocks;
     st.a_ti = 0;
     st.a_kb = st.member;
     st.armed = 0;
@@ -220,17 +232,35 @@ __device__ __forceinline__ void stream_fetch_resid(StreamState& st, const Linear
 }
 
 // Fills the free slots of the ring with the product's next boxes; `consumed`: how many of its boxes have been used.
+template <int MT = 1, bool RIDE = false>
 __device__ __forceinline__ void stream_arm(StreamState& st, const CUtensorMap* wmap, __nv_bfloat16* my_ring, unsigned long long* my_full,
                                            int consumed) {
     if ((threadIdx.x & 31) == 0)
-        while (st.armed < st.units && st.armed < consumed + st.slots) arm_next(st, wmap, my_ring, my_full);
+        while (st.armed < st.units && st.armed < consumed + st.slots) arm_next<MT, RIDE>(st, wmap, my_ring, my_full);
 }
 
-template <int MODE, int MT = 1>
+template <int MODE, int MT = 1, bool RIDE = false>
 __device__ __forceinline__ void stream_begin(StreamState& st, const LinearParams& p, const CUtensorMap* wmap,
                                              __nv_bfloat16* my_ring, unsigned long long* my_full, unsigned base) {
     stream_plan<MODE, MT>(st, p, base);
-    stream_arm(st, wmap, my_ring, my_full, 0);
+    stream_arm<MT, RIDE>(st, wmap, my_ring, my_full, 0);
+}
+
+// Where x rides with the boxes: sends x after the boxes that were asked for before x could be read (none of them has been
+// used yet), and lets every later box bring its x along.  Lane 0 of the warp asks, as for the boxes.
+template <int MT>
+__device__ __forceinline__ void stream_ride_x(StreamState& st, const CUtensorMap* xmap, __nv_bfloat16* my_ring,
+                                              unsigned long long* my_full) {
+    constexpr int SLOT = slot_elems(MT, true);
+    st.xmap = xmap;
+    if ((threadIdx.x & 31) != 0) return;
+    int sl = (int)(st.base % (unsigned)st.slots), j = 0;
+    for (int u = 0; u < st.armed; ++u) {
+        const int kb = st.member + j * st.group;
+        tma::load_3d(my_ring + (size_t)sl * SLOT + SLOT_ELEMS, xmap, 0, 0, kb * (BOXK / 64), &my_full[sl]);
+        if (++sl == st.slots) sl = 0;
+        if (++j == st.my_kblocks) j = 0;
+    }
 }
 
 // A product whose k is short (at most XREG_KB boxes a warp when its eight warps share every tile) keeps x in REGISTERS:
@@ -323,12 +353,13 @@ __device__ __forceinline__ void stream_stage_x(const LinearParams& p, __nv_bfloa
 }
 
 // The products of every box of this warp's tiles and the tiles' epilogues.  Returns false if a wait gave up.
-template <int MT, int MODE, typename TO, bool XREG = false>
+template <int MT, int MODE, typename TO, bool XREG = false, bool RIDE = false>
 __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& p, const CUtensorMap* wmap, __nv_bfloat16* my_ring,
                                            unsigned long long* my_full, float* red, const __nv_bfloat16* x_s,
                                            const float* row_scale, const uint4 (*xb)[PIECES][MT] = nullptr) {
     constexpr int FEATURES = MODE == MODE_SWIGLU ? 8 : 16;
     constexpr int CHAINS = MT == 1 ? 4 : 2;
+    constexpr int SLOT = slot_elems(MT, RIDE);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qr = lane >> 2, qc = lane & 3;  // MMA row (a feature of the tile) and column pair (tokens) of this thread
     const int fr = feature_row(qr);           // the feature of the tile that MMA row qr stands for
@@ -434,6 +465,8 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
     };
 
     int unit = 0;
+    int sl = (int)(st.base % (unsigned)st.slots);            // the slot of the next box and the phase of its mbarrier
+    unsigned phase = (st.base / (unsigned)st.slots) & 1u;
     TL(const long long tl0 = clock64(); long long tl_loop = 0, tl_sync = 0, tl_w = 0, tl_l = 0, tl_a = 0, tl_m = 0; int tl_n = 0, tl_dummy = 0;)
     for (int ti = 0; ti < my_tiles; ++ti) {
         // CHAINS independent sums per token tile, joined when the tile is complete: an MMA waits for the one before it
@@ -448,15 +481,15 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
         auto box = [&](const int kb, auto jtag) {  // one box: k-block kb of this tile (jtag: which of the warp's k-blocks it is)
             constexpr int j = decltype(jtag)::value;
             (void)j;
-            const unsigned at = st.base + unit, sl = at & (unsigned)(st.slots - 1);
             TL(const long long c0 = clock64();)
-            if (!gave_up && !tma::mbar_wait(&my_full[sl], (at >> st.slots_log2) & 1)) {
+            if (!gave_up && !tma::mbar_wait(&my_full[sl], phase)) {
                 gave_up = true;
                 if (p.error_flag) atomicExch(p.error_flag, 1);
             }
             TL(const long long c1 = clock64(); tl_w += c1 - c0;)
             // the box lies as [2 pieces of 64 k][rows][64] with the 128-byte swizzle: chunk c of row r at chunk c ^ (r & 7)
-            const __nv_bfloat16* slot = my_ring + (size_t)sl * SLOT_ELEMS + fr * 64;
+            const __nv_bfloat16* slot = my_ring + (size_t)sl * SLOT + fr * 64;
+            [[maybe_unused]] const __nv_bfloat16* xs = my_ring + (size_t)sl * SLOT + SLOT_ELEMS;  // RIDE: [2 pieces][8 MT rows][64]
             const int k0 = kb * BOXK;
             uint4 a[PIECES][2], b[PIECES][MT];
 #pragma unroll
@@ -470,7 +503,10 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
                     if constexpr (XREG) b[i][t] = xb[j][i][t];
-                    else b[i][t] = have ? *reinterpret_cast<const uint4*>(xrow[t] + k0 + i * 32) : make_uint4(0, 0, 0, 0);
+                    else if constexpr (RIDE) {  // rows beyond M and k beyond K arrived as zeros
+                        const int row = 8 * t + qr;
+                        b[i][t] = *reinterpret_cast<const uint4*>(xs + (i >> 1) * (8 * MT * 64) + row * 64 + (((((i & 1) << 2) | qc) ^ (row & 7)) * 8));
+                    } else b[i][t] = have ? *reinterpret_cast<const uint4*>(xrow[t] + k0 + i * 32) : make_uint4(0, 0, 0, 0);
                 }
             }
             TL(if (a[PIECES - 1][1].w == 0x7fc12345u && b[PIECES - 1][0].w == 0x7fc12345u) ++tl_dummy; const long long c2 = clock64(); tl_l += c2 - c1;)
@@ -488,9 +524,13 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
             // issued, not when the lanes meet.  (Asked for between the loads and the products, the next box was seen
             // to land in the slot before the loads had read it, when loads from global memory stood in the way.)
             __syncwarp();
-            if (lane == 0 && st.armed < units) arm_next(st, wmap, my_ring, my_full);
+            if (lane == 0 && st.armed < units) arm_next<MT, RIDE>(st, wmap, my_ring, my_full);
             TL(__syncwarp(); tl_a += clock64() - c4;)
             ++unit;
+            if (++sl == st.slots) {
+                sl = 0;
+                phase ^= 1u;
+            }
         };
         if constexpr (XREG) {  // unrolled, so that xb[j] is a register
             if (member < kblocks) box(member, std::integral_constant<int, 0>{});
@@ -544,7 +584,7 @@ __device__ __forceinline__ bool stream_run(StreamState& st, const LinearParams& 
     // more here, bounded, so that no copy lands in shared memory after the CTA has left)
     if (gave_up && lane == 0)
         for (unit = max(0, units - st.slots); unit < units; ++unit)
-            tma::mbar_wait(&my_full[(st.base + unit) & (unsigned)(st.slots - 1)], ((st.base + unit) >> st.slots_log2) & 1);
+            tma::mbar_wait(&my_full[(st.base + unit) % (unsigned)st.slots], ((st.base + unit) / (unsigned)st.slots) & 1u);
     TL(if (threadIdx.x == 0) { st.tl_loop = (int)tl_loop; st.tl_sync = (int)tl_sync; st.tl_all = (int)(clock64() - tl0) + (tl_dummy & 1);
        st.tl_sec[0] = (int)tl_w; st.tl_sec[1] = (int)tl_l; st.tl_sec[2] = (int)tl_a; st.tl_sec[3] = (int)tl_m; st.tl_sec[4] = tl_n; })
     return !gave_up;

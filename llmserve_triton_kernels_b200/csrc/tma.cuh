@@ -48,11 +48,12 @@ inline bool make_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, 
 // A map over a row-major 16-bit matrix [rows, cols], cols a multiple of 64, seen as [cols / 64][rows][64]: a box is
 // `box_rows` rows of two consecutive 64-element pieces, laid down in shared memory as [2][box_rows][64] with the
 // 128-byte swizzle (the 16-byte chunk c of row r lies at chunk c ^ (r & 7)).  Coordinates: (0, row, piece).
-inline bool make_map_row_pieces_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+inline bool make_map_row_pieces_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                                     uint64_t ld = 0) {  // ld: elements from row to row (0: cols)
     EncodeTiledFn fn = encode_fn();
     if (!fn || cols % 64) return false;
     const cuuint64_t dims[3] = {64, rows, cols / 64};
-    const cuuint64_t strides[2] = {cols * 2, 128};  // bytes between rows, between pieces
+    const cuuint64_t strides[2] = {(ld ? ld : cols) * 2, 128};  // bytes between rows, between pieces
     const cuuint32_t box[3] = {64, box_rows, 2};
     const cuuint32_t elem[3] = {1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,

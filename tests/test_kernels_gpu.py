@@ -85,7 +85,8 @@ def test_linear_float32_is_true_32_bit_and_row_independent(m, n, k):
     "m,n,k",
     [(1, 48, 64), (9, 344, 96), (130, 2560, 2048), (64, 100, 172), (8, 2560, 2048), (64, 11264, 2048), (33, 2048, 5632),
      (5, 40, 72), (17, 100, 48), (3, 64, 88), (16, 17, 8), (1, 32000, 2048), (2048, 2048, 5632), (257, 129, 8), (128, 128, 64),
-     (1000, 3000, 1096), (5, 2048, 5632), (8, 1000, 3008), (1, 2368, 6144)],
+     (1000, 3000, 1096), (5, 2048, 5632), (8, 1000, 3008), (1, 2368, 6144), (13, 2048, 5632), (16, 4096, 11008),
+     (7, 3000, 28672)],
 )
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("policy", ["own", "auto"])
@@ -102,7 +103,7 @@ def test_linear_bfloat16(m, n, k, out_dtype, policy, monkeypatch):
 
 @pytest.mark.parametrize("m,inter,k", [(1, 5632, 2048), (8, 172 * 8, 64), (16, 100, 96), (5, 16, 8), (17, 100, 96), (300, 5632, 2048),
                                        (129, 200, 72), (2048, 1000, 256), (64, 5632, 2048), (127, 172 * 8, 64), (33, 100, 96),
-                                       (50, 102, 104), (3, 1184, 4096), (8, 500, 2304)])
+                                       (50, 102, 104), (3, 1184, 4096), (8, 500, 2304), (16, 1184, 4096), (11, 3000, 14336)])
 @pytest.mark.parametrize("policy", ["own", "auto"])
 def test_linear_swiglu_fused_for_few_rows(m, inter, k, policy, monkeypatch):
     monkeypatch.setattr(ops(), "_GEMM_POLICY", policy)
@@ -139,7 +140,8 @@ def test_weight_streaming_product_when_warps_reach_their_first_box_early(m, inte
 
 @pytest.mark.parametrize("m,hidden,k,n_next", [(1, 2048, 5632, 2560), (8, 2048, 2048, 11264), (16, 96, 256, 40), (3, 72, 64, 172),
                                               (5, 128, 320, 100), (128, 96, 256, 40), (300, 2048, 5632, 2560), (2048, 2048, 2048, 11264),
-                                              (131, 72, 24, 172), (8, 2048, 5632, 2560), (7, 1000, 3008, 172)])
+                                              (131, 72, 24, 172), (8, 2048, 5632, 2560), (7, 1000, 3008, 172), (16, 2048, 5632, 2560),
+                                              (12, 4096, 11008, 100)])
 def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
     """A product that adds into the residual stream and hands it on in factored normalised form,
     and the next product that consumes that form: together they must equal
@@ -181,7 +183,7 @@ def test_residual_sink_and_factored_norm(m, hidden, k, n_next):
 @pytest.mark.parametrize("m,H,KV,D,hidden,page_size,rotate", [(1, 32, 4, 64, 2048, 16, True), (8, 4, 2, 16, 64, 8, True),
                                                             (16, 3, 1, 32, 192, 4, True), (5, 6, 3, 128, 320, 16, False),
                                                             (2, 5, 0, 48, 128, 1, True), (9, 32, 4, 64, 2048, 16, True),
-                                                            (4, 8, 2, 64, 4096, 16, True)])
+                                                            (4, 8, 2, 64, 4096, 16, True), (12, 8, 2, 128, 4096, 16, True)])
 def test_linear_qkv_rope_fused_for_few_rows(m, H, KV, D, hidden, page_size, rotate):
     """Projection, rotation and cache write in one kernel against the three done plainly."""
     o = ops()
