@@ -13,6 +13,11 @@
 // side — a sum over k does not care about the order — so the fragments need no shuffles and no
 // ldmatrix.
 //
+// Where x lives is chosen per launch (see launch()): in the registers of the lanes that multiply with it
+// (k <= 2048, few tiles a CTA), riding with the weight boxes (one tile a CTA, or x too long for shared
+// memory), or copied into shared memory once (x reused over many tiles).  The first two have no barrier of
+// the CTA before the first product.
+//
 // Fused ends (decode steps are bound by launches as much as by bytes):
 //   * input in factored normalised form: x holds v * norm_weight (v the residual stream) and
 //     in_ss holds partial sums of v^2 per row; the product is scaled by rsqrt(sum / K + eps) at the
