@@ -37,8 +37,9 @@ namespace {
 
 using namespace lin;
 
-// One product: MT 8-token tiles (M <= 8 MT); see linear_stream.cuh for how a CTA streams.
 enum { X_STAGED = 0, X_REGISTERS = 1, X_RIDES = 2 };  // where a kernel keeps x
+
+// One product: MT 8-token tiles (M <= 8 MT); see linear_stream.cuh for how a CTA streams.
 
 template <int MT, int MODE, typename TO, int XWHERE>
 __device__ __forceinline__ void linear_decode_body(const LinearParams& p, const CUtensorMap& wmap, const CUtensorMap* xmap = nullptr) {
@@ -142,7 +143,8 @@ int sm_count() {
 // Tensor maps of row-major matrices [rows, K] (ld elements from row to row), made once per (address, shape, box): of
 // weight matrices, which live as long as the model, and of x where it rides with the boxes (activations of a shape come
 // back to the same addresses from a caching allocator, and a captured step keeps its buffers).
-const CUtensorMap* weight_map(const void* w, int rows, int K, int box_rows, int ld = 0) {
+// The map is handed out by value: an entry may be dropped by the next call.
+bool weight_map(CUtensorMap* out, const void* w, int rows, int K, int box_rows, int ld = 0) {
     struct Key {
         const void* w;
         int rows, K, box, ld;
@@ -158,11 +160,14 @@ const CUtensorMap* weight_map(const void* w, int rows, int K, int box_rows, int 
     std::lock_guard<std::mutex> guard(lock);
     const Key key{w, rows, K, box_rows, ld};
     auto it = maps.find(key);
-    if (it != maps.end()) return &it->second;
-    if (maps.size() > 8192) maps.clear();  // maps are handed to kernels by value: none is in use between launches
-    CUtensorMap map;
-    if (!tma::make_map_row_pieces_bf16(&map, w, rows, K, box_rows, ld)) return nullptr;
-    return &maps.emplace(key, map).first->second;
+    if (it != maps.end()) {
+        *out = it->second;
+        return true;
+    }
+    if (maps.size() > 8192) maps.clear();  // (activations that never came back to the same address)
+    if (!tma::make_map_row_pieces_bf16(out, w, rows, K, box_rows, ld)) return false;
+    maps.emplace(key, *out);
+    return true;
 }
 
 constexpr size_t SMEM_LIMIT = 227 * 1024;
@@ -199,10 +204,11 @@ int launch_ride(const LinearParams& p, cudaStream_t stream) {
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = smem;
     }
-    const CUtensorMap* wmap = weight_map(p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, MODE == MODE_QKV ? 8 : FEATURES);
-    const CUtensorMap* xmap = weight_map(p.x, p.M, p.K, 8 * MT, p.ldx);
-    if (!wmap || !xmap) return LLM_ERR_UNSUPPORTED;
-    return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, *wmap, *xmap);
+    CUtensorMap wmap, xmap;
+    if (!weight_map(&wmap, p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, MODE == MODE_QKV ? 8 : FEATURES) ||
+        !weight_map(&xmap, p.x, p.M, p.K, 8 * MT, p.ldx))
+        return LLM_ERR_UNSUPPORTED;
+    return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, wmap, xmap);
 }
 
 template <int MT, int MODE, typename TO>
@@ -261,9 +267,9 @@ int launch(const LinearParams& p, cudaStream_t stream) {
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = smem;
     }
-    const CUtensorMap* map = weight_map(p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, MODE == MODE_QKV ? 8 : FEATURES);
-    if (!map) return LLM_ERR_UNSUPPORTED;
-    return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, *map);
+    CUtensorMap map;
+    if (!weight_map(&map, p.w, MODE == MODE_SWIGLU ? p.up_offset + p.N : p.N, p.K, MODE == MODE_QKV ? 8 : FEATURES)) return LLM_ERR_UNSUPPORTED;
+    return launch_pdl(kernel, dim3(grid), dim3(THREADS), smem, stream, q, map);
 }
 
 // MODE_QKV: the product for all heads, rotary encoding of query and key heads, and the write of keys and
